@@ -1,0 +1,204 @@
+/*
+ * C ABI of libmegamoe_sm100.so: the sm_100a kernels behind the `mega_moe` Python
+ * operator (expert-parallel MoE layer: routing metadata, dispatch, FC1 + weighted
+ * gated activation, FC2 + combine, top-k reduce, and the five backward stages).
+ *
+ * The reference implementation (Mega-MoE-TD) has no foreign-function boundary of
+ * its own: its Python operator launches Triton-Ascend kernels directly.  Each entry
+ * point below therefore names the reference *launch site* it stands in for
+ * (path:line inside the reference project).  `mega_moe/_native.py` binds all of them
+ * with ctypes; INTEGRATION.md shows the binding.
+ *
+ * Conventions
+ *   - every function returns 0 (MM_OK) or a negative MM_ERR_* code and never throws;
+ *     mm_last_error() returns the message of the calling thread's last failure;
+ *   - all pointers are device pointers unless a parameter says "host";
+ *   - the library never takes ownership of caller memory;
+ *   - kernels are enqueued on `stream` and the call returns without synchronising,
+ *     unless the comment says "synchronous";
+ *   - bf16 tensors are passed as void*, int32 index tables as int32_t*;
+ *   - device-side waits are bounded: a wait that runs out writes an mm_status_record
+ *     into the caller's status buffer and the kernel returns normally.
+ */
+#ifndef MEGA_MOE_B200_H_
+#define MEGA_MOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef __CUDA_RUNTIME_H__
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
+enum {
+  MM_OK = 0,
+  MM_ERR_ARG = -1,   /* invalid argument (shape, alignment, null pointer) */
+  MM_ERR_CUDA = -2,  /* a CUDA runtime / driver call failed */
+  MM_ERR_LIMIT = -3  /* request exceeds a fixed limit of the entry point */
+};
+
+/* Activation selector shared by forward and backward (reference: config.py:28-32). */
+enum { MM_ACT_SWIGLU = 0, MM_ACT_SITUGLU = 1, MM_ACT_CLAMP_SWIGLU = 2 };
+
+/* Device status record (32 bytes).  code: 0 ok, 1 wait timed out, 2 receive-capacity
+ * overflow, 3 bad index.  Mirrors the reference's bounded-spin diagnostic record
+ * (kernels/dispatch_fc2_bwd.py:23-42). */
+typedef struct mm_status_record {
+  int32_t code, site, slot, want, seen, block, pad0, pad1;
+} mm_status_record;
+
+/* ---- library ---------------------------------------------------------------- */
+int mm_abi_version(void);
+const char* mm_last_error(void);
+/* Number of SMs of the current device (persistent grids are sized from it; stands in
+ * for the AICore-count query of config.py:37-62). */
+int mm_num_sms(int* out_host);
+
+/* ---- status ------------------------------------------------------------------ */
+int mm_status_reset(void* status, cudaStream_t stream);
+/* synchronous: waits for `stream`, then copies the record to host memory */
+int mm_status_read(const void* status, mm_status_record* out_host, cudaStream_t stream);
+
+/* ---- symmetric buffers over CUDA IPC (reference: runtime/workspace.py:159-222,
+ *      aclshmem_create_tensor / aclshmem_free_tensor) ----------------------------- */
+int mm_symm_alloc(size_t bytes, void** dptr_host, unsigned char handle_host[64]);
+int mm_symm_open(const unsigned char handle_host[64], void** peer_ptr_host);
+int mm_symm_close(void* peer_ptr);
+int mm_symm_free(void* dptr);
+
+/* Cross-rank barrier through flag words in symmetric memory: writes `epoch` into slot
+ * [rank] of every peer's flag array, then waits (bounded) until all `world` slots of the
+ * local array hold a value >= epoch.  peer_flags: device array of `world` pointers.
+ * Stands in for libshmem_device.barrier_all_vec() (runtime/routing.py:91,142). */
+int mm_rank_barrier(int32_t* const* peer_flags, int rank, int world, int epoch, void* status,
+                    cudaStream_t stream);
+
+/* ---- routing metadata --------------------------------------------------------- */
+/* Scratch bytes mm_route_local needs for `num_routes` routes and `bins` count bins. */
+size_t mm_route_scratch_bytes(int num_routes, int bins);
+
+/* Route filter + stable expert-major sort + local count row
+ * (reference: runtime/routing.py:635-671 and kernels/fused_forward.py:158-190,307-447).
+ *   selected        [num_routes] flat [T, k] expert ids; valid iff 0 <= id < num_experts
+ *   send_route      [num_routes] out: flat route id of each send row (valid prefix)
+ *   send_token      [num_routes] out: route id / top_k
+ *   send_bucket     [num_routes] out: expert id of each send row
+ *   route_to_send   [num_routes] out: inverse permutation, -1 for dropped routes
+ *   count_row       [bins] out: routes per expert, zero padded
+ *   local_stats     [2] out: {number of valid routes, 0}
+ */
+int mm_route_local(const int32_t* selected, int num_routes, int top_k, int num_experts, int bins,
+                   int32_t* send_route, int32_t* send_token, int32_t* send_bucket,
+                   int32_t* route_to_send, int32_t* count_row, int32_t* local_stats, void* scratch,
+                   size_t scratch_bytes, cudaStream_t stream);
+
+/* Offsets from the replicated count cube [world, bins]
+ * (reference: runtime/routing.py:93-140,318-416; kernels/fused_forward.py:241-304,337-358,
+ * 450-480).  Also builds the 128-row tile table of the grouped GEMMs (the counterpart of
+ * ops/_torch_forward.py:103-128) and, per received row, the source rank and the row's
+ * position in that source's send order (kernels/fc2_combine.py:82-136).
+ *   send_bucket_starts, send_bucket_dst_starts   [world * epr]
+ *   recv_counts_re [world, epr]   recv_per_expert [epr]   recv_expert_offs [epr + 1]
+ *   recv_seg_starts [epr, world + 1]   pull_dst_start [epr * world]
+ *   stats [2 + world] = {M, max over destinations, per-destination totals}
+ *   mtile_group / mtile_row0 [capacity_rows / 128 + epr]   num_mtiles [1]
+ *   row_src_rank / row_src_pos [capacity_rows]
+ * If M exceeds capacity_rows the status record gets code 2 and num_mtiles is 0. */
+int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, int bins,
+                      int capacity_rows, int32_t* send_bucket_starts,
+                      int32_t* send_bucket_dst_starts, int32_t* recv_counts_re,
+                      int32_t* recv_per_expert, int32_t* recv_expert_offs,
+                      int32_t* recv_seg_starts, int32_t* pull_dst_start, int32_t* stats,
+                      int32_t* mtile_group, int32_t* mtile_row0, int32_t* num_mtiles,
+                      int32_t* row_src_rank, int32_t* row_src_pos, void* status,
+                      cudaStream_t stream);
+
+/* ---- dispatch / combine data movement ---------------------------------------------- */
+/* Push send row i (= src[send_token[i]]) to rank send_bucket[i] / epr at row
+ * send_bucket_dst_starts[b] + (i - send_bucket_starts[b]) of that rank's receive buffer,
+ * with its fp32 routing weight alongside when `weights` is not null
+ * (reference: kernels/dispatch_fc1.py:365-508; kernels/dispatch_fc2_bwd.py:254-306).
+ *   peer_rows / peer_weights: device arrays of `world` base pointers. */
+int mm_dispatch_rows(const void* src, int hidden, const float* weights, const int32_t* send_token,
+                     const int32_t* send_route, const int32_t* send_bucket,
+                     const int32_t* send_bucket_starts, const int32_t* send_bucket_dst_starts,
+                     const int32_t* local_stats, int max_routes, int epr, int capacity_rows,
+                     void* const* peer_rows, float* const* peer_weights, cudaStream_t stream);
+
+/* out[t] = bf16(sum_j fp32(rows[route_to_send[t*k + j]])) in slot order, -1 skipped
+ * (reference: kernels/fused_forward.py:1319-1387).  When gate_in is not null also
+ * gate_out[t, j] = gate_in[route_to_send[t*k + j]] (0 for dropped), the routing-weight
+ * gradient gather of kernels/combine_fc1_bwd.py:357-394. */
+int mm_topk_reduce(const void* rows, int64_t ld_rows, const int32_t* route_to_send, int tokens,
+                   int top_k, int hidden, void* out, const void* gate_in, void* gate_out,
+                   cudaStream_t stream);
+
+/* ---- grouped GEMMs (tcgen05 / TMEM) ------------------------------------------------- */
+typedef struct mm_gemm_desc {
+  const void* a;              /* [a_rows_cap, K] bf16 rows grouped by expert */
+  int64_t lda;                /* elements between A rows */
+  int64_t a_rows_cap;         /* rows the buffer holds (tensor-map extent) */
+  const void* b;              /* per-group weights */
+  int32_t b_k_major;          /* 1: [g][n][k] with k contiguous; 0: [g][k][n] with n contiguous */
+  int32_t b_cols_total;       /* n extent of the weight table (2F for the packed gate|up table) */
+  int64_t b_ld;               /* elements between consecutive rows of one group's matrix */
+  int64_t b_group_stride;     /* elements between groups */
+  int32_t num_groups;
+  int32_t N;                  /* output columns (fused FC1: F) */
+  int32_t K;                  /* reduction extent */
+  int32_t grid_limit;         /* 0: one CTA per SM */
+  const int32_t* group_offs;  /* [num_groups + 1] */
+  const int32_t* mtile_group; /* from mm_route_finalize */
+  const int32_t* mtile_row0;
+  const int32_t* num_mtiles;
+  void* status;
+} mm_gemm_desc;
+
+/* FC1 with the weighted gated activation fused in the epilogue
+ * (reference: kernels/fused_forward.py:551-876).  b is the packed [E, H, 2F] table
+ * (b_k_major = 0, b_cols_total = 2F, N = F).
+ *   act_out [rows, F] = bf16(f(bf16(gate), bf16(up)) * row_weight)
+ *   raw_out [rows, 2F] = bf16 gate | up (may be null) */
+int mm_fc1_swiglu(const mm_gemm_desc* d, void* act_out, int64_t ld_act, void* raw_out,
+                  int64_t ld_raw, const float* row_weight, int activation, float beta,
+                  float linear_beta, float clamp_limit, cudaStream_t stream);
+
+/* out[rows of g, 0:N] = bf16(A[rows of g] * B_g)
+ * (reference: kernels/dispatch_fc1.py:580-751 for FC1 without activation,
+ *  kernels/dispatch_fc2_bwd.py:309-485 for the FC2 input gradient). */
+int mm_grouped_gemm(const mm_gemm_desc* d, void* out, int64_t ld_out, cudaStream_t stream);
+
+/* Same product, but each output row is stored into rank row_dst_rank[row]'s buffer at row
+ * row_dst_pos[row] (reference: FC2 + return, kernels/fused_forward.py:1010-1025,1161-1279;
+ * FC1 input gradient + push, kernels/combine_fc1_bwd.py:114-286). */
+int mm_grouped_gemm_scatter(const mm_gemm_desc* d, const int32_t* row_dst_rank,
+                            const int32_t* row_dst_pos, void* const* peer_bases, int64_t ld_dst,
+                            cudaStream_t stream);
+
+/* Weight gradient: out[g][m', n'] = bf16(sum over rows of g: grad_out[row, m'] * orig_in[row, n'])
+ * (reference: kernels/transposed_grouped_gemm.py:24-66; kernels/mega_bwd.py:394-493).
+ * Groups without rows produce zeros. */
+int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void* orig_in,
+                     int64_t ld_in, int32_t Nw, int64_t rows_cap, const int32_t* group_offs,
+                     int32_t num_groups, void* out, int64_t ld_out, int64_t out_group_stride,
+                     void* status, int32_t grid_limit, cudaStream_t stream);
+
+/* ---- backward stage 2 ------------------------------------------------------------- */
+/* Gated-activation backward per received row (reference: kernels/swiglu_bwd.py:15-83):
+ *   grad_fc1 [rows, 2F] = dGate | dUp (bf16), grad_scale [rows] = bf16(sum f(g) v(u) dC).
+ * `num_rows` is read from device memory (stats[0]).  When peer_gate is not null the row's
+ * grad_scale is also stored to rank row_dst_rank[row] at peer_gate[rank][row_dst_pos[row]]. */
+int mm_swiglu_bwd(const void* grad_act, int64_t ld_ga, const void* fc1_out, int64_t ld_fc1,
+                  const void* row_scale_bf16, int ffn, const int32_t* num_rows, int max_rows,
+                  void* grad_fc1, int64_t ld_gf, void* grad_scale, int activation, float beta,
+                  float linear_beta, float clamp_limit, const int32_t* row_dst_rank,
+                  const int32_t* row_dst_pos, void* const* peer_gate, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MEGA_MOE_B200_H_ */

@@ -1,0 +1,252 @@
+// Host-side launchers of the tcgen05 grouped GEMM: tensor-map construction and the
+// four C-ABI entry points that use it (declared in include/mega_moe_b200.h).
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "gemm_sm100.cuh"
+#include "internal.h"
+
+namespace mm {
+
+namespace {
+
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+std::once_flag g_encode_once;
+
+bool load_encode_fn() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  });
+  return g_encode != nullptr;
+}
+
+// bf16 tensor map with a 128-byte swizzle; dims/strides innermost first, strides in bytes
+// for dimensions 1.. (dimension 0 is contiguous).
+bool encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                const uint64_t* strides_bytes, const uint32_t* box) {
+  if (!load_encode_fn()) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  cuuint64_t gdim[3];
+  cuuint64_t gstr[2];
+  cuuint32_t bdim[3];
+  cuuint32_t estr[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    if (i > 0) gstr[i - 1] = strides_bytes[i - 1];
+  }
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
+                        const_cast<void*>(base), gdim, gstr, bdim, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed (code %d): rank=%d dims=%llu,%llu box=%u,%u base=%p",
+              (int)r, rank, (unsigned long long)dims[0], (unsigned long long)dims[1], box[0],
+              box[1], base);
+    return false;
+  }
+  return true;
+}
+
+std::once_flag g_attr_once;
+int g_num_sms = 0;
+
+bool prepare_kernel() {
+  static bool ok = false;
+  std::call_once(g_attr_once, [] {
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(grouped_gemm_kernel): %s", cudaGetErrorString(e));
+      return;
+    }
+    ok = true;
+  });
+  if (!ok) return false;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return false;
+  return true;
+}
+
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid_limit,
+           cudaStream_t stream) {
+  if (!prepare_kernel()) return MM_ERR_CUDA;
+  int grid = g_num_sms;
+  if (grid_limit > 0 && grid_limit < grid) grid = grid_limit;
+  grouped_gemm_kernel<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(tmA, tmB, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("grouped_gemm_kernel launch: %s", cudaGetErrorString(e));
+    return MM_ERR_CUDA;
+  }
+  return MM_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// A rows [a_rows_cap, K] (K contiguous, leading dimension lda elements).
+// B per group: b_k_major != 0 -> [N_total, K] with K contiguous; else [K, N_total] with N contiguous.
+int grouped_rows_gemm(int epi, const mm_gemm_desc& d, GemmParams p, cudaStream_t stream) {
+  if (!aligned16(d.a) || !aligned16(d.b) || (d.lda % 8) || (d.b_ld % 8) || (d.b_group_stride % 8)) {
+    set_error("grouped GEMM operands must be 16-byte aligned with strides that are multiples of 8");
+    return MM_ERR_ARG;
+  }
+  if (d.K <= 0 || (d.K % 8) || d.N <= 0 || (d.N % 32)) {
+    set_error("grouped GEMM needs K %% 8 == 0 and N %% 32 == 0 (K=%d N=%d)", d.K, d.N);
+    return MM_ERR_ARG;
+  }
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[2] = {(uint64_t)d.K, (uint64_t)d.a_rows_cap};
+    uint64_t str[1] = {(uint64_t)d.lda * 2};
+    uint32_t box[2] = {64, (uint32_t)kBlockM};
+    if (!encode_map(&tmA, d.a, 2, dims, str, box)) return MM_ERR_CUDA;
+  }
+  const int b_cols = d.b_cols_total;  // full column extent of B (2F for the packed gate|up table)
+  if (d.b_k_major) {
+    uint64_t dims[3] = {(uint64_t)d.K, (uint64_t)b_cols, (uint64_t)d.num_groups};
+    uint64_t str[2] = {(uint64_t)d.b_ld * 2, (uint64_t)d.b_group_stride * 2};
+    uint32_t box[3] = {64, (uint32_t)kBlockN, 1};
+    if (!encode_map(&tmB, d.b, 3, dims, str, box)) return MM_ERR_CUDA;
+  } else {
+    uint64_t dims[3] = {(uint64_t)b_cols, (uint64_t)d.K, (uint64_t)d.num_groups};
+    uint64_t str[2] = {(uint64_t)d.b_ld * 2, (uint64_t)d.b_group_stride * 2};
+    uint32_t box[3] = {64, 64, 1};
+    if (!encode_map(&tmB, d.b, 3, dims, str, box)) return MM_ERR_CUDA;
+  }
+  p.kind = kGroupedRows;
+  p.epi = epi;
+  p.num_groups = d.num_groups;
+  p.N = d.N;
+  p.K = d.K;
+  p.a_mn = 0;
+  p.b_mn = d.b_k_major ? 0 : 1;
+  p.idesc = make_idesc_bf16(kBlockM, kBlockN, 0, p.b_mn);
+  p.group_offs = d.group_offs;
+  p.mtile_group = d.mtile_group;
+  p.mtile_row0 = d.mtile_row0;
+  p.num_mtiles = d.num_mtiles;
+  p.status = reinterpret_cast<StatusRecord*>(d.status);
+  if (epi == kEpiSwiglu) {
+    if (d.b_k_major || (d.N % 128)) {
+      set_error("fused FC1 needs the [E, H, 2F] weight layout and F %% 128 == 0");
+      return MM_ERR_ARG;
+    }
+    p.n_tiles = d.N / (kBlockN / 2);
+    p.swiglu_F = d.N;
+  } else {
+    p.n_tiles = (d.N + kBlockN - 1) / kBlockN;
+    p.swiglu_F = 0;
+  }
+  return launch(tmA, tmB, p, d.grid_limit, stream);
+}
+
+}  // namespace mm
+
+using namespace mm;
+
+extern "C" {
+
+int mm_fc1_swiglu(const mm_gemm_desc* d, void* act_out, int64_t ld_act, void* raw_out,
+                  int64_t ld_raw, const float* row_weight, int activation, float beta,
+                  float linear_beta, float clamp_limit, cudaStream_t stream) {
+  if (!d || !act_out || !row_weight) {
+    set_error("mm_fc1_swiglu: null argument");
+    return MM_ERR_ARG;
+  }
+  GemmParams p{};
+  p.out = reinterpret_cast<__nv_bfloat16*>(act_out);
+  p.ld_out = ld_act;
+  p.out2 = reinterpret_cast<__nv_bfloat16*>(raw_out);
+  p.ld_out2 = ld_raw;
+  p.row_weight = row_weight;
+  p.act = activation;
+  p.act_beta = beta;
+  p.act_linear_beta = linear_beta;
+  p.act_clamp = clamp_limit;
+  return grouped_rows_gemm(kEpiSwiglu, *d, p, stream);
+}
+
+int mm_grouped_gemm(const mm_gemm_desc* d, void* out, int64_t ld_out, cudaStream_t stream) {
+  if (!d || !out) {
+    set_error("mm_grouped_gemm: null argument");
+    return MM_ERR_ARG;
+  }
+  GemmParams p{};
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.ld_out = ld_out;
+  return grouped_rows_gemm(kEpiStore, *d, p, stream);
+}
+
+int mm_grouped_gemm_scatter(const mm_gemm_desc* d, const int32_t* row_dst_rank,
+                            const int32_t* row_dst_pos, void* const* peer_bases, int64_t ld_dst,
+                            cudaStream_t stream) {
+  if (!d || !row_dst_rank || !row_dst_pos || !peer_bases) {
+    set_error("mm_grouped_gemm_scatter: null argument");
+    return MM_ERR_ARG;
+  }
+  GemmParams p{};
+  p.row_dst_rank = row_dst_rank;
+  p.row_dst_pos = row_dst_pos;
+  p.peer_bases = reinterpret_cast<__nv_bfloat16* const*>(peer_bases);
+  p.ld_dst = ld_dst;
+  return grouped_rows_gemm(kEpiScatter, *d, p, stream);
+}
+
+int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void* orig_in,
+                     int64_t ld_in, int32_t Nw, int64_t rows_cap, const int32_t* group_offs,
+                     int32_t num_groups, void* out, int64_t ld_out, int64_t out_group_stride,
+                     void* status, int32_t grid_limit, cudaStream_t stream) {
+  if (!grad_out || !orig_in || !group_offs || !out) {
+    set_error("mm_grouped_wgrad: null argument");
+    return MM_ERR_ARG;
+  }
+  if ((Mw % 8) || (Nw % 32) || (ld_go % 8) || (ld_in % 8) || (ld_out % 8) ||
+      (out_group_stride % 8)) {
+    set_error("mm_grouped_wgrad: extents/strides must be multiples of 8 (Nw of 32)");
+    return MM_ERR_ARG;
+  }
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[2] = {(uint64_t)Mw, (uint64_t)rows_cap};
+    uint64_t str[1] = {(uint64_t)ld_go * 2};
+    uint32_t box[2] = {64, 64};
+    if (!encode_map(&tmA, grad_out, 2, dims, str, box)) return MM_ERR_CUDA;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)Nw, (uint64_t)rows_cap, 1};
+    uint64_t str[2] = {(uint64_t)ld_in * 2, (uint64_t)ld_in * 2 * (uint64_t)rows_cap};
+    uint32_t box[3] = {64, 64, 1};
+    if (!encode_map(&tmB, orig_in, 3, dims, str, box)) return MM_ERR_CUDA;
+  }
+  GemmParams p{};
+  p.kind = kGroupedReduce;
+  p.epi = kEpiStore;
+  p.num_groups = num_groups;
+  p.N = Nw;
+  p.Mw = Mw;
+  p.a_mn = 1;
+  p.b_mn = 1;
+  p.idesc = make_idesc_bf16(kBlockM, kBlockN, 1, 1);
+  p.m_tiles = (Mw + kBlockM - 1) / kBlockM;
+  p.n_tiles = (Nw + kBlockN - 1) / kBlockN;
+  p.group_offs = group_offs;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.ld_out = ld_out;
+  p.out_group_stride = out_group_stride;
+  p.status = reinterpret_cast<StatusRecord*>(status);
+  return launch(tmA, tmB, p, grid_limit, stream);
+}
+
+}  // extern "C"

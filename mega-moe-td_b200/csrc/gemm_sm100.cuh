@@ -1,0 +1,429 @@
+// Grouped GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM -> epilogue.
+//
+// One persistent CTA per SM, six warps:
+//   warp 0      TMA producer (one lane issues cp.async.bulk.tensor loads)
+//   warp 1      TMEM allocator and MMA issuer (one lane issues tcgen05.mma)
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, convert, stage, store
+// A four-stage shared-memory ring feeds the tensor core; two 128x256 fp32
+// accumulators in TMEM let the epilogue of tile i overlap the main loop of i+1.
+//
+// Two problem kinds share the kernel:
+//   kGroupedRows  out[rows of group g, :] = A[rows of g, 0:K] * B_g      (ragged M)
+//       used for FC1, FC2 and the two input-gradient GEMMs
+//   kGroupedReduce out_g[m', n'] = sum over rows of g: A[row, m'] * B[row, n'] (ragged K)
+//       used for the two weight-gradient GEMMs; both operands are MN-major
+#pragma once
+
+#include "common.cuh"
+
+namespace mm {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kStageABytes = kBlockM * kBlockK * 2;               // 16 KB
+constexpr int kStageBBytes = kBlockN * kBlockK * 2;               // 32 KB
+constexpr int kStageBytes = kStageABytes + kStageBBytes;          // 48 KB
+constexpr int kBoxBytes = 64 * 64 * 2;                            // one 64x64 MN-major box
+constexpr int kEpiWarps = 4;
+constexpr int kStagingPerWarp = 3 * 32 * 64;                      // three 32-row x 64-byte buffers
+constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
+constexpr int kTmemCols = 512;
+constexpr int kGemmSmemBytes =
+    kStages * kStageBytes + kEpiWarps * kStagingPerWarp + 256 /*barriers*/ + 1024 /*alignment*/;
+
+enum GemmKind : int32_t { kGroupedRows = 0, kGroupedReduce = 1 };
+enum EpiMode : int32_t { kEpiStore = 0, kEpiSwiglu = 1, kEpiScatter = 2 };
+enum Activation : int32_t { kActSwiglu = 0, kActSitu = 1, kActClampSwiglu = 2 };
+
+struct GemmParams {
+  int32_t kind;
+  int32_t epi;
+  int32_t num_groups;
+  int32_t N;             // logical output columns (kEpiSwiglu: F; kGroupedReduce: n' extent)
+  int32_t K;             // reduction extent (kGroupedRows)
+  int32_t Mw;            // kGroupedReduce: m' extent
+  int32_t a_mn;          // A operand is MN-major
+  int32_t b_mn;          // B operand is MN-major
+  int32_t n_tiles;       // tiles along N (kEpiSwiglu: F / 128)
+  int32_t m_tiles;       // kGroupedReduce: tiles along m'
+  int32_t swiglu_F;      // column offset of the "up" half inside B and inside out2
+  int32_t act;
+  float act_beta;
+  float act_linear_beta; // <= 0: no transform on up
+  float act_clamp;
+  uint32_t idesc;
+  const int32_t* group_offs;    // [num_groups + 1] row offsets of each group
+  const int32_t* mtile_group;   // kGroupedRows: group of each 128-row tile
+  const int32_t* mtile_row0;    // kGroupedRows: first row of each 128-row tile
+  const int32_t* num_mtiles;    // kGroupedRows: device scalar, number of 128-row tiles
+  __nv_bfloat16* out;
+  int64_t ld_out;
+  int64_t out_group_stride;     // kGroupedReduce: elements between consecutive groups
+  __nv_bfloat16* out2;          // kEpiSwiglu: raw gate|up rows, may be null
+  int64_t ld_out2;
+  const float* row_weight;      // kEpiSwiglu: fp32 weight of each row
+  const int32_t* row_dst_rank;  // kEpiScatter: destination rank of each row
+  const int32_t* row_dst_pos;   // kEpiScatter: destination row index
+  __nv_bfloat16* const* peer_bases;  // kEpiScatter: base pointer of the destination buffer per rank
+  int64_t ld_dst;
+  StatusRecord* status;
+};
+
+struct TileInfo {
+  int32_t group;
+  int32_t row0;        // kGroupedRows: first A row; kGroupedReduce: first m' index
+  int32_t rows_valid;  // rows of the 128-row tile that carry output
+  int32_t n0;          // first output column (kEpiSwiglu: first F column)
+  int32_t num_kb;      // k-blocks of 64
+  int32_t krow0;       // kGroupedReduce: first reduction row
+  int32_t kcnt;        // kGroupedReduce: number of reduction rows
+};
+
+__device__ __forceinline__ int32_t total_tiles(const GemmParams& p) {
+  if (p.kind == kGroupedRows) return (*p.num_mtiles) * p.n_tiles;
+  return p.num_groups * p.m_tiles * p.n_tiles;
+}
+
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int32_t t, int32_t nmt) {
+  TileInfo ti;
+  if (p.kind == kGroupedRows) {
+    const int32_t nt = t / nmt;
+    const int32_t mt = t - nt * nmt;
+    ti.group = p.mtile_group[mt];
+    ti.row0 = p.mtile_row0[mt];
+    const int32_t end = p.group_offs[ti.group + 1];
+    ti.rows_valid = min(kBlockM, end - ti.row0);
+    ti.n0 = nt * (p.epi == kEpiSwiglu ? kBlockN / 2 : kBlockN);
+    ti.num_kb = (p.K + kBlockK - 1) / kBlockK;
+    ti.krow0 = 0;
+    ti.kcnt = 0;
+  } else {
+    const int32_t per_group = p.m_tiles * p.n_tiles;
+    ti.group = t / per_group;
+    const int32_t r = t - ti.group * per_group;
+    const int32_t nt = r / p.m_tiles;
+    const int32_t mt = r - nt * p.m_tiles;
+    ti.row0 = mt * kBlockM;
+    ti.rows_valid = min(kBlockM, p.Mw - ti.row0);
+    ti.n0 = nt * kBlockN;
+    ti.krow0 = p.group_offs[ti.group];
+    ti.kcnt = p.group_offs[ti.group + 1] - ti.krow0;
+    ti.num_kb = (ti.kcnt + kBlockK - 1) / kBlockK;
+  }
+  return ti;
+}
+
+__device__ __forceinline__ float gated_activation(float g, float u, const GemmParams& p) {
+  if (p.act == kActSwiglu) {
+    return g / (1.0f + __expf(-g)) * u;
+  } else if (p.act == kActClampSwiglu) {
+    g = fminf(g, p.act_clamp);
+    u = fminf(fmaxf(u, -p.act_clamp), p.act_clamp);
+    return g / (1.0f + __expf(-g)) * u;
+  } else {
+    const float a = p.act_beta * tanhf(g / p.act_beta) / (1.0f + __expf(-g));
+    if (p.act_linear_beta > 0.0f) u = p.act_linear_beta * tanhf(u / p.act_linear_beta);
+    return a * u;
+  }
+}
+
+// Write 32 bf16 values of this lane's row into a 32-row x 64-byte staging buffer
+// (16-byte chunks XOR-swizzled by row so that both phases are bank-conflict free).
+__device__ __forceinline__ void stage_row(uint8_t* stg, uint32_t lane, const uint32_t (&v)[16]) {
+  const uint32_t sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint4 q = make_uint4(v[4 * c + 0], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    *reinterpret_cast<uint4*>(stg + lane * 64 + ((c ^ sw) << 4)) = q;
+  }
+}
+
+// Store a staged 32 x 32 bf16 block: each warp instruction writes 8 rows x 64 bytes.
+// row_ptr is this lane's row base (already offset to the block's first column).
+__device__ __forceinline__ void flush_rows(const uint8_t* stg, uint32_t lane, uint8_t* row_ptr,
+                                           int valid) {
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const uint32_t r = it * 8 + (lane >> 2);
+    const uint32_t c = lane & 3;
+    const uint4 q = *reinterpret_cast<const uint4*>(stg + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+    const uint64_t pr = __shfl_sync(0xffffffffu, (unsigned long long)row_ptr, r);
+    const int ok = __shfl_sync(0xffffffffu, valid, r);
+    if (ok) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pr) + c * 16) = q;
+  }
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stages = smem;
+  uint8_t* staging = smem + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpiWarps * kStagingPerWarp);
+  uint64_t* full_bar = bars;                  // [kStages]
+  uint64_t* empty_bar = bars + kStages;       // [kStages]
+  uint64_t* tmem_full = bars + 2 * kStages;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;       // [2]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], kEpiWarps * 32);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  const int32_t nmt = (p.kind == kGroupedRows) ? *p.num_mtiles : 0;
+  const int32_t ntiles = total_tiles(p);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int32_t t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
+        const TileInfo ti = decode_tile(p, t, nmt);
+        for (int kb = 0; kb < ti.num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kSiteSmemEmpty, stage)) {
+            alive = false;
+            break;
+          }
+          uint8_t* sA = stages + stage * kStageBytes;
+          uint8_t* sB = sA + kStageABytes;
+          mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+          if (p.kind == kGroupedRows) {
+            const int32_t k0 = kb * kBlockK;
+            tma_load_2d(sA, &tmA, &full_bar[stage], k0, ti.row0);
+            if (!p.b_mn) {
+              tma_load_3d(sB, &tmB, &full_bar[stage], k0, ti.n0, ti.group);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                int32_t col;
+                if (p.epi == kEpiSwiglu) {
+                  col = (i < 2) ? (ti.n0 + 64 * i) : (p.swiglu_F + ti.n0 + 64 * (i - 2));
+                } else {
+                  col = ti.n0 + 64 * i;
+                }
+                tma_load_3d(sB + i * kBoxBytes, &tmB, &full_bar[stage], col, k0, ti.group);
+              }
+            }
+          } else {
+            const int32_t kr = ti.krow0 + kb * kBlockK;
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              tma_load_2d(sA + i * kBoxBytes, &tmA, &full_bar[stage], ti.row0 + 64 * i, kr);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              tma_load_3d(sB + i * kBoxBytes, &tmB, &full_bar[stage], ti.n0 + 64 * i, kr, 0);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!alive) {
+        // Give loads already in flight time to land before the CTA retires.
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 1000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool alive = true;
+    const uint32_t a_lbo = p.a_mn ? (uint32_t)kBoxBytes : 16u;
+    const uint32_t b_lbo = p.b_mn ? (uint32_t)kBoxBytes : 16u;
+    const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
+    const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+    for (int32_t t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
+      const TileInfo ti = decode_tile(p, t, nmt);
+      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kSiteTmemEmpty, acc)) {
+        alive = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + acc * kBlockN;
+      for (int kb = 0; kb < ti.num_kb; ++kb) {
+        if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kSiteSmemFull, stage)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
+        uint8_t* sA = stages + stage * kStageBytes;
+        if (p.kind == kGroupedReduce) {
+          const int32_t valid = ti.kcnt - kb * kBlockK;
+          if (valid < kBlockK) {
+            // Rows past the end of the group belong to the next group: clear them in
+            // all six 64x64 boxes (K rows are 128 contiguous bytes in this layout).
+            const int32_t first = valid * 128;
+            for (int b = 0; b < 6; ++b) {
+              uint8_t* box = sA + b * kBoxBytes;
+              for (int32_t off = first + lane * 16; off < kBoxBytes; off += 32 * 16)
+                *reinterpret_cast<uint4*>(box + off) = make_uint4(0, 0, 0, 0);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+        }
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(sA);
+          const uint32_t b_addr = a_addr + kStageABytes;
+          const uint64_t a_desc = make_smem_desc(a_addr, a_lbo, 1024);
+          const uint64_t b_desc = make_smem_desc(b_addr, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            umma_f16(d_tmem, a_desc + (uint64_t)(k * a_kstep), b_desc + (uint64_t)(k * b_kstep),
+                     p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!alive) break;
+      if (lane == 0) umma_commit(&tmem_full[acc]);
+      __syncwarp();
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
+    const uint32_t ew = warp - 2;
+    uint8_t* stg = staging + ew * kStagingPerWarp;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int32_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      const TileInfo ti = decode_tile(p, t, nmt);
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, kSiteTmemFull, acc)) break;
+      tc_fence_after_sync();
+      const int32_t row = q * 32 + lane;
+      const int valid = row < ti.rows_valid;
+      const uint32_t t_acc = tmem_base + acc * kBlockN + ((q * 32u) << 16);
+
+      if (p.epi == kEpiSwiglu) {
+        const int64_t grow = (int64_t)ti.row0 + row;
+        uint8_t* act_ptr = reinterpret_cast<uint8_t*>(p.out + grow * p.ld_out + ti.n0);
+        uint8_t* raw_ptr =
+            p.out2 ? reinterpret_cast<uint8_t*>(p.out2 + grow * p.ld_out2 + ti.n0) : nullptr;
+        const float w = valid ? p.row_weight[grow] : 0.0f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(t_acc + c * 32, rg);
+          tmem_ld_32x32(t_acc + 128 + c * 32, ru);
+          tmem_ld_wait();
+          uint32_t pa[16], pg[16], pu[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g0 = bf16_round(__uint_as_float(rg[2 * j]));
+            const float g1 = bf16_round(__uint_as_float(rg[2 * j + 1]));
+            const float u0 = bf16_round(__uint_as_float(ru[2 * j]));
+            const float u1 = bf16_round(__uint_as_float(ru[2 * j + 1]));
+            pg[j] = pack_bf16x2(g0, g1);
+            pu[j] = pack_bf16x2(u0, u1);
+            pa[j] = pack_bf16x2(gated_activation(g0, u0, p) * w, gated_activation(g1, u1, p) * w);
+          }
+          stage_row(stg, lane, pa);
+          if (raw_ptr) {
+            stage_row(stg + 2048, lane, pg);
+            stage_row(stg + 4096, lane, pu);
+          }
+          __syncwarp();
+          flush_rows(stg, lane, act_ptr + c * 64, valid);
+          if (raw_ptr) {
+            flush_rows(stg + 2048, lane, raw_ptr + c * 64, valid);
+            flush_rows(stg + 4096, lane, raw_ptr + (int64_t)p.swiglu_F * 2 + c * 64, valid);
+          }
+          __syncwarp();
+        }
+      } else {
+        uint8_t* row_ptr = nullptr;
+        if (valid) {
+          if (p.epi == kEpiScatter) {
+            const int64_t grow = (int64_t)ti.row0 + row;
+            const int32_t rk = p.row_dst_rank[grow];
+            const int64_t pos = p.row_dst_pos[grow];
+            row_ptr = reinterpret_cast<uint8_t*>(p.peer_bases[rk] + pos * p.ld_dst + ti.n0);
+          } else if (p.kind == kGroupedRows) {
+            row_ptr =
+                reinterpret_cast<uint8_t*>(p.out + ((int64_t)ti.row0 + row) * p.ld_out + ti.n0);
+          } else {
+            row_ptr = reinterpret_cast<uint8_t*>(p.out + (int64_t)ti.group * p.out_group_stride +
+                                                 ((int64_t)ti.row0 + row) * p.ld_out + ti.n0);
+          }
+        }
+        const bool zero_tile = (ti.num_kb == 0);
+#pragma unroll 1
+        for (int c = 0; c < kBlockN / 32; ++c) {
+          if (ti.n0 + c * 32 >= p.N) break;
+          uint32_t r[32];
+          uint32_t pk[16];
+          if (!zero_tile) {
+            tmem_ld_32x32(t_acc + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              pk[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) pk[j] = 0u;
+          }
+          stage_row(stg, lane, pk);
+          __syncwarp();
+          flush_rows(stg, lane, row_ptr + c * 64, valid);
+          __syncwarp();
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tmem_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace mm

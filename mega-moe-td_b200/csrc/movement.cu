@@ -1,0 +1,319 @@
+// HBM / NVLink bound kernels around the grouped GEMMs: dispatch (row push into the
+// owning rank's receive buffer), top-k reduce (gather-sum of returned rows), the gated
+// activation backward, and the cross-rank flag barrier.
+#include "common.cuh"
+#include "internal.h"
+
+namespace mm {
+
+__device__ __forceinline__ uint4 ld_nc_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void st_16(void* p, const uint4& v) {
+  asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+// ---------------------------------------------------------------------------------
+// Dispatch: one warp per send row, 16 bytes per lane per step, four steps in flight.
+// ---------------------------------------------------------------------------------
+constexpr int kDispatchThreads = 256;
+
+__global__ void __launch_bounds__(kDispatchThreads)
+dispatch_rows_kernel(const uint8_t* __restrict__ src, int row_bytes,
+                     const float* __restrict__ weights, const int32_t* __restrict__ send_token,
+                     const int32_t* __restrict__ send_route, const int32_t* __restrict__ send_bucket,
+                     const int32_t* __restrict__ send_bucket_starts,
+                     const int32_t* __restrict__ send_bucket_dst_starts,
+                     const int32_t* __restrict__ local_stats, int epr, int capacity_rows,
+                     void* const* __restrict__ peer_rows, float* const* __restrict__ peer_weights) {
+  const int n = local_stats[0];
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = kDispatchThreads / 32;
+  const int chunks = row_bytes >> 4;
+  for (int i = blockIdx.x * warps_per_block + (threadIdx.x >> 5); i < n;
+       i += gridDim.x * warps_per_block) {
+    const int b = send_bucket[i];
+    const int dst_rank = b / epr;
+    const int dst_row = send_bucket_dst_starts[b] + (i - send_bucket_starts[b]);
+    if (dst_row >= capacity_rows) continue;  // overflow is reported by the metadata kernel
+    const uint8_t* s = src + (size_t)send_token[i] * row_bytes;
+    uint8_t* d = reinterpret_cast<uint8_t*>(peer_rows[dst_rank]) + (size_t)dst_row * row_bytes;
+    int c = lane;
+    for (; c + 96 < chunks; c += 128) {
+      const uint4 v0 = ld_nc_16(s + (size_t)c * 16);
+      const uint4 v1 = ld_nc_16(s + (size_t)(c + 32) * 16);
+      const uint4 v2 = ld_nc_16(s + (size_t)(c + 64) * 16);
+      const uint4 v3 = ld_nc_16(s + (size_t)(c + 96) * 16);
+      st_16(d + (size_t)c * 16, v0);
+      st_16(d + (size_t)(c + 32) * 16, v1);
+      st_16(d + (size_t)(c + 64) * 16, v2);
+      st_16(d + (size_t)(c + 96) * 16, v3);
+    }
+    for (; c < chunks; c += 32) st_16(d + (size_t)c * 16, ld_nc_16(s + (size_t)c * 16));
+    if (weights != nullptr && lane == 0) peer_weights[dst_rank][dst_row] = weights[send_route[i]];
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Top-k reduce: out[t] = bf16(sum_j fp32(rows[route_to_send[t*k + j]])), slot order.
+// One block per token; each thread owns 16-byte column chunks.
+// ---------------------------------------------------------------------------------
+constexpr int kReduceThreads = 256;
+constexpr int kMaxTopK = 64;
+
+__global__ void __launch_bounds__(kReduceThreads)
+topk_reduce_kernel(const uint8_t* __restrict__ rows, int64_t ld_bytes,
+                   const int32_t* __restrict__ route_to_send, int tokens, int top_k, int row_bytes,
+                   uint8_t* __restrict__ out, const __nv_bfloat16* __restrict__ gate_in,
+                   __nv_bfloat16* __restrict__ gate_out) {
+  __shared__ int32_t idx[kMaxTopK];
+  const int chunks = row_bytes >> 4;
+  for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
+    __syncthreads();
+    if (threadIdx.x < top_k) {
+      const int32_t r = route_to_send[(size_t)t * top_k + threadIdx.x];
+      idx[threadIdx.x] = r;
+      if (gate_in != nullptr)
+        gate_out[(size_t)t * top_k + threadIdx.x] = r >= 0 ? gate_in[r] : __float2bfloat16(0.0f);
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < chunks; c += kReduceThreads) {
+      float acc[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] = 0.0f;
+      for (int j = 0; j < top_k; ++j) {
+        const int32_t r = idx[j];
+        if (r < 0) continue;
+        const uint4 v = ld_nc_16(rows + (size_t)r * ld_bytes + (size_t)c * 16);
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc[2 * q] += __uint_as_float(u[q] << 16);
+          acc[2 * q + 1] += __uint_as_float(u[q] & 0xffff0000u);
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      st_16(out + (size_t)t * row_bytes + (size_t)c * 16, o);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Gated-activation backward: one block per received row.
+// ---------------------------------------------------------------------------------
+constexpr int kSwigluBwdThreads = 256;
+
+__device__ __forceinline__ void act_pair(float g, float u, int act, float beta, float lbeta,
+                                         float clamp, float& act_g, float& dact_g, float& v,
+                                         float& dv) {
+  if (act == MM_ACT_SWIGLU) {
+    const float s = 1.0f / (1.0f + __expf(-g));
+    act_g = g * s;
+    dact_g = act_g * (1.0f - s) + s;
+    v = u;
+    dv = 1.0f;
+  } else if (act == MM_ACT_CLAMP_SWIGLU) {
+    const float gc = fminf(g, clamp);
+    const float uc = fminf(fmaxf(u, -clamp), clamp);
+    const float s = 1.0f / (1.0f + __expf(-gc));
+    act_g = gc * s;
+    dact_g = (s + gc * s * (1.0f - s)) * (g <= clamp ? 1.0f : 0.0f);
+    v = uc;
+    dv = fabsf(u) <= clamp ? 1.0f : 0.0f;
+  } else {
+    const float t = tanhf(g / beta);
+    const float s = 1.0f / (1.0f + __expf(-g));
+    act_g = beta * t * s;
+    dact_g = (1.0f - t * t) * s + beta * t * s * (1.0f - s);
+    if (lbeta > 0.0f) {
+      const float tu = tanhf(u / lbeta);
+      v = lbeta * tu;
+      dv = 1.0f - tu * tu;
+    } else {
+      v = u;
+      dv = 1.0f;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kSwigluBwdThreads)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ grad_act, int64_t ld_ga,
+                  const __nv_bfloat16* __restrict__ fc1_out, int64_t ld_fc1,
+                  const __nv_bfloat16* __restrict__ row_scale, int ffn,
+                  const int32_t* __restrict__ num_rows, int max_rows,
+                  __nv_bfloat16* __restrict__ grad_fc1, int64_t ld_gf,
+                  __nv_bfloat16* __restrict__ grad_scale, int act, float beta, float lbeta,
+                  float clamp, const int32_t* __restrict__ row_dst_rank,
+                  const int32_t* __restrict__ row_dst_pos, void* const* __restrict__ peer_gate) {
+  __shared__ float red[kSwigluBwdThreads / 32];
+  const int n = min(*num_rows, max_rows);
+  const int pairs = ffn >> 1;
+  for (int row = blockIdx.x; row < n; row += gridDim.x) {
+    const __nv_bfloat162* dc = reinterpret_cast<const __nv_bfloat162*>(grad_act + (size_t)row * ld_ga);
+    const __nv_bfloat162* ga = reinterpret_cast<const __nv_bfloat162*>(fc1_out + (size_t)row * ld_fc1);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(fc1_out + (size_t)row * ld_fc1 + ffn);
+    __nv_bfloat162* dg = reinterpret_cast<__nv_bfloat162*>(grad_fc1 + (size_t)row * ld_gf);
+    __nv_bfloat162* du = reinterpret_cast<__nv_bfloat162*>(grad_fc1 + (size_t)row * ld_gf + ffn);
+    const float sc = __bfloat162float(row_scale[row]);
+    float part = 0.0f;
+    for (int i = threadIdx.x; i < pairs; i += kSwigluBwdThreads) {
+      const float2 c = __bfloat1622float2(dc[i]);
+      const float2 g = __bfloat1622float2(ga[i]);
+      const float2 u = __bfloat1622float2(up[i]);
+      float a0, d0, v0, dv0, a1, d1, v1, dv1;
+      act_pair(g.x, u.x, act, beta, lbeta, clamp, a0, d0, v0, dv0);
+      act_pair(g.y, u.y, act, beta, lbeta, clamp, a1, d1, v1, dv1);
+      dg[i] = __floats2bfloat162_rn(c.x * d0 * v0 * sc, c.y * d1 * v1 * sc);
+      du[i] = __floats2bfloat162_rn(c.x * a0 * dv0 * sc, c.y * a1 * dv1 * sc);
+      part += a0 * v0 * c.x + a1 * v1 * c.y;
+    }
+#pragma unroll
+    for (int k = 16; k > 0; k >>= 1) part += __shfl_xor_sync(0xffffffffu, part, k);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.0f;
+      for (int k = 0; k < kSwigluBwdThreads / 32; ++k) s += red[k];
+      const __nv_bfloat16 v = __float2bfloat16_rn(s);
+      grad_scale[row] = v;
+      if (peer_gate != nullptr) {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(peer_gate[row_dst_rank[row]]);
+        dst[row_dst_pos[row]] = v;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Cross-rank barrier through flag words in symmetric memory.
+// ---------------------------------------------------------------------------------
+__global__ void rank_barrier_kernel(int32_t* const* __restrict__ peer_flags, int rank, int world,
+                                    int epoch, StatusRecord* status) {
+  const int s = threadIdx.x;
+  if (s >= world) return;
+  // Make every earlier store of this GPU (issued by preceding kernels of the stream)
+  // visible system-wide before the flag that announces them.
+  __threadfence_system();
+  int32_t* remote = peer_flags[s] + rank;
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const int32_t* mine = peer_flags[rank] + s;
+  const uint64_t t0 = globaltimer_ns();
+  int32_t seen;
+  uint32_t spins = 0;
+  while (true) {
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    if (seen >= epoch) break;
+    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
+      report_status(status, kWaitTimeout, kSiteRankBarrier, s, epoch, seen);
+      break;
+    }
+    __nanosleep(64);
+  }
+}
+
+}  // namespace mm
+
+using namespace mm;
+
+extern "C" {
+
+int mm_dispatch_rows(const void* src, int hidden, const float* weights, const int32_t* send_token,
+                     const int32_t* send_route, const int32_t* send_bucket,
+                     const int32_t* send_bucket_starts, const int32_t* send_bucket_dst_starts,
+                     const int32_t* local_stats, int max_routes, int epr, int capacity_rows,
+                     void* const* peer_rows, float* const* peer_weights, cudaStream_t stream) {
+  if (!src || !send_token || !send_route || !send_bucket || !send_bucket_starts ||
+      !send_bucket_dst_starts || !local_stats || !peer_rows || (weights && !peer_weights)) {
+    set_error("mm_dispatch_rows: null argument");
+    return MM_ERR_ARG;
+  }
+  if (hidden <= 0 || (hidden % 8) || epr <= 0) {
+    set_error("mm_dispatch_rows: hidden must be a positive multiple of 8 (got %d)", hidden);
+    return MM_ERR_ARG;
+  }
+  if (max_routes <= 0) return MM_OK;
+  int sms = 148;
+  mm_num_sms(&sms);
+  const int warps = kDispatchThreads / 32;
+  int blocks = (max_routes + warps - 1) / warps;
+  if (blocks > sms * 8) blocks = sms * 8;
+  dispatch_rows_kernel<<<blocks, kDispatchThreads, 0, stream>>>(
+      reinterpret_cast<const uint8_t*>(src), hidden * 2, weights, send_token, send_route,
+      send_bucket, send_bucket_starts, send_bucket_dst_starts, local_stats, epr, capacity_rows,
+      peer_rows, peer_weights);
+  return check_launch("dispatch_rows_kernel");
+}
+
+int mm_topk_reduce(const void* rows, int64_t ld_rows, const int32_t* route_to_send, int tokens,
+                   int top_k, int hidden, void* out, const void* gate_in, void* gate_out,
+                   cudaStream_t stream) {
+  if (!rows || !route_to_send || !out || (gate_in && !gate_out)) {
+    set_error("mm_topk_reduce: null argument");
+    return MM_ERR_ARG;
+  }
+  if (top_k <= 0 || top_k > kMaxTopK || hidden <= 0 || (hidden % 8) || (ld_rows % 8)) {
+    set_error("mm_topk_reduce: top_k must be in [1, %d] and hidden a multiple of 8", kMaxTopK);
+    return MM_ERR_ARG;
+  }
+  if (tokens <= 0) return MM_OK;
+  int sms = 148;
+  mm_num_sms(&sms);
+  int blocks = tokens < sms * 8 ? tokens : sms * 8;
+  topk_reduce_kernel<<<blocks, kReduceThreads, 0, stream>>>(
+      reinterpret_cast<const uint8_t*>(rows), ld_rows * 2, route_to_send, tokens, top_k, hidden * 2,
+      reinterpret_cast<uint8_t*>(out), reinterpret_cast<const __nv_bfloat16*>(gate_in),
+      reinterpret_cast<__nv_bfloat16*>(gate_out));
+  return check_launch("topk_reduce_kernel");
+}
+
+int mm_swiglu_bwd(const void* grad_act, int64_t ld_ga, const void* fc1_out, int64_t ld_fc1,
+                  const void* row_scale_bf16, int ffn, const int32_t* num_rows, int max_rows,
+                  void* grad_fc1, int64_t ld_gf, void* grad_scale, int activation, float beta,
+                  float linear_beta, float clamp_limit, const int32_t* row_dst_rank,
+                  const int32_t* row_dst_pos, void* const* peer_gate, cudaStream_t stream) {
+  if (!grad_act || !fc1_out || !row_scale_bf16 || !num_rows || !grad_fc1 || !grad_scale ||
+      (peer_gate && (!row_dst_rank || !row_dst_pos))) {
+    set_error("mm_swiglu_bwd: null argument");
+    return MM_ERR_ARG;
+  }
+  if (ffn <= 0 || (ffn % 2) || (ld_ga % 2) || (ld_fc1 % 2) || (ld_gf % 2)) {
+    set_error("mm_swiglu_bwd: ffn and leading dimensions must be even");
+    return MM_ERR_ARG;
+  }
+  if (max_rows <= 0) return MM_OK;
+  int sms = 148;
+  mm_num_sms(&sms);
+  int blocks = max_rows < sms * 8 ? max_rows : sms * 8;
+  swiglu_bwd_kernel<<<blocks, kSwigluBwdThreads, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(grad_act), ld_ga,
+      reinterpret_cast<const __nv_bfloat16*>(fc1_out), ld_fc1,
+      reinterpret_cast<const __nv_bfloat16*>(row_scale_bf16), ffn, num_rows, max_rows,
+      reinterpret_cast<__nv_bfloat16*>(grad_fc1), ld_gf, reinterpret_cast<__nv_bfloat16*>(grad_scale),
+      activation, beta, linear_beta, clamp_limit, row_dst_rank, row_dst_pos, peer_gate);
+  return check_launch("swiglu_bwd_kernel");
+}
+
+int mm_rank_barrier(int32_t* const* peer_flags, int rank, int world, int epoch, void* status,
+                    cudaStream_t stream) {
+  if (!peer_flags || world <= 0 || world > 1024 || rank < 0 || rank >= world) {
+    set_error("mm_rank_barrier: bad arguments");
+    return MM_ERR_ARG;
+  }
+  rank_barrier_kernel<<<1, ((world + 31) / 32) * 32, 0, stream>>>(
+      peer_flags, rank, world, epoch, reinterpret_cast<StatusRecord*>(status));
+  return check_launch("rank_barrier_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,462 @@
+// Routing metadata kernels: route filter, stable expert-major counting sort, local count
+// row, and the offset tables derived from the replicated count cube.
+//
+// The sort is a three-pass counting sort whose result does not depend on scheduling:
+//   1. every block histograms a fixed, contiguous chunk of routes;
+//   2. one block turns the per-block histograms into exclusive offsets per expert and
+//      scans the expert totals into bucket starts;
+//   3. every block revisits its chunk in order and ranks each route among the equal
+//      keys that precede it (warp match + per-warp counts), so ties keep ascending
+//      route order exactly like a stable sort.
+#include "common.cuh"
+#include "internal.h"
+
+namespace mm {
+
+constexpr int kRouteChunk = 2048;
+constexpr int kRouteThreads = 256;
+constexpr int kRouteWarps = kRouteThreads / 32;
+constexpr int kMaxBins = 4096;
+
+__global__ void __launch_bounds__(kRouteThreads)
+route_hist_kernel(const int32_t* __restrict__ selected, int n, int num_experts, int bins,
+                  int32_t* __restrict__ block_hist) {
+  extern __shared__ int32_t hist[];
+  for (int b = threadIdx.x; b < bins; b += kRouteThreads) hist[b] = 0;
+  __syncthreads();
+  const int base = blockIdx.x * kRouteChunk;
+  for (int i = threadIdx.x; i < kRouteChunk; i += kRouteThreads) {
+    const int r = base + i;
+    if (r < n) {
+      const int e = selected[r];
+      if (e >= 0 && e < num_experts) atomicAdd(&hist[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < bins; b += kRouteThreads)
+    block_hist[(size_t)blockIdx.x * bins + b] = hist[b];
+}
+
+// Block-wide exclusive scan of one value per thread (1024 threads).
+__device__ __forceinline__ int block_exclusive_scan_1024(int v, int* warp_sums, int* total) {
+  const int lane = threadIdx.x & 31;
+  const int w = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += t;
+  }
+  if (lane == 31) warp_sums[w] = inc;
+  __syncthreads();
+  if (w == 0) {
+    int s = warp_sums[lane];
+    int sinc = s;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, sinc, d);
+      if (lane >= d) sinc += t;
+    }
+    warp_sums[lane] = sinc - s;
+    if (lane == 31) *total = sinc;
+  }
+  __syncthreads();
+  return warp_sums[w] + inc - v;
+}
+
+__global__ void __launch_bounds__(1024)
+route_scan_kernel(int32_t* __restrict__ block_hist, int nblk, int bins,
+                  int32_t* __restrict__ bucket_start, int32_t* __restrict__ count_row,
+                  int32_t* __restrict__ local_stats) {
+  extern __shared__ int32_t tot[];  // [bins]
+  __shared__ int warp_sums[32];
+  __shared__ int total;
+  for (int b = threadIdx.x; b < bins; b += 1024) {
+    int run = 0;
+    for (int k = 0; k < nblk; ++k) {
+      const size_t idx = (size_t)k * bins + b;
+      const int t = block_hist[idx];
+      block_hist[idx] = run;
+      run += t;
+    }
+    tot[b] = run;
+    count_row[b] = run;
+  }
+  __syncthreads();
+  const int per = (bins + 1023) / 1024;
+  const int first = threadIdx.x * per;
+  int local = 0;
+  for (int j = 0; j < per; ++j)
+    if (first + j < bins) local += tot[first + j];
+  int off = block_exclusive_scan_1024(local, warp_sums, &total);
+  for (int j = 0; j < per; ++j) {
+    if (first + j < bins) {
+      bucket_start[first + j] = off;
+      off += tot[first + j];
+    }
+  }
+  if (threadIdx.x == 0) {
+    local_stats[0] = total;
+    local_stats[1] = 0;
+  }
+}
+
+__global__ void __launch_bounds__(kRouteThreads)
+route_scatter_kernel(const int32_t* __restrict__ selected, int n, int top_k, int num_experts,
+                     int bins, const int32_t* __restrict__ block_hist,
+                     const int32_t* __restrict__ bucket_start, int32_t* __restrict__ send_route,
+                     int32_t* __restrict__ send_token, int32_t* __restrict__ send_bucket,
+                     int32_t* __restrict__ route_to_send) {
+  extern __shared__ int32_t sm[];
+  int32_t* run = sm;              // [bins] next free position of each expert for this block
+  int32_t* warp_cnt = sm + bins;  // [kRouteWarps][bins]
+  for (int b = threadIdx.x; b < bins; b += kRouteThreads)
+    run[b] = bucket_start[b] + block_hist[(size_t)blockIdx.x * bins + b];
+  for (int b = threadIdx.x; b < kRouteWarps * bins; b += kRouteThreads) warp_cnt[b] = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int w = threadIdx.x >> 5;
+  const int base = blockIdx.x * kRouteChunk;
+  for (int tile = 0; tile < kRouteChunk; tile += kRouteThreads) {
+    const int r = base + tile + threadIdx.x;
+    int e = -1;
+    if (r < n) {
+      e = selected[r];
+      if (e < 0 || e >= num_experts) e = -1;
+    }
+    const bool valid = e >= 0;
+    const unsigned mask = __match_any_sync(0xffffffffu, e);
+    const int rank_w = __popc(mask & ((1u << lane) - 1u));
+    const int cnt = __popc(mask);
+    const bool leader = rank_w == 0;
+    if (valid && leader) warp_cnt[w * bins + e] = cnt;
+    __syncthreads();
+    if (valid) {
+      int pos = run[e] + rank_w;
+      for (int w2 = 0; w2 < w; ++w2) pos += warp_cnt[w2 * bins + e];
+      send_route[pos] = r;
+      send_token[pos] = r / top_k;
+      send_bucket[pos] = e;
+      route_to_send[r] = pos;
+    } else if (r < n) {
+      route_to_send[r] = -1;
+    }
+    __syncthreads();
+    if (valid && leader) {
+      atomicAdd(&run[e], cnt);
+      warp_cnt[w * bins + e] = 0;
+    }
+    __syncthreads();
+  }
+}
+
+// One block.  Shared memory: tot[nb] | pre[nb] | loc[nb] | tiles[epr + 1].
+__global__ void __launch_bounds__(1024)
+route_finalize_kernel(const int32_t* __restrict__ cube, int rank, int world, int epr, int bins,
+                      int capacity_rows, int32_t* __restrict__ send_bucket_starts,
+                      int32_t* __restrict__ send_bucket_dst_starts,
+                      int32_t* __restrict__ recv_counts_re, int32_t* __restrict__ recv_per_expert,
+                      int32_t* __restrict__ recv_expert_offs, int32_t* __restrict__ recv_seg_starts,
+                      int32_t* __restrict__ pull_dst_start, int32_t* __restrict__ stats,
+                      int32_t* __restrict__ mtile_group, int32_t* __restrict__ mtile_row0,
+                      int32_t* __restrict__ num_mtiles, StatusRecord* status) {
+  extern __shared__ int32_t sm[];
+  const int nb = world * epr;
+  int32_t* tot = sm;
+  int32_t* pre = sm + nb;
+  int32_t* loc = sm + 2 * nb;
+  int32_t* tiles = sm + 3 * nb;  // [epr + 1] exclusive tile offsets of the local experts
+  __shared__ int warp_sums[32];
+  __shared__ int scan_total;
+  const int tid = threadIdx.x;
+
+  for (int b = tid; b < nb; b += 1024) {
+    int t = 0, p = 0;
+    for (int s = 0; s < world; ++s) {
+      const int c = cube[(size_t)s * bins + b];
+      t += c;
+      if (s < rank) p += c;
+    }
+    tot[b] = t;
+    pre[b] = p;
+    loc[b] = cube[(size_t)rank * bins + b];
+  }
+  __syncthreads();
+
+  // send_bucket_starts: exclusive scan of the local row over all buckets.
+  {
+    const int per = (nb + 1023) / 1024;
+    const int first = tid * per;
+    int local = 0;
+    for (int j = 0; j < per; ++j)
+      if (first + j < nb) local += loc[first + j];
+    int off = block_exclusive_scan_1024(local, warp_sums, &scan_total);
+    for (int j = 0; j < per; ++j) {
+      if (first + j < nb) {
+        send_bucket_starts[first + j] = off;
+        off += loc[first + j];
+      }
+    }
+  }
+  __syncthreads();
+
+  // Per destination: running base over its experts (one warp per destination, chunks of 32).
+  {
+    const int lane = tid & 31;
+    const int w = tid >> 5;
+    for (int d = w; d < world; d += 32) {
+      int base = 0;
+      for (int e0 = 0; e0 < epr; e0 += 32) {
+        const int le = e0 + lane;
+        const int b = d * epr + le;
+        const int v = (le < epr) ? tot[b] : 0;
+        int inc = v;
+#pragma unroll
+        for (int k = 1; k < 32; k <<= 1) {
+          const int t = __shfl_up_sync(0xffffffffu, inc, k);
+          if (lane >= k) inc += t;
+        }
+        const int excl = base + inc - v;
+        if (le < epr) {
+          send_bucket_dst_starts[b] = excl + pre[b];
+          if (d == rank) {
+            recv_per_expert[le] = v;
+            recv_expert_offs[le] = excl;
+          }
+        }
+        base += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) {
+        stats[2 + d] = base;
+        if (d == rank) {
+          recv_expert_offs[epr] = base;
+          stats[0] = base;
+        }
+      }
+    }
+  }
+
+  // Receive-side tables of this rank.
+  for (int i = tid; i < world * epr; i += 1024) {
+    const int s = i / epr;
+    const int le = i - s * epr;
+    recv_counts_re[i] = cube[(size_t)s * bins + rank * epr + le];
+  }
+  for (int le = tid; le < epr; le += 1024) {
+    int run = 0;
+    for (int s = 0; s < world; ++s) {
+      recv_seg_starts[le * (world + 1) + s] = run;
+      run += cube[(size_t)s * bins + rank * epr + le];
+    }
+    recv_seg_starts[le * (world + 1) + world] = run;
+  }
+  // pull_dst_start[le * world + s]: position of bucket (rank, le) in source s's send order.
+  {
+    const int lane = tid & 31;
+    const int w = tid >> 5;
+    const int first_bucket = rank * epr;
+    for (int s = w; s < world; s += 32) {
+      int base = 0;
+      for (int b0 = 0; b0 < first_bucket; b0 += 32) {
+        const int b = b0 + lane;
+        int v = (b < first_bucket) ? cube[(size_t)s * bins + b] : 0;
+#pragma unroll
+        for (int k = 16; k > 0; k >>= 1) v += __shfl_xor_sync(0xffffffffu, v, k);
+        base += v;
+      }
+      for (int e0 = 0; e0 < epr; e0 += 32) {
+        const int le = e0 + lane;
+        const int v = (le < epr) ? cube[(size_t)s * bins + first_bucket + le] : 0;
+        int inc = v;
+#pragma unroll
+        for (int k = 1; k < 32; k <<= 1) {
+          const int t = __shfl_up_sync(0xffffffffu, inc, k);
+          if (lane >= k) inc += t;
+        }
+        if (le < epr) pull_dst_start[le * world + s] = base + inc - v;
+        base += __shfl_sync(0xffffffffu, inc, 31);
+      }
+    }
+  }
+  __syncthreads();
+
+  // 128-row tile table of the local experts, receive total and capacity check.
+  {
+    const int per = (epr + 1023) / 1024;
+    const int first = tid * per;
+    int local_tiles = 0, local_rows = 0;
+    for (int j = 0; j < per; ++j) {
+      if (first + j < epr) {
+        const int c = tot[rank * epr + first + j];
+        local_tiles += (c + 127) >> 7;
+        local_rows += c;
+      }
+    }
+    int toff = block_exclusive_scan_1024(local_tiles, warp_sums, &scan_total);
+    const int total_tiles = scan_total;
+    int roff = block_exclusive_scan_1024(local_rows, warp_sums, &scan_total);
+    for (int j = 0; j < per; ++j) {
+      if (first + j < epr) {
+        const int c = tot[rank * epr + first + j];
+        const int nt = (c + 127) >> 7;
+        for (int i = 0; i < nt; ++i) {
+          mtile_group[toff + i] = first + j;
+          mtile_row0[toff + i] = roff + i * 128;
+        }
+        toff += nt;
+        roff += c;
+      }
+    }
+    if (tid == 0) {
+      int max_required = 0;
+      for (int d = 0; d < world; ++d) max_required = max(max_required, stats[2 + d]);
+      stats[1] = max_required;
+      if (max_required > capacity_rows) {
+        report_status(status, kCapacityOverflow, 0, 0, capacity_rows, max_required);
+        *num_mtiles = 0;
+      } else {
+        *num_mtiles = total_tiles;
+      }
+    }
+  }
+}
+
+// Per received row: the rank that sent it and the row's position in that rank's send order.
+// One warp per (local expert, source) segment.
+__global__ void __launch_bounds__(256)
+route_row_tables_kernel(const int32_t* __restrict__ recv_expert_offs,
+                        const int32_t* __restrict__ recv_seg_starts,
+                        const int32_t* __restrict__ pull_dst_start, int world, int epr,
+                        int capacity_rows, int32_t* __restrict__ row_src_rank,
+                        int32_t* __restrict__ row_src_pos) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int nseg = world * epr;
+  for (int seg = blockIdx.x * warps_per_block + (threadIdx.x >> 5); seg < nseg;
+       seg += gridDim.x * warps_per_block) {
+    const int le = seg / world;
+    const int s = seg - le * world;
+    const int seg0 = recv_seg_starts[le * (world + 1) + s];
+    const int cnt = recv_seg_starts[le * (world + 1) + s + 1] - seg0;
+    const int row0 = recv_expert_offs[le] + seg0;
+    const int pos0 = pull_dst_start[le * world + s];
+    for (int i = lane; i < cnt; i += 32) {
+      const int row = row0 + i;
+      if (row < capacity_rows) {
+        row_src_rank[row] = s;
+        row_src_pos[row] = pos0 + i;
+      }
+    }
+  }
+}
+
+}  // namespace mm
+
+using namespace mm;
+
+extern "C" {
+
+size_t mm_route_scratch_bytes(int num_routes, int bins) {
+  if (num_routes < 0 || bins <= 0) return 0;
+  const size_t nblk = ((size_t)num_routes + kRouteChunk - 1) / kRouteChunk;
+  return (nblk + 1) * (size_t)bins * sizeof(int32_t);
+}
+
+int mm_route_local(const int32_t* selected, int num_routes, int top_k, int num_experts, int bins,
+                   int32_t* send_route, int32_t* send_token, int32_t* send_bucket,
+                   int32_t* route_to_send, int32_t* count_row, int32_t* local_stats, void* scratch,
+                   size_t scratch_bytes, cudaStream_t stream) {
+  if (!selected || !send_route || !send_token || !send_bucket || !route_to_send || !count_row ||
+      !local_stats || !scratch) {
+    set_error("mm_route_local: null argument");
+    return MM_ERR_ARG;
+  }
+  if (num_routes < 0 || top_k <= 0 || num_experts <= 0 || bins < num_experts || bins > kMaxBins) {
+    set_error("mm_route_local: bad sizes (routes=%d top_k=%d experts=%d bins=%d, bins <= %d)",
+              num_routes, top_k, num_experts, bins, kMaxBins);
+    return MM_ERR_ARG;
+  }
+  if (scratch_bytes < mm_route_scratch_bytes(num_routes, bins)) {
+    set_error("mm_route_local: scratch too small (%zu < %zu)", scratch_bytes,
+              mm_route_scratch_bytes(num_routes, bins));
+    return MM_ERR_ARG;
+  }
+  const int nblk = (num_routes + kRouteChunk - 1) / kRouteChunk;
+  int32_t* block_hist = reinterpret_cast<int32_t*>(scratch);
+  int32_t* bucket_start = block_hist + (size_t)nblk * bins;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(route_scatter_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (kRouteWarps + 1) * kMaxBins * (int)sizeof(int32_t));
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(route_scatter_kernel): %s", cudaGetErrorString(e));
+      return MM_ERR_CUDA;
+    }
+    attr_done = true;
+  }
+  if (nblk > 0) {
+    route_hist_kernel<<<nblk, kRouteThreads, bins * sizeof(int32_t), stream>>>(
+        selected, num_routes, num_experts, bins, block_hist);
+    if (int rc = check_launch("route_hist_kernel")) return rc;
+  }
+  route_scan_kernel<<<1, 1024, bins * sizeof(int32_t), stream>>>(block_hist, nblk, bins,
+                                                                 bucket_start, count_row,
+                                                                 local_stats);
+  if (int rc = check_launch("route_scan_kernel")) return rc;
+  if (nblk > 0) {
+    route_scatter_kernel<<<nblk, kRouteThreads, (kRouteWarps + 1) * bins * sizeof(int32_t),
+                           stream>>>(selected, num_routes, top_k, num_experts, bins, block_hist,
+                                     bucket_start, send_route, send_token, send_bucket,
+                                     route_to_send);
+    if (int rc = check_launch("route_scatter_kernel")) return rc;
+  }
+  return MM_OK;
+}
+
+int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, int bins,
+                      int capacity_rows, int32_t* send_bucket_starts,
+                      int32_t* send_bucket_dst_starts, int32_t* recv_counts_re,
+                      int32_t* recv_per_expert, int32_t* recv_expert_offs,
+                      int32_t* recv_seg_starts, int32_t* pull_dst_start, int32_t* stats,
+                      int32_t* mtile_group, int32_t* mtile_row0, int32_t* num_mtiles,
+                      int32_t* row_src_rank, int32_t* row_src_pos, void* status,
+                      cudaStream_t stream) {
+  if (!count_cube || !send_bucket_starts || !send_bucket_dst_starts || !recv_counts_re ||
+      !recv_per_expert || !recv_expert_offs || !recv_seg_starts || !pull_dst_start || !stats ||
+      !mtile_group || !mtile_row0 || !num_mtiles || !row_src_rank || !row_src_pos) {
+    set_error("mm_route_finalize: null argument");
+    return MM_ERR_ARG;
+  }
+  const int nb = world * epr;
+  if (world <= 0 || epr <= 0 || rank < 0 || rank >= world || bins < nb || nb > kMaxBins) {
+    set_error("mm_route_finalize: bad sizes (rank=%d world=%d epr=%d bins=%d)", rank, world, epr,
+              bins);
+    return MM_ERR_ARG;
+  }
+  const size_t smem = (size_t)(3 * nb + epr + 1) * sizeof(int32_t);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(route_finalize_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (4 * kMaxBins + 1) * (int)sizeof(int32_t));
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(route_finalize_kernel): %s", cudaGetErrorString(e));
+      return MM_ERR_CUDA;
+    }
+    attr_done = true;
+  }
+  route_finalize_kernel<<<1, 1024, smem, stream>>>(
+      count_cube, rank, world, epr, bins, capacity_rows, send_bucket_starts, send_bucket_dst_starts,
+      recv_counts_re, recv_per_expert, recv_expert_offs, recv_seg_starts, pull_dst_start, stats,
+      mtile_group, mtile_row0, num_mtiles, reinterpret_cast<StatusRecord*>(status));
+  if (int rc = check_launch("route_finalize_kernel")) return rc;
+  const int nseg = world * epr;
+  const int blocks = (nseg + 7) / 8;
+  route_row_tables_kernel<<<blocks, 256, 0, stream>>>(recv_expert_offs, recv_seg_starts,
+                                                      pull_dst_start, world, epr, capacity_rows,
+                                                      row_src_rank, row_src_pos);
+  return check_launch("route_row_tables_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,127 @@
+"""Thin launch helpers shared by the forward and backward operators.
+
+Each helper turns torch tensors into the plain pointers / sizes of one C-ABI call.  Nothing
+here computes on the host: a missing shared library raises from ``_native.lib()``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _native as N
+from ..runtime.workspace import MoEForwardContext
+
+
+def weight_operand(weight: torch.Tensor, k_dim: int, n_dim: int):
+    """Describe a per-expert weight ``[E, *, *]`` as the B operand of ``A[rows, K] @ B[K, N]``.
+
+    ``k_dim`` / ``n_dim`` name which of dimensions 1 and 2 is the reduction / output axis.
+    Returns ``(b_k_major, ld, group_stride, n_total)``; one of the two axes must be
+    contiguous, which covers both the natural layout and a transposed stride view.
+    """
+    if weight.dim() != 3:
+        raise ValueError("expert weights must be 3-D")
+    sk, sn = weight.stride(k_dim), weight.stride(n_dim)
+    if sk == 1:
+        b_k_major, ld = 1, sn
+    elif sn == 1:
+        b_k_major, ld = 0, sk
+    else:
+        raise ValueError("expert weight must be contiguous along its reduction or output axis")
+    return b_k_major, ld, weight.stride(0), weight.shape[n_dim]
+
+
+def make_desc(ctx: MoEForwardContext, a: torch.Tensor, a_rows_cap: int, lda: int,
+              weight: torch.Tensor, k_dim: int, n_dim: int, n_out: int, k_extent: int,
+              *, group_offs=None, mtile_group=None, mtile_row0=None, num_mtiles=None,
+              grid_limit: int = 0) -> N.GemmDesc:
+    b_k_major, ld, gs, n_total = weight_operand(weight, k_dim, n_dim)
+    d = N.GemmDesc()
+    d.a = a.data_ptr()
+    d.lda = lda
+    d.a_rows_cap = a_rows_cap
+    d.b = weight.data_ptr()
+    d.b_k_major = b_k_major
+    d.b_cols_total = n_total
+    d.b_ld = ld
+    d.b_group_stride = gs
+    d.num_groups = weight.shape[0]
+    d.N = n_out
+    d.K = k_extent
+    d.grid_limit = grid_limit
+    d.group_offs = (group_offs if group_offs is not None
+                    else ctx.metadata_recv_expert_offs).data_ptr()
+    d.mtile_group = (mtile_group if mtile_group is not None else ctx.mtile_group).data_ptr()
+    d.mtile_row0 = (mtile_row0 if mtile_row0 is not None else ctx.mtile_row0).data_ptr()
+    d.num_mtiles = (num_mtiles if num_mtiles is not None else ctx.num_mtiles).data_ptr()
+    d.status = ctx.status.data_ptr()
+    return d
+
+
+def dispatch_rows(ctx: MoEForwardContext, src: torch.Tensor, weights, num_routes: int, plan=None):
+    """Push the send rows of ``src`` (and their routing weights) to the owning ranks."""
+    p = plan if plan is not None else ctx
+    N.check(N.lib().mm_dispatch_rows(
+        src.data_ptr(), ctx.hidden_size, N.ptr(weights),
+        p.send_token_indices.data_ptr(), p.send_route_indices.data_ptr(),
+        p.send_bucket.data_ptr(), p.metadata_send_bucket_starts.data_ptr(),
+        p.metadata_send_bucket_dst_starts.data_ptr(), p.metadata_local_stats.data_ptr(),
+        num_routes, ctx.experts_per_rank, ctx.max_received_routes,
+        ctx.symm.peer_table("peer_mem").data_ptr(),
+        ctx.symm.peer_table("routing_weight_mem").data_ptr() if weights is not None else None,
+        N.stream_ptr()), "mm_dispatch_rows")
+
+
+def fc1_swiglu(ctx, desc, act_out, raw_out, row_weight, activation, beta, linear_beta, clamp):
+    N.check(N.lib().mm_fc1_swiglu(
+        C.byref(desc), act_out.data_ptr(), act_out.stride(0),
+        N.ptr(raw_out), raw_out.stride(0) if raw_out is not None else 0,
+        row_weight.data_ptr(), N.ACT_IDS[activation], float(beta),
+        float(linear_beta) if linear_beta is not None else 0.0, float(clamp),
+        N.stream_ptr()), "mm_fc1_swiglu")
+
+
+def grouped_gemm(desc, out):
+    N.check(N.lib().mm_grouped_gemm(C.byref(desc), out.data_ptr(), out.stride(0),
+                                    N.stream_ptr()), "mm_grouped_gemm")
+
+
+def grouped_gemm_scatter(ctx, desc, region: str, ld_dst: int, plan=None):
+    p = plan if plan is not None else ctx
+    N.check(N.lib().mm_grouped_gemm_scatter(
+        C.byref(desc), p.row_src_rank.data_ptr(), p.row_src_pos.data_ptr(),
+        ctx.symm.peer_table(region).data_ptr(), ld_dst, N.stream_ptr()),
+        "mm_grouped_gemm_scatter")
+
+
+def grouped_wgrad(ctx, grad_out, orig_in, rows_cap, group_offs, num_groups, out):
+    """out[g] [Mw, Nw] = grad_out[rows of g]^T @ orig_in[rows of g]."""
+    N.check(N.lib().mm_grouped_wgrad(
+        grad_out.data_ptr(), grad_out.stride(0), grad_out.shape[1],
+        orig_in.data_ptr(), orig_in.stride(0), orig_in.shape[1], rows_cap,
+        group_offs.data_ptr(), num_groups, out.data_ptr(), out.stride(1), out.stride(0),
+        ctx.status.data_ptr(), 0, N.stream_ptr()), "mm_grouped_wgrad")
+
+
+def topk_reduce(rows, route_to_send, tokens, top_k, hidden, out, gate_in=None, gate_out=None):
+    N.check(N.lib().mm_topk_reduce(
+        rows.data_ptr(), rows.stride(0), route_to_send.data_ptr(), tokens, top_k, hidden,
+        out.data_ptr(), N.ptr(gate_in), N.ptr(gate_out), N.stream_ptr()), "mm_topk_reduce")
+
+
+def swiglu_bwd(ctx, grad_act, fc1_out, row_scale, ffn, num_rows_dev, max_rows, grad_fc1,
+               grad_scale, activation, beta, linear_beta, clamp, plan=None, push_gate=True):
+    p = plan if plan is not None else ctx
+    N.check(N.lib().mm_swiglu_bwd(
+        grad_act.data_ptr(), grad_act.stride(0), fc1_out.data_ptr(), fc1_out.stride(0),
+        row_scale.data_ptr(), ffn, num_rows_dev.data_ptr(), max_rows,
+        grad_fc1.data_ptr(), grad_fc1.stride(0), grad_scale.data_ptr(),
+        N.ACT_IDS[activation], float(beta if beta is not None else 1.0),
+        float(linear_beta) if linear_beta is not None else 0.0,
+        float(clamp if clamp is not None else 7.0),
+        p.row_src_rank.data_ptr() if push_gate else None,
+        p.row_src_pos.data_ptr() if push_gate else None,
+        ctx.symm.peer_table("combine_gate_mem").data_ptr() if push_gate else None,
+        N.stream_ptr()), "mm_swiglu_bwd")

@@ -1,0 +1,187 @@
+"""Five-stage MoE backward on B200 (API of the reference's ``ops/backward.py``).
+
+Given ``dy [T, H]`` the stages are the reference's (src/mega_moe/ops/backward.py:27-34):
+
+1. dispatch ``dy`` rows to the expert ranks (same routes as the forward) and compute the
+   FC2 input gradient ``grad_swiglu = recv_dy @ fc2[e]``;
+2. gated-activation backward -> ``grad_fc1_output``, ``grad_gate``;
+3. FC2 weight gradient ``grad_fc2[e] = recv_dy^T @ swiglu_out_weighted``;
+4. FC1 input gradient, each row stored straight into the source rank's combine buffer
+   together with its gate gradient, then the top-k gather-sum -> ``grad_hidden``,
+   ``grad_routing_weights``;
+5. FC1 weight gradient ``grad_fc1[e] = grad_fc1_output^T @ recv_hidden_sorted``.
+
+All GEMMs run on the tcgen05 grouped-GEMM kernel; the name ``moe_backward_triton`` is kept
+only because callers import it.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..runtime.routing import launch_routing_metadata
+from ..runtime.workspace import context_of
+from . import _launch as L
+from .forward import snapshot_plan
+
+
+def _plan_for(saved, ctx):
+    """Routing tables for ``saved``: the forward's snapshot, or a rebuild from the experts.
+
+    A saved dict produced by the Torch functional forward carries no device routing tables;
+    they are a pure function of ``selected_experts``, so they are rebuilt here.
+    """
+    plan = saved.get("_plan")
+    if plan is not None:
+        return plan
+    selected = saved["selected_experts"]
+    if selected.dtype != torch.int32:
+        selected = selected.to(torch.int32)
+    selected = selected.contiguous()
+    launch_routing_metadata(ctx, selected)
+    plan = snapshot_plan(ctx)
+    saved["_plan"] = plan
+    return plan
+
+
+def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=None):
+    """Run the five backward stages; returns the reference's dict of gradients.
+
+    ``saved`` is either the dict returned by ``FusedMoEForward.forward(return_saved=True)``
+    or the 39-key dict of the Torch functional forward (``ops/_torch_forward.py:294-320`` of
+    the reference).  ``peer_mem`` must be the symmetric receive buffer of a live operator
+    context; it is reused as the receive buffer of the ``dy`` dispatch.
+    """
+    if grad_transport is not None:
+        raise ValueError("grad_transport requires a MoonEP saved_phys, which is not implemented")
+    recv_hidden_sorted = saved.get("recv_hidden_sorted")
+    if recv_hidden_sorted is None:
+        raise ValueError(
+            "saved is missing recv_hidden_sorted; the fused backward requires "
+            "the activation section (replay saved or return_saved=True)")
+    if recv_hidden_sorted.data_ptr() == peer_mem.data_ptr():
+        raise ValueError(
+            "saved['recv_hidden_sorted'] aliases peer_mem; the receive buffer "
+            "is single-in-flight and was overwritten after dispatch")
+    ctx = context_of(peer_mem)
+    dtype = saved["fc1_1"].dtype
+    dy = dy.to(dtype).contiguous()
+    tokens, hidden = dy.shape
+    top_k = int(saved["topk"])
+    fc1_output = saved["fc1_output"]
+    m = fc1_output.shape[0]
+    ffn = fc1_output.shape[1] // 2
+    epr = int(saved["experts_per_rank"])
+    fc1_combined = saved["fc1_combined"]   # [E, 2F, H]
+    fc2 = saved["fc2"]                      # [E, H, F]
+    device = dy.device
+    plan = _plan_for(saved, ctx)
+    cap = ctx.max_received_routes
+    num_routes = tokens * top_k
+    group_offs = plan.metadata_recv_expert_offs
+    tiles = dict(group_offs=group_offs, mtile_group=plan.mtile_group,
+                 mtile_row0=plan.mtile_row0, num_mtiles=plan.num_mtiles)
+
+    # ---- stage 1: dispatch dy + FC2 input gradient ------------------------------------
+    L.dispatch_rows(ctx, dy, None, num_routes, plan=plan)
+    ctx.rank_barrier()
+    recv_dy = ctx.peer_mem.view(cap, hidden)
+    grad_swiglu = torch.empty(m, ffn, dtype=dtype, device=device)
+    if m > 0:
+        desc = L.make_desc(ctx, recv_dy, cap, hidden, fc2, k_dim=1, n_dim=2, n_out=ffn,
+                           k_extent=hidden, **tiles)
+        L.grouped_gemm(desc, grad_swiglu)
+    grad_fc2_out_sorted = recv_dy[:m]
+
+    # ---- stage 3: FC2 weight gradient (reads the receive buffer, so it runs before the
+    #      barrier of stage 4 lets peers dispatch into it again) ---------------------------
+    act = saved["swiglu_out_weighted"]
+    if m > 0:
+        grad_fc2 = torch.empty(epr, hidden, ffn, dtype=dtype, device=device)
+        L.grouped_wgrad(ctx, recv_dy, act, m, group_offs, epr, grad_fc2)
+    else:
+        grad_fc2 = torch.zeros(epr, hidden, ffn, dtype=dtype, device=device)
+
+    # ---- stage 2: gated-activation backward (+ gate gradient pushed to the source) -----
+    grad_fc1_output = torch.empty(m, 2 * ffn, dtype=dtype, device=device)
+    grad_gate = torch.empty(m, dtype=dtype, device=device)
+    if m > 0:
+        L.swiglu_bwd(ctx, grad_swiglu, fc1_output, saved["recv_weights_sorted"], ffn,
+                     plan.metadata_stats, m, grad_fc1_output, grad_gate,
+                     saved.get("activation", "swiglu") or "swiglu", saved.get("situ_beta"),
+                     saved.get("situ_linear_beta"), saved.get("clamp_limit"), plan=plan)
+
+    # ---- stage 5: FC1 weight gradient -------------------------------------------------
+    if m > 0:
+        grad_fc1 = torch.empty(epr, 2 * ffn, hidden, dtype=dtype, device=device)
+        L.grouped_wgrad(ctx, grad_fc1_output, recv_hidden_sorted, m, group_offs, epr, grad_fc1)
+    else:
+        grad_fc1 = torch.zeros(epr, 2 * ffn, hidden, dtype=dtype, device=device)
+
+    # ---- stage 4: FC1 input gradient -> source ranks, then gather-sum -------------------
+    if m > 0:
+        desc = L.make_desc(ctx, grad_fc1_output, m, 2 * ffn, fc1_combined, k_dim=1, n_dim=2,
+                           n_out=hidden, k_extent=2 * ffn, **tiles)
+        L.grouped_gemm_scatter(ctx, desc, "combine_mem", hidden, plan=plan)
+    ctx.rank_barrier()
+    grad_hidden = torch.empty(tokens, hidden, dtype=dtype, device=device)
+    grad_routing_weights = torch.empty(tokens, top_k, dtype=dtype, device=device)
+    L.topk_reduce(ctx.combine_mem, plan.route_to_send, tokens, top_k, hidden, grad_hidden,
+                  gate_in=ctx.combine_gate_mem, gate_out=grad_routing_weights)
+
+    grad_fc1_1, grad_fc1_2 = torch.chunk(grad_fc1, 2, dim=1)
+    return dict(
+        grad_hidden=grad_hidden, grad_routing_weights=grad_routing_weights,
+        grad_fc1_1=grad_fc1_1, grad_fc1_2=grad_fc1_2, grad_fc2=grad_fc2,
+        grad_swiglu=grad_swiglu, grad_fc1_output=grad_fc1_output, grad_gate=grad_gate,
+        grad_fc2_out_sorted=grad_fc2_out_sorted, grad_fc1=grad_fc1,
+    )
+
+
+class MegaMoEBackwardFunction(torch.autograd.Function):
+    """EP-MoE whose forward is this package's fused operator and whose backward is the
+    five-stage CUDA backward.
+
+    Signature of the reference class (ops/backward.py:405-455):
+    ``apply(hidden_states, routing_weights, selected_experts, fc1_1, fc1_2, fc2, ep_group,
+    topk, peer_mem)`` with ``fc1_1`` / ``fc1_2`` ``[E_local, F, H]`` and ``fc2``
+    ``[E_local, H, F]``.  The reference runs a Torch functional forward here; this build has
+    no Torch compute path, so the forward goes through the operator that owns ``peer_mem``.
+    """
+
+    @staticmethod
+    def forward(ctx, hidden_states, routing_weights, selected_experts, fc1_1, fc1_2, fc2,
+                ep_group, topk, peer_mem):
+        from .forward import pack_gate_up_weights
+        context = context_of(peer_mem)
+        op_ref = context._extra.get("operator")
+        op = op_ref() if op_ref is not None else None
+        if op is None:
+            raise ValueError("peer_mem does not belong to a live FusedMoEForward operator")
+        with torch.no_grad():
+            gate_up = pack_gate_up_weights(fc1_1, fc1_2)
+            out, saved = op.forward(
+                hidden_states, selected_experts.to(torch.int32).contiguous(), gate_up, fc2,
+                routing_weights.float().contiguous(), return_saved=True)
+        ctx.saved = saved
+        ctx.peer_mem = peer_mem
+        ctx.rw_dtype = routing_weights.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        grads = moe_backward_triton(ctx.saved, dy, ctx.peer_mem)
+        return (
+            grads["grad_hidden"],
+            grads["grad_routing_weights"].to(ctx.rw_dtype),
+            None,
+            grads["grad_fc1_1"],
+            grads["grad_fc1_2"],
+            grads["grad_fc2"],
+            None,
+            None,
+            None,
+        )
+
+
+__all__ = ["MegaMoEBackwardFunction", "moe_backward_triton"]

@@ -1,0 +1,486 @@
+"""BF16 post-routing MoE forward on B200 (API of the reference's ``ops/forward.py``).
+
+The public boundary starts with selected experts and FP32 routing weights; router matmul,
+softmax and top-k selection are outside it (reference: src/mega_moe/ops/forward.py:1-6).
+
+Pipeline of one ``forward`` call, all on the caller's CUDA stream and without host
+synchronisation unless ``return_saved`` or a reduced receive capacity asks for one:
+
+    routing metadata (CUDA kernels + one NCCL all-gather of the count row)
+    -> dispatch: rows pushed by P2P stores into the owning rank's receive buffer
+    -> rank barrier (flag words in symmetric memory)
+    -> FC1 grouped GEMM (tcgen05) with bf16 rounding + weighted gated activation fused
+    -> FC2 grouped GEMM whose epilogue stores each row into the source rank's combine buffer
+    -> rank barrier -> top-k gather-sum
+"""
+
+from __future__ import annotations
+
+import types
+import weakref
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed
+
+from ..config import MoEForwardConfig
+from ..runtime.routing import (
+    MoERoutingPlan,
+    build_routing_plan,
+    check_receive_capacity,
+    launch_routing_metadata,
+)
+from ..runtime.workspace import create_moe_forward_context
+from . import _launch as L
+
+
+@dataclass
+class DispatchFC1Result:
+    """Outputs and route identity produced by the dispatch plus FC1 stage."""
+
+    routing_plan: MoERoutingPlan
+    fc1_output: torch.Tensor
+    dispatched_tokens: torch.Tensor
+    received_routing_weights: torch.Tensor
+    send_route_indices: torch.Tensor
+
+
+_PLAN_FIELDS = (
+    "send_token_indices", "send_route_indices", "send_bucket", "route_to_send",
+    "metadata_send_bucket_starts", "metadata_send_bucket_dst_starts", "metadata_local_stats",
+    "metadata_stats", "metadata_recv_expert_offs", "metadata_recv_counts_re",
+    "metadata_recv_per_expert", "mtile_group", "mtile_row0", "num_mtiles", "row_src_rank",
+    "row_src_pos",
+)
+
+
+def snapshot_plan(context) -> types.SimpleNamespace:
+    """Clone the routing tables of the last metadata launch (a few MB of int32)."""
+    return types.SimpleNamespace(**{name: getattr(context, name).clone() for name in _PLAN_FIELDS})
+
+
+class FusedMoEForward(torch.nn.Module):
+    """Fused EP all-to-all + grouped GEMM MoE operator for B200.
+
+    Same constructor, attributes and ``forward`` contract as the reference class
+    (src/mega_moe/ops/forward.py:68-243,1884-2109).  Instances are single-in-flight and
+    single-stream because their workspaces are reused; they are not thread-safe.
+    """
+
+    def __init__(
+        self,
+        ep_group: Optional[torch.distributed.ProcessGroup],
+        *,
+        max_tokens_per_rank: int,
+        hidden_size: int,
+        top_k: int,
+        num_experts: int,
+        config: Optional[MoEForwardConfig] = None,
+    ):
+        super().__init__()
+        if max_tokens_per_rank <= 0:
+            raise ValueError("max_tokens_per_rank must be positive")
+        if hidden_size <= 0:
+            raise ValueError("hidden_size must be positive")
+        if top_k <= 0:
+            raise ValueError("top_k must be positive")
+        if num_experts <= 0:
+            raise ValueError("num_experts must be positive")
+        if config is not None and not isinstance(config, MoEForwardConfig):
+            raise TypeError("config must be a MoEForwardConfig instance or None")
+
+        self.ep_group = ep_group
+        if ep_group is not None:
+            self.rank = ep_group.rank()
+            self.world_size = ep_group.size()
+        elif torch.distributed.is_available() and torch.distributed.is_initialized():
+            self.rank = torch.distributed.get_rank()
+            self.world_size = torch.distributed.get_world_size()
+        else:
+            self.rank = 0
+            self.world_size = 1
+        if num_experts % self.world_size:
+            raise ValueError("num_experts must be divisible by the EP world size")
+        if hidden_size % 8:
+            raise ValueError("hidden_size must be a multiple of 8 (16-byte rows)")
+
+        self.max_tokens_per_rank = max_tokens_per_rank
+        self.hidden_size = hidden_size
+        self.top_k = top_k
+        self.num_experts = num_experts
+        self.experts_per_rank = num_experts // self.world_size
+        self.activation_dtype = torch.bfloat16
+        self.config = config if config is not None else MoEForwardConfig()
+        self.enable_moonep = self.config.enable_moonep
+        self.enable_single_kernel_forward = self.config.enable_single_kernel_forward
+        self.replica_budget = 0
+        self.physical_experts_per_rank = self.experts_per_rank
+        self.receive_capacity_factor = self.config.resolved_receive_capacity_factor(
+            self.world_size)
+        self.num_aicore_programs = self.config.num_aicore_programs
+        self.num_aivector_programs = self.config.num_aivector_programs
+        self._save_fc1_dtype = self.config.save_fc1_dtype
+        self.activation = self.config.activation
+        self.situ_beta = self.config.situ_beta
+        self.situ_linear_beta = self.config.situ_linear_beta
+        self.clamp_limit = self.config.clamp_limit
+
+        self._tile_signal_epoch = 1
+        self._routing_owner_token = object()
+        self._routing_generation = 0
+        self.context = create_moe_forward_context(
+            max_tokens_per_rank=max_tokens_per_rank,
+            hidden_size=hidden_size,
+            top_k=top_k,
+            num_experts=num_experts,
+            rank=self.rank,
+            world_size=self.world_size,
+            receive_capacity_factor=self.receive_capacity_factor,
+            dispatch_fc1_block_size_m=self.config.dispatch_fc1_block_size_m,
+            single_kernel_dispatch_block_size_m=(
+                self.config.single_kernel_dispatch_block_size_m
+                if self.enable_single_kernel_forward else None),
+            enable_moonep=self.enable_moonep,
+            ep_group=self.ep_group,
+        )
+        self.context._extra["operator"] = weakref.ref(self)
+        self._route_to_send = self.context.route_to_send
+        self._forward_stream = None
+        self._act_buf = None
+        self._fc1_buf = None
+        self._routing_weights_keepalive = None
+
+        # All ranks must observe zeroed symmetric buffers before first use.
+        torch.cuda.synchronize()
+        if self.world_size > 1:
+            torch.distributed.barrier(group=self.ep_group)
+
+    # ===================== buffer management =====================
+    def _ensure_activation_buffers(self, ffn: int, need_fc1: bool):
+        cap = max(self.context.max_received_routes, 1)
+        dev = self.context.peer_mem.device
+        if self._act_buf is None or self._act_buf.shape[1] != ffn:
+            self._act_buf = torch.empty(cap, ffn, dtype=torch.bfloat16, device=dev)
+            self._fc1_buf = None
+        if need_fc1 and self._fc1_buf is None:
+            self._fc1_buf = torch.empty(cap, 2 * ffn, dtype=torch.bfloat16, device=dev)
+
+    def sync(self):
+        torch.cuda.synchronize()
+
+    def finalize(self):
+        """Drain the device, then release the symmetric block and all workspaces."""
+        if self.context.peer_mem is not None:
+            torch.cuda.synchronize(self.context.peer_mem.device)
+        if self.world_size > 1 and self.context.symm is not None:
+            torch.distributed.barrier(group=self.ep_group)
+        self._act_buf = None
+        self._fc1_buf = None
+        self._route_to_send = None
+        self._forward_stream = None
+        self._routing_weights_keepalive = None
+        self.context.finalize()
+
+    def read_last_forward_phase_timing(self):
+        """Per-phase device stamps are not recorded by this build."""
+        return None
+
+    # ===================== validation =====================
+    def _validate_topk_indices(self, selected_experts: torch.Tensor):
+        if selected_experts.ndim != 2:
+            raise ValueError(
+                "selected_experts must have shape [tokens, top_k], got "
+                f"{tuple(selected_experts.shape)}")
+        if selected_experts.shape[1] != self.top_k:
+            raise ValueError(
+                f"selected_experts must have top_k={self.top_k}, got shape "
+                f"{tuple(selected_experts.shape)}")
+        if selected_experts.dtype != torch.int32:
+            raise TypeError(
+                f"selected_experts must use torch.int32, got {selected_experts.dtype}")
+        if selected_experts.device != self.context.peer_mem.device:
+            raise ValueError("selected_experts must be on the operator's CUDA device")
+        if not selected_experts.is_contiguous():
+            raise ValueError("selected_experts must be contiguous")
+        if selected_experts.shape[0] > self.max_tokens_per_rank:
+            raise ValueError(
+                f"input has {selected_experts.shape[0]} tokens, exceeding "
+                f"max_tokens_per_rank={self.max_tokens_per_rank}")
+
+    def _validate_dispatch_inputs(self, hidden_states, selected_experts):
+        self._validate_topk_indices(selected_experts)
+        if hidden_states.ndim != 2:
+            raise ValueError(
+                f"hidden_states must have shape [tokens, hidden], got {tuple(hidden_states.shape)}")
+        expected_shape = (selected_experts.shape[0], self.hidden_size)
+        if hidden_states.shape != expected_shape:
+            raise ValueError(
+                f"hidden_states must have shape {expected_shape}, got {tuple(hidden_states.shape)}")
+        if hidden_states.dtype != self.activation_dtype:
+            raise TypeError(
+                f"hidden_states must use {self.activation_dtype}, got {hidden_states.dtype}")
+        if hidden_states.device != selected_experts.device:
+            raise ValueError("hidden_states and selected_experts must be on the same device")
+        if not hidden_states.is_contiguous():
+            raise ValueError("hidden_states must be contiguous")
+
+    def _validate_gate_up_weight(self, gate_up_weight, device):
+        if gate_up_weight.ndim != 3:
+            raise ValueError("gate_up_weight must have shape [experts_per_rank, hidden, 2F]")
+        if gate_up_weight.shape[0] != self.experts_per_rank:
+            raise ValueError(
+                f"gate_up_weight has {gate_up_weight.shape[0]} local experts, "
+                f"expected {self.experts_per_rank}")
+        if gate_up_weight.shape[1] != self.hidden_size:
+            raise ValueError(
+                "gate_up_weight must use [experts_per_rank, hidden, 2F] layout "
+                f"with hidden_size={self.hidden_size}, got {tuple(gate_up_weight.shape)}")
+        packed_output_size = gate_up_weight.shape[2]
+        if packed_output_size <= 0 or packed_output_size % 2:
+            raise ValueError("gate_up_weight output dimension must be a positive even value (2F)")
+        if gate_up_weight.dtype != self.activation_dtype:
+            raise TypeError(
+                f"gate_up_weight must use {self.activation_dtype}, got {gate_up_weight.dtype}")
+        if gate_up_weight.device != device:
+            raise ValueError("gate_up_weight and hidden_states must be on the same device")
+        if not gate_up_weight.is_contiguous():
+            raise ValueError("gate_up_weight must be contiguous and pre-packed before forward")
+
+    def _check_stream(self, device):
+        current_stream = torch.cuda.current_stream(device)
+        if self._forward_stream is None:
+            self._forward_stream = current_stream
+        elif self._forward_stream != current_stream:
+            raise RuntimeError(
+                "FusedMoEForward is single-stream; recreate the operator for "
+                "a different caller stream")
+
+    # ===================== routing metadata =========================
+    def build_routing_plan(self, selected_experts: torch.Tensor, *,
+                           moonep_plan_hook: Optional[Callable] = None) -> MoERoutingPlan:
+        """Build stable dispatch/count metadata for one set of selected experts."""
+        self._validate_topk_indices(selected_experts)
+        self._routing_generation += 1
+        generation = self._routing_generation
+        plan = build_routing_plan(self.context, selected_experts)
+        plan.owner_token = self._routing_owner_token
+        plan.generation = generation
+        plan.selected_experts_version = selected_experts._version
+        return plan
+
+    # ===================== dispatch + FC1 ===========================
+    def dispatch_fc1(
+        self,
+        hidden_states: torch.Tensor,
+        selected_experts: torch.Tensor,
+        routing_plan: MoERoutingPlan,
+        fc1_weight: torch.Tensor,
+        fc1_output: Optional[torch.Tensor] = None,
+        *,
+        routing_weights: torch.Tensor,
+        final_barrier: bool = True,
+        **_moonep_unused,
+    ) -> DispatchFC1Result:
+        """Dispatch routes and run the local experts' FC1 (no activation).
+
+        ``fc1_weight`` uses the contiguous ``[expert, K, N]`` layout (reference:
+        ops/forward.py:928-1320); ``fc1_output`` is ``[num_received_routes, N]`` bf16.
+        """
+        self._validate_dispatch_inputs(hidden_states, selected_experts)
+        if routing_plan.selected_experts is not selected_experts:
+            raise ValueError("routing_plan must be built from this exact selected_experts tensor")
+        if (routing_plan.owner_token is not self._routing_owner_token
+                or routing_plan.generation != self._routing_generation):
+            raise RuntimeError("routing plan belongs to another or superseded operator")
+        if routing_plan.num_input_tokens != hidden_states.shape[0]:
+            raise ValueError("routing plan token count does not match hidden_states")
+        if fc1_weight.ndim != 3:
+            raise ValueError("fc1_weight must be a 3D local-expert weight tensor")
+        if fc1_weight.shape[0] != self.experts_per_rank:
+            raise ValueError(
+                f"fc1_weight has {fc1_weight.shape[0]} local experts, "
+                f"expected {self.experts_per_rank}")
+        if fc1_weight.shape[1] != self.hidden_size:
+            raise ValueError("fc1_weight must use [expert, hidden, N] layout")
+        if fc1_weight.dtype != self.activation_dtype:
+            raise TypeError(f"fc1_weight must use {self.activation_dtype}")
+        if (routing_weights.shape != selected_experts.shape
+                or routing_weights.dtype != torch.float32
+                or not routing_weights.is_contiguous()):
+            raise ValueError(
+                "routing_weights must be contiguous FP32 with the same shape as selected_experts")
+        ctx = self.context
+        m = routing_plan.num_received_routes
+        n_out = fc1_weight.shape[2]
+        if fc1_output is None:
+            fc1_output = torch.empty(m, n_out, dtype=self.activation_dtype,
+                                     device=hidden_states.device)
+        elif fc1_output.shape != (m, n_out) or fc1_output.dtype != self.activation_dtype:
+            raise ValueError(f"fc1_output must be BF16 with shape {(m, n_out)}")
+        num_routes = selected_experts.numel()
+        L.dispatch_rows(ctx, hidden_states, routing_weights, num_routes)
+        ctx.rank_barrier()
+        if m > 0:
+            recv = ctx.peer_mem.view(ctx.max_received_routes, self.hidden_size)
+            desc = L.make_desc(ctx, recv, ctx.max_received_routes, self.hidden_size, fc1_weight,
+                               k_dim=1, n_dim=2, n_out=n_out, k_extent=self.hidden_size)
+            L.grouped_gemm(desc, fc1_output)
+        if final_barrier:
+            ctx.rank_barrier()
+        recv_rows = ctx.peer_mem.view(ctx.max_received_routes, self.hidden_size)[:m]
+        return DispatchFC1Result(
+            routing_plan=routing_plan,
+            fc1_output=fc1_output,
+            dispatched_tokens=recv_rows,
+            received_routing_weights=ctx.routing_weight_mem[:m],
+            send_route_indices=routing_plan.send_route_indices,
+        )
+
+    # ===================== full forward ================================
+    def forward(
+        self,
+        hidden_states: torch.Tensor,
+        selected_experts: torch.Tensor,
+        gate_up_weight: torch.Tensor,
+        down_weight: torch.Tensor,
+        routing_weights: torch.Tensor,
+        *,
+        return_saved: bool = False,
+    ):
+        """Run the complete BF16 post-routing MoE forward.
+
+        Shapes: ``hidden_states [T, H]`` bf16, ``selected_experts [T, k]`` int32,
+        ``gate_up_weight [EPR, H, 2F]`` bf16 (gate columns first), ``down_weight [EPR, H, F]``
+        bf16 (contiguous or a transposed view of ``[EPR, F, H]``), ``routing_weights [T, k]``
+        fp32.  Returns ``out [T, H]`` bf16, or ``(out, saved)`` with the intermediates the
+        five-stage backward consumes.
+        """
+        self._validate_dispatch_inputs(hidden_states, selected_experts)
+        self._validate_gate_up_weight(gate_up_weight, hidden_states.device)
+        self._check_stream(hidden_states.device)
+        if (routing_weights.shape != selected_experts.shape
+                or routing_weights.dtype != torch.float32
+                or routing_weights.device != hidden_states.device
+                or not routing_weights.is_contiguous()):
+            raise ValueError(
+                "routing_weights must be contiguous FP32 with the same shape "
+                "and device as selected_experts")
+        ffn_size = gate_up_weight.shape[2] // 2
+        expected_down_shape = (self.experts_per_rank, self.hidden_size, ffn_size)
+        if (down_weight.ndim != 3
+                or tuple(down_weight.shape) != expected_down_shape
+                or down_weight.dtype != self.activation_dtype
+                or down_weight.device != hidden_states.device):
+            raise ValueError(
+                "down_weight must be BF16 with shape "
+                f"{expected_down_shape} on the input device (a strided "
+                "natural-layout [E, F, H] view flows through unstaged)")
+        if (gate_up_weight.shape[2] % self.config.fc1_gemm_block_size_n
+                or self.hidden_size % self.config.fc1_gemm_block_size_k
+                or self.hidden_size % self.config.fc2_gemm_block_size_n
+                or ffn_size % self.config.fc2_gemm_block_size_k):
+            raise ValueError("configured FC1/FC2 N and K tiles must divide the weight dimensions")
+        if ffn_size % 128:
+            raise ValueError("expert FFN size must be a multiple of 128")
+
+        ctx = self.context
+        tokens = hidden_states.shape[0]
+        num_routes = tokens * self.top_k
+        hidden = self.hidden_size
+        cap = ctx.max_received_routes
+        self._ensure_activation_buffers(ffn_size, need_fc1=return_saved)
+        out = torch.empty(tokens, hidden, dtype=self.activation_dtype, device=hidden_states.device)
+
+        launch_routing_metadata(ctx, selected_experts)
+        self._routing_generation += 1
+        self._routing_weights_keepalive = routing_weights
+        L.dispatch_rows(ctx, hidden_states, routing_weights, num_routes)
+        ctx.rank_barrier()
+        recv = ctx.peer_mem.view(cap, hidden)
+        fc1_desc = L.make_desc(ctx, recv, cap, hidden, gate_up_weight, k_dim=1, n_dim=2,
+                               n_out=ffn_size, k_extent=hidden)
+        L.fc1_swiglu(ctx, fc1_desc, self._act_buf, self._fc1_buf if return_saved else None,
+                     ctx.routing_weight_mem, self.activation, self.situ_beta,
+                     self.situ_linear_beta, self.clamp_limit)
+        saved = None
+        if return_saved:
+            # The receive buffer is rewritten by the next dispatch (forward or backward), so
+            # the rows the FC1 weight gradient needs are copied out here, before the barrier
+            # that lets peers write again (reference: ops/forward.py:2074-2080).
+            recv_copy = recv.clone()
+            weights_copy = ctx.routing_weight_mem.to(torch.bfloat16)
+        fc2_desc = L.make_desc(ctx, self._act_buf, cap, ffn_size, down_weight, k_dim=2, n_dim=1,
+                               n_out=hidden, k_extent=ffn_size)
+        L.grouped_gemm_scatter(ctx, fc2_desc, "combine_mem", hidden)
+        ctx.rank_barrier()
+        L.topk_reduce(ctx.combine_mem, ctx.route_to_send, tokens, self.top_k, hidden, out)
+        check_receive_capacity(ctx)
+        if not return_saved:
+            return out
+
+        plan = snapshot_plan(ctx)
+        num_received_routes = int(ctx.metadata_stats[0].item())
+        num_sent_routes = int(ctx.metadata_local_stats[0].item())
+        m = num_received_routes
+        fc1_output = self._fc1_buf[:m].clone()
+        saved = {
+            # minimal contract of the reference's single-launch forward
+            # (ops/forward.py:1813-1873)
+            "fc1_output": fc1_output,
+            "recv_weights_sorted": weights_copy[:m],
+            "hidden_states": hidden_states,
+            "selected_experts": selected_experts,
+            "routing_weights": routing_weights,
+            "recv_expert_offsets": plan.metadata_recv_expert_offs,
+            "recv_counts_by_source_expert": plan.metadata_recv_counts_re,
+            "send_token_indices": plan.send_token_indices[:num_sent_routes],
+            "send_route_indices": plan.send_route_indices[:num_sent_routes],
+            "total_send": num_sent_routes,
+            "total_recv": m,
+            "M": m,
+            "_routing_generation": self._routing_generation,
+            "_owner_token": id(self._routing_owner_token),
+            "_single_kernel_snapshot": True,
+            # activation section and scalars of the full backward contract
+            # (ops/_torch_forward.py:294-320)
+            "recv_hidden_sorted": recv_copy[:m],
+            "swiglu_out_weighted": self._act_buf[:m].clone(),
+            "gate": fc1_output[:, :ffn_size],
+            "up": fc1_output[:, ffn_size:],
+            "expert_counts": plan.metadata_recv_per_expert,
+            "split_size_cum_per_expert": plan.metadata_recv_expert_offs,
+            "batch_size": tokens, "hidden_dim": hidden, "ffn_dim": ffn_size,
+            "num_experts": self.num_experts, "experts_per_rank": self.experts_per_rank,
+            "topk": self.top_k, "world_size": self.world_size, "ep_rank": self.rank,
+            "ep_group": self.ep_group,
+            "activation": self.activation, "situ_beta": self.situ_beta,
+            "situ_linear_beta": self.situ_linear_beta, "clamp_limit": self.clamp_limit,
+            # weight references: [E, 2F, H] / [E, F, H] views of the packed table
+            "fc1_combined": gate_up_weight.transpose(1, 2),
+            "fc1_1": gate_up_weight[:, :, :ffn_size].transpose(1, 2),
+            "fc1_2": gate_up_weight[:, :, ffn_size:].transpose(1, 2),
+            "fc2": down_weight,
+            "output": out, "dy": None,
+            "_plan": plan,
+        }
+        return out, saved
+
+
+def pack_gate_up_weights(gate_weight_local: torch.Tensor,
+                         up_weight_local: torch.Tensor) -> torch.Tensor:
+    """Pack local BF16 gate/up projections as contiguous ``[E, H, 2F]``."""
+    if gate_weight_local.ndim != 3 or up_weight_local.ndim != 3:
+        raise ValueError(
+            "gate and up weights must have shape [experts_per_rank, ffn_size, hidden_size]")
+    if gate_weight_local.shape != up_weight_local.shape:
+        raise ValueError(
+            "gate and up weight shapes must match, got "
+            f"{gate_weight_local.shape} and {up_weight_local.shape}")
+    if gate_weight_local.dtype != torch.bfloat16 or up_weight_local.dtype != torch.bfloat16:
+        raise TypeError("gate and up weights must both use torch.bfloat16")
+    if gate_weight_local.device != up_weight_local.device:
+        raise ValueError("gate and up weights must be on the same device")
+    return torch.cat(
+        (gate_weight_local.transpose(1, 2), up_weight_local.transpose(1, 2)), dim=2
+    ).contiguous()

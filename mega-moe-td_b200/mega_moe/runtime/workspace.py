@@ -1,0 +1,305 @@
+"""Symmetric (peer-mapped) buffers and reusable metadata workspaces of one MoE operator.
+
+Counterpart of the reference's ``runtime/workspace.py`` (MoEForwardContext,
+create_moe_forward_context: src/mega_moe/runtime/workspace.py:11-314).  The ACLSHMEM
+symmetric heap becomes one ``cudaMalloc`` block per rank whose CUDA-IPC handle is exchanged
+once over the EP process group; every rank then holds a table of ``world`` base pointers per
+region and kernels store straight into a peer's memory over NVLink.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as N
+
+
+def next_power_of_2(n: int) -> int:
+    return 1 if n <= 1 else 1 << (n - 1).bit_length()
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class SymmetricBlock:
+    """One same-sized device allocation per rank, mapped into every rank's address space.
+
+    ``regions`` maps a name to a byte size; each region starts at a 256-byte aligned offset
+    that is identical on all ranks.  ``local(name, dtype)`` is a torch view of this rank's
+    region, ``peer_table(name)`` a device int64 tensor of ``world`` base pointers.
+    """
+
+    def __init__(self, regions: dict[str, int], rank: int, world_size: int, group, device):
+        self.rank = rank
+        self.world_size = world_size
+        self.device = device
+        self.offsets: dict[str, int] = {}
+        self.sizes: dict[str, int] = {}
+        off = 0
+        for name, size in regions.items():
+            self.offsets[name] = off
+            self.sizes[name] = size
+            off += _align(max(size, 16))
+        self.nbytes = off
+        lib = N.lib()
+        base = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        N.check(lib.mm_symm_alloc(self.nbytes, C.byref(base), handle), "mm_symm_alloc")
+        self.base = base.value
+        self.peer_bases = [0] * world_size
+        self.peer_bases[rank] = self.base
+        self._opened: list[int] = []
+        if world_size > 1:
+            handles: list = [None] * world_size
+            dist.all_gather_object(handles, handle.raw, group=group)
+            for r, h in enumerate(handles):
+                if r == rank:
+                    continue
+                p = C.c_void_p()
+                N.check(lib.mm_symm_open(h, C.byref(p)), f"mm_symm_open(rank {r})")
+                self.peer_bases[r] = p.value
+                self._opened.append(p.value)
+        self._tables: dict[str, torch.Tensor] = {}
+
+    def local(self, name: str, dtype: torch.dtype) -> torch.Tensor:
+        return N.tensor_from_ptr(self.base + self.offsets[name], self.sizes[name], dtype,
+                                 self.device)
+
+    def peer_table(self, name: str) -> torch.Tensor:
+        if name not in self._tables:
+            ptrs = [b + self.offsets[name] for b in self.peer_bases]
+            self._tables[name] = torch.tensor(ptrs, dtype=torch.int64, device=self.device)
+        return self._tables[name]
+
+    def free(self):
+        lib = N.lib()
+        for p in self._opened:
+            lib.mm_symm_close(p)
+        self._opened = []
+        if self.base:
+            lib.mm_symm_free(self.base)
+            self.base = 0
+
+
+@dataclass
+class MoEForwardContext:
+    """Single-in-flight symmetric buffers and reusable routing workspaces.
+
+    Field names follow the reference context (runtime/workspace.py:11-59); the ``combine_*``,
+    ``send_*``, ``mtile_*`` and ``row_src_*`` members are workspaces of the CUDA pipeline.
+    A routing plan must be consumed before the next plan is built because the metadata
+    tensors are reused in place.
+    """
+
+    hidden_size: int
+    num_experts: int
+    experts_per_rank: int
+    replica_budget: int
+    physical_experts_per_rank: int
+    world_size: int
+    rank: int
+    receive_capacity_factor: float
+    max_source_tiles: int
+    top_k: int = 0
+    max_tokens_per_rank: int = 0
+    max_received_routes: int = 0
+
+    symm: Optional[SymmetricBlock] = None
+    peer_mem: Optional[torch.Tensor] = None
+    routing_weight_mem: Optional[torch.Tensor] = None
+    signal_mem: Optional[torch.Tensor] = None
+    combine_mem: Optional[torch.Tensor] = None
+    combine_gate_mem: Optional[torch.Tensor] = None
+    row_token_indices: Optional[torch.Tensor] = None
+    row_route_indices: Optional[torch.Tensor] = None
+    metadata_counts_mem: Optional[torch.Tensor] = None
+    metadata_num_bins: int = 0
+    metadata_send_bucket_starts: Optional[torch.Tensor] = None
+    metadata_send_bucket_dst_starts: Optional[torch.Tensor] = None
+    metadata_recv_counts_re: Optional[torch.Tensor] = None
+    metadata_recv_seg_starts: Optional[torch.Tensor] = None
+    metadata_recv_per_expert: Optional[torch.Tensor] = None
+    metadata_recv_expert_offs: Optional[torch.Tensor] = None
+    metadata_stats: Optional[torch.Tensor] = None
+    metadata_pull_dst_start: Optional[torch.Tensor] = None
+    metadata_local_stats: Optional[torch.Tensor] = None
+    metadata_count_row: Optional[torch.Tensor] = None
+    send_token_indices: Optional[torch.Tensor] = None
+    send_route_indices: Optional[torch.Tensor] = None
+    send_bucket: Optional[torch.Tensor] = None
+    route_to_send: Optional[torch.Tensor] = None
+    route_scratch: Optional[torch.Tensor] = None
+    mtile_group: Optional[torch.Tensor] = None
+    mtile_row0: Optional[torch.Tensor] = None
+    num_mtiles: Optional[torch.Tensor] = None
+    row_src_rank: Optional[torch.Tensor] = None
+    row_src_pos: Optional[torch.Tensor] = None
+    status: Optional[torch.Tensor] = None
+    barrier_epoch: int = 0
+    ep_group: object = None
+    _extra: dict = field(default_factory=dict)
+
+    # ---- device helpers -------------------------------------------------------------
+    def rank_barrier(self) -> None:
+        """All ranks' earlier stores into this rank's symmetric memory are visible after it."""
+        if self.world_size == 1:
+            return
+        self.barrier_epoch += 1
+        if self.barrier_epoch >= 2**31 - 1:
+            raise RuntimeError("barrier epoch exhausted; recreate the operator")
+        N.check(N.lib().mm_rank_barrier(
+            self.symm.peer_table("flags").data_ptr(), self.rank, self.world_size,
+            self.barrier_epoch, self.status.data_ptr(), N.stream_ptr()), "mm_rank_barrier")
+
+    def read_status(self) -> N.StatusRecord:
+        rec = N.StatusRecord()
+        N.check(N.lib().mm_status_read(self.status.data_ptr(), C.byref(rec), N.stream_ptr()),
+                "mm_status_read")
+        return rec
+
+    def reset_status(self) -> None:
+        N.check(N.lib().mm_status_reset(self.status.data_ptr(), N.stream_ptr()),
+                "mm_status_reset")
+
+    def finalize(self):
+        """Release the symmetric allocation and drop ordinary workspaces."""
+        if self.symm is not None:
+            torch.cuda.synchronize()
+            unregister_context(self)
+            self.symm.free()
+            self.symm = None
+        for name in list(self.__dataclass_fields__):
+            if isinstance(getattr(self, name), torch.Tensor):
+                setattr(self, name, None)
+
+
+# peer_mem data pointer -> context, so that moe_backward_triton(saved, dy, peer_mem) can find
+# the symmetric workspaces that belong to the buffer it was handed.
+_CONTEXTS: dict[int, MoEForwardContext] = {}
+
+
+def register_context(ctx: MoEForwardContext) -> None:
+    _CONTEXTS[ctx.peer_mem.data_ptr()] = ctx
+
+
+def unregister_context(ctx: MoEForwardContext) -> None:
+    if ctx.peer_mem is not None:
+        _CONTEXTS.pop(ctx.peer_mem.data_ptr(), None)
+
+
+def context_of(peer_mem: torch.Tensor) -> MoEForwardContext:
+    ctx = _CONTEXTS.get(peer_mem.data_ptr())
+    if ctx is None:
+        raise ValueError(
+            "peer_mem is not the symmetric receive buffer of a live MoE operator context")
+    return ctx
+
+
+def create_moe_forward_context(
+    *,
+    max_tokens_per_rank: int,
+    hidden_size: int,
+    top_k: int,
+    num_experts: int,
+    rank: int,
+    world_size: int,
+    receive_capacity_factor: float,
+    dispatch_fc1_block_size_m: int,
+    single_kernel_dispatch_block_size_m: Optional[int] = None,
+    enable_moonep: bool = False,
+    ep_group=None,
+    device=None,
+) -> MoEForwardContext:
+    """Allocate the symmetric block and the metadata tables (reference lines 105-314).
+
+    Sizes follow the reference: ``max_received_routes = int(max_tokens * top_k * factor)``
+    rows of ``hidden_size`` bf16 in ``peer_mem``, one fp32 routing weight per row, a
+    ``[world, next_pow2(world * epr)]`` int32 count cube.  The symmetric block also holds the
+    combine buffer (``max_tokens * top_k`` rows returned by FC2 or by the FC1 input
+    gradient), a bf16 gate-gradient channel and the barrier flag words.
+    """
+    if type(enable_moonep) is not bool:
+        raise TypeError("enable_moonep must be a bool")
+    if enable_moonep:
+        raise NotImplementedError("MoonEP is not implemented in the B200 build")
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    experts_per_rank = num_experts // world_size
+    max_received_routes = int(max_tokens_per_rank * top_k * receive_capacity_factor)
+    if max_received_routes >= torch.iinfo(torch.int32).max:
+        raise ValueError("dispatch receive offsets exceed int32 range")
+    source_tile_m = dispatch_fc1_block_size_m
+    if single_kernel_dispatch_block_size_m is not None:
+        source_tile_m = min(source_tile_m, single_kernel_dispatch_block_size_m)
+    num_routes = max_tokens_per_rank * top_k
+    max_source_tiles = (num_routes + source_tile_m - 1) // source_tile_m
+    ctx = MoEForwardContext(
+        hidden_size=hidden_size,
+        num_experts=num_experts,
+        experts_per_rank=experts_per_rank,
+        replica_budget=0,
+        physical_experts_per_rank=experts_per_rank,
+        world_size=world_size,
+        rank=rank,
+        receive_capacity_factor=receive_capacity_factor,
+        max_source_tiles=max_source_tiles,
+        top_k=top_k,
+        max_tokens_per_rank=max_tokens_per_rank,
+        max_received_routes=max_received_routes,
+        ep_group=ep_group,
+    )
+    regions = {
+        "flags": 4096,
+        "peer_mem": max_received_routes * hidden_size * 2,
+        "routing_weight_mem": max_received_routes * 4,
+        "combine_mem": num_routes * hidden_size * 2,
+        "combine_gate_mem": num_routes * 2,
+    }
+    ctx.symm = SymmetricBlock(regions, rank, world_size, ep_group, device)
+    ctx.peer_mem = ctx.symm.local("peer_mem", torch.bfloat16)
+    ctx.routing_weight_mem = ctx.symm.local("routing_weight_mem", torch.float32)
+    ctx.signal_mem = ctx.symm.local("flags", torch.int32)
+    ctx.combine_mem = ctx.symm.local("combine_mem", torch.bfloat16).view(num_routes, hidden_size)
+    ctx.combine_gate_mem = ctx.symm.local("combine_gate_mem", torch.bfloat16)
+
+    num_buckets = world_size * experts_per_rank
+    bins = next_power_of_2(num_buckets)
+    ctx.metadata_num_bins = bins
+    i32 = dict(dtype=torch.int32, device=device)
+    ctx.metadata_counts_mem = torch.zeros(world_size * bins, **i32)
+    ctx.metadata_count_row = torch.zeros(bins, **i32)
+    ctx.metadata_send_bucket_starts = torch.empty(num_buckets, **i32)
+    ctx.metadata_send_bucket_dst_starts = torch.empty(num_buckets, **i32)
+    ctx.metadata_recv_counts_re = torch.empty((world_size, experts_per_rank), **i32)
+    ctx.metadata_recv_seg_starts = torch.empty((experts_per_rank, world_size + 1), **i32)
+    ctx.metadata_recv_per_expert = torch.empty(experts_per_rank, **i32)
+    ctx.metadata_recv_expert_offs = torch.zeros(experts_per_rank + 1, **i32)
+    ctx.metadata_stats = torch.zeros(2 + world_size, **i32)
+    ctx.metadata_pull_dst_start = torch.empty(experts_per_rank * world_size, **i32)
+    ctx.metadata_local_stats = torch.zeros(2, **i32)
+    ctx.row_token_indices = torch.arange(num_routes, **i32) // top_k
+    ctx.row_route_indices = torch.arange(num_routes, **i32)
+    ctx.send_token_indices = torch.zeros(num_routes, **i32)
+    ctx.send_route_indices = torch.zeros(num_routes, **i32)
+    ctx.send_bucket = torch.zeros(num_routes, **i32)
+    ctx.route_to_send = torch.full((num_routes,), -1, **i32)
+    scratch_bytes = N.lib().mm_route_scratch_bytes(num_routes, bins)
+    ctx.route_scratch = torch.empty(max(scratch_bytes, 16), dtype=torch.uint8, device=device)
+    max_tiles = max_received_routes // 128 + experts_per_rank + 1
+    ctx.mtile_group = torch.zeros(max_tiles, **i32)
+    ctx.mtile_row0 = torch.zeros(max_tiles, **i32)
+    ctx.num_mtiles = torch.zeros(1, **i32)
+    ctx.row_src_rank = torch.zeros(max(max_received_routes, 1), **i32)
+    ctx.row_src_pos = torch.zeros(max(max_received_routes, 1), **i32)
+    ctx.status = torch.zeros(8, **i32)
+    register_context(ctx)
+    return ctx
+
+
+__all__ = ["MoEForwardContext", "SymmetricBlock", "create_moe_forward_context", "context_of"]
