@@ -1,0 +1,394 @@
+"""Benchmark of the expert-parallel MoE layer: forward + five-stage backward, tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one forward plus one backward of the layer over one batch of synthetic
+tokens per rank.  The default workload is the Kimi-K3-shaped layer (896 experts, top-16,
+hidden 7168, expert FFN 2048, 8192 tokens per rank) with the experts split evenly over the
+N ranks.  ``value`` is measured with all inputs resident in HBM; ``e2e`` adds, inside the
+timed region, the host->device copies of the step's inputs from pinned memory and the
+device->host copies of its results.
+
+``--impl reference`` times the reference's algorithm on the host CPU instead: the CPU oracle
+(a restatement of the reference's Torch functional forward/backward) on a bounded sample of
+the same workload, with all host threads.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+for p in (REPO, REPO / "mega-moe-td_b200"):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+WORKLOADS = {
+    # the configuration the headline metric is quoted on
+    "kimi_k3_e896_k16_t8192": dict(tokens=8192, hidden=7168, ffn=2048, experts=896, top_k=16,
+                                   capacity=1.25, zipf=None),
+    # smaller shapes for quick checks and ncu captures (not bench lines)
+    "qwen3_30b_e128_k8_t4096": dict(tokens=4096, hidden=2048, ffn=768, experts=128, top_k=8,
+                                    capacity=1.25, zipf=None),
+    "small_e32_k4_t1024": dict(tokens=1024, hidden=1024, ffn=512, experts=32, top_k=4,
+                               capacity=2.0, zipf=None),
+}
+DEFAULT_WORKLOAD = "kimi_k3_e896_k16_t8192"
+METRIC = "MoE fwd+bwd tokens/s (E896 top-16 H7168 F2048, 8K tok/rank), whole job"
+
+
+def measured_peaks():
+    path = REPO / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return dict(hbm_gbs=float(d["hbm_gbs"]), tflops=float(d["bf16_tflops_sustained"]),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                clocks.append(float(f[1]))
+                max_clock = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def make_device_inputs(w, rank, world, device):
+    """Seeded synthetic inputs of one rank, created on the device (weights are tens of GB)."""
+    epr = w["experts"] // world
+    g = torch.Generator(device=device).manual_seed(1000 + rank)
+    T, H, F, E, k = w["tokens"], w["hidden"], w["ffn"], w["experts"], w["top_k"]
+    x = torch.randn(T, H, generator=g, device=device).to(torch.bfloat16)
+    dy = torch.randn(T, H, generator=g, device=device).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, device=device)
+    if w.get("zipf"):
+        from oracle import moe_oracle as O  # only to build the seeded bias vector
+        logits = logits + O.zipf_expert_bias(E, w["zipf"]).to(device)[None, :]
+    top_v, top_i = torch.topk(logits, k, dim=-1)
+    rw = torch.softmax(top_v, dim=-1).float().contiguous()
+    sel = top_i.to(torch.int32).contiguous()
+    gate_up = torch.empty(epr, H, 2 * F, dtype=torch.bfloat16, device=device)
+    down = torch.empty(epr, H, F, dtype=torch.bfloat16, device=device)
+    for e0 in range(0, epr, 64):
+        gate_up[e0:e0 + 64].normal_(0.0, 0.02, generator=g)
+        down[e0:e0 + 64].normal_(0.0, 0.02, generator=g)
+    return x, dy, rw, sel, gate_up, down
+
+
+class GemmTimer:
+    """CUDA events around every grouped-GEMM launch of the timed steps."""
+
+    def __init__(self):
+        self.pairs = []
+
+    def __call__(self, name):
+        s = torch.cuda.Event(enable_timing=True)
+        e = torch.cuda.Event(enable_timing=True)
+        self.pairs.append((name, s, e))
+        return s, e
+
+    def summary(self):
+        per = {}
+        for name, s, e in self.pairs:
+            per.setdefault(name, []).append(s.elapsed_time(e))
+        return per
+
+
+def run_ours(args, w, name):
+    import mega_moe
+    from mega_moe import _native as N
+    from mega_moe.ops import _launch as L
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+    T, H, F, E, k = w["tokens"], w["hidden"], w["ffn"], w["experts"], w["top_k"]
+    cfg = mega_moe.MoEForwardConfig(receive_capacity_factor=min(float(w["capacity"]), float(world)),
+                                    enable_single_kernel_forward=True)
+    # symmetric buffers first: they are plain cudaMalloc blocks outside torch's allocator
+    op = mega_moe.FusedMoEForward(group, max_tokens_per_rank=T, hidden_size=H, top_k=k,
+                                  num_experts=E, config=cfg)
+    x, dy, rw, sel, gate_up, down = make_device_inputs(w, rank, world, device)
+    x.requires_grad_(True)
+    rw.requires_grad_(True)
+    gate_up.requires_grad_(True)
+    down.requires_grad_(True)
+    host = dict(x=x.detach().cpu().pin_memory(), dy=dy.cpu().pin_memory(),
+                rw=rw.detach().cpu().pin_memory(), sel=sel.cpu().pin_memory())
+    host_out = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    host_gh = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    host_grw = torch.empty(T, k, dtype=torch.float32).pin_memory()
+    state = __import__("types").SimpleNamespace()
+
+    def step(xx, rr, ss, dd):
+        out = mega_moe.MegaMoEFunction.apply(op, xx, rr, ss, gate_up, down, op.context.peer_mem,
+                                             state)
+        grads = torch.autograd.grad(out, [xx, rr, gate_up, down], dd)
+        return out, grads
+
+    def barrier():
+        if world > 1:
+            dist.barrier(group=group)
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            fn()
+        t1.record()
+        barrier()
+        ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=group)
+        return float(ms.item())
+
+    def resident_step():
+        step(x, rw, sel, dy)
+
+    def e2e_step():
+        xx = host["x"].to(device, non_blocking=True).requires_grad_(True)
+        rr = host["rw"].to(device, non_blocking=True).requires_grad_(True)
+        ss = host["sel"].to(device, non_blocking=True)
+        dd = host["dy"].to(device, non_blocking=True)
+        out, grads = step(xx, rr, ss, dd)
+        host_out.copy_(out.detach(), non_blocking=True)
+        host_gh.copy_(grads[0], non_blocking=True)
+        host_grw.copy_(grads[1], non_blocking=True)
+
+    for _ in range(args.warmup):
+        resident_step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    timer = GemmTimer()
+    L.EVENT_HOOK = timer
+    total_ms = timed(resident_step, args.steps)
+    L.EVENT_HOOK = None
+    clocks = sampler.stop() if rank == 0 else None
+    gemm_ms = timer.summary()
+    before = N.launch_count
+    resident_step()
+    torch.cuda.synchronize()
+    launches_per_step = N.launch_count - before
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps)
+    status = op.context.read_status()
+    m_rows = int(op.context.metadata_stats[0].item())
+
+    ms_per_step = total_ms / args.steps
+    tokens_per_s = world * T / (ms_per_step / 1e3)
+    e2e_tokens_per_s = world * T / (e2e_ms / args.steps / 1e3)
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = sum(t.numel() * t.element_size() for t in (host_out, host_gh, host_grw))
+
+    # roofline of the dominant kernel (the grouped GEMM, six launches per step)
+    peaks = measured_peaks()
+    epr = E // world
+    gemm_total_ms = sum(sum(v) for v in gemm_ms.values()) / args.steps
+    flops = 18.0 * m_rows * H * F
+    weight_bytes = epr * 3 * H * F * 2
+    # weights are read twice (forward, input gradient) and their gradients written once;
+    # every [M, *] operand or result of the six GEMMs is read or written once
+    act_bytes = m_rows * 2 * (H + 2 * F + F + H + H + F + 2 * F + H + H + F + 2 * F + H)
+    bytes_alg = 3 * weight_bytes + act_bytes
+    t_tensor = flops / (peaks["tflops"] * 1e12)
+    t_hbm = bytes_alg / (peaks["hbm_gbs"] * 1e9)
+    if t_hbm >= t_tensor:
+        achieved = bytes_alg / (gemm_total_ms / 1e3) / 1e9
+        roofline = dict(bound="hbm", achieved=round(achieved, 1), peak=peaks["hbm_gbs"],
+                        unit="GB/s", frac=round(achieved / peaks["hbm_gbs"], 4), traffic=None)
+    else:
+        achieved = flops / (gemm_total_ms / 1e3) / 1e12
+        roofline = dict(bound="tensor", achieved=round(achieved, 1), peak=peaks["tflops"],
+                        unit="TFLOP/s", frac=round(achieved / peaks["tflops"], 4), traffic=None)
+    roofline["kernel"] = "grouped_gemm_kernel (6 launches per step)"
+    roofline["kernel_ms_per_step"] = round(gemm_total_ms, 3)
+    roofline["peak_source"] = peaks["source"]
+    roofline["per_launch_ms"] = {k_: round(sum(v) / len(v), 3) for k_, v in gemm_ms.items()}
+
+    line = None
+    if rank == 0:
+        cpu = cpu_baseline_sample(w, seconds_hint=20.0) if world == 1 else None
+        line = {
+            "metric": METRIC if name == DEFAULT_WORKLOAD else f"MoE fwd+bwd tokens/s ({name})",
+            "value": round(tokens_per_s, 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": name, "tokens_per_rank": T, "hidden": H, "ffn": F,
+                       "experts": E, "top_k": k, "experts_per_rank": epr,
+                       "receive_capacity_factor": cfg.receive_capacity_factor
+                       if cfg.receive_capacity_factor is not None else world,
+                       "received_rows_rank0": m_rows, "parallelism": f"ep{world}",
+                       "l2": "inputs larger than L2 (expert weights and their gradients "
+                             f"are {3 * weight_bytes / 1e9:.1f} GB per rank and step)"},
+            "tokens_per_s_per_gpu": round(tokens_per_s / world, 1),
+            "e2e": {"value": round(e2e_tokens_per_s, 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": round(e2e_ms / args.steps, 3)},
+            "gpu_launches": launches_per_step * args.steps,
+            "gpu_launches_per_step": launches_per_step,
+            "roofline": roofline,
+            "clocks": clocks,
+            "device_status": status.code,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+    op.finalize()
+    if world > 1:
+        dist.destroy_process_group()
+    return line
+
+
+def cpu_baseline_sample(w, seconds_hint=20.0, steps=1, warmup=0):
+    """Time the CPU oracle (forward_saved + backward) on a bounded sample of the workload.
+
+    The sample keeps the per-expert problem of the workload (same hidden / FFN size, the same
+    mean rows per expert) but only ``sample_experts`` experts, so that the host holds the
+    weights and one pass takes seconds.  tokens/s = (sample routes / top_k) / time.
+    """
+    from oracle import moe_oracle as O
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    H, F, E, k, T = w["hidden"], w["ffn"], w["experts"], w["top_k"], w["tokens"]
+    rows_per_expert = max(1, T * k // E)
+    flop_per_expert = 18.0 * rows_per_expert * H * F
+    budget = seconds_hint * 0.15e12          # assume ~0.15 TFLOP/s of bf16 matmul on the host
+    sample_experts = int(max(1, min(E, 64, budget // flop_per_expert)))
+    routes = rows_per_expert * sample_experts
+    tokens = max(1, routes)                  # top-1 over the sampled experts keeps rows/expert
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(tokens, H, generator=g).to(torch.bfloat16)
+    dy = torch.randn(tokens, H, generator=g).to(torch.bfloat16)
+    sel = (torch.arange(tokens) % sample_experts).to(torch.int32).view(tokens, 1)
+    rw = torch.rand(tokens, 1, generator=g)
+    w1 = (torch.randn(sample_experts, F, H, generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(sample_experts, F, H, generator=g) * 0.02).to(torch.bfloat16)
+    w3 = (torch.randn(sample_experts, H, F, generator=g) * 0.02).to(torch.bfloat16)
+
+    def one():
+        _, saved = O.forward_saved([x], [rw], [sel], [w1], [w2], [w3], 1)
+        O.backward(saved, [dy])
+
+    for _ in range(warmup):
+        one()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": round(routes / k / dt, 2), "unit": "tokens/s", "cores": threads,
+            "kind": "port",
+            "sample": f"{sample_experts} of {E} experts with {rows_per_expert} rows each "
+                      f"(H={H}, F={F}): {routes} routes = {routes / k:.1f} tokens at top-{k}; "
+                      f"{dt:.2f} s per forward+backward",
+            "seconds_per_pass": round(dt, 3)}
+
+
+def run_reference(args, w, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    cpu = cpu_baseline_sample(w, seconds_hint=10.0, steps=args.steps, warmup=min(args.warmup, 1))
+    T = w["tokens"]
+    return {
+        "impl": "reference",
+        "metric": METRIC if name == DEFAULT_WORKLOAD else f"MoE fwd+bwd tokens/s ({name})",
+        "value": cpu["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(cpu["seconds_per_pass"] * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": name, "tokens_per_rank": T, "hidden": w["hidden"],
+                   "ffn": w["ffn"], "experts": w["experts"], "top_k": w["top_k"]},
+        "cpu_baseline": cpu,
+        "e2e": {"value": cpu["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=None, help="override tokens per rank")
+    args = ap.parse_args()
+    w = dict(WORKLOADS[args.workload])
+    if args.tokens:
+        w["tokens"] = args.tokens
+    if args.impl == "reference":
+        line = run_reference(args, w, args.workload)
+    else:
+        line = run_ours(args, w, args.workload)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -74,6 +74,14 @@ SIGNATURES = {
 
 _lib: Optional[C.CDLL] = None
 
+# Number of CUDA kernels this package has launched (benchmarks report it).
+launch_count = 0
+
+
+def count_launches(n: int) -> None:
+    global launch_count
+    launch_count += n
+
 
 def lib() -> C.CDLL:
     """Load the shared library once; fail loudly when it has not been built."""

@@ -13,6 +13,24 @@ import torch
 from .. import _native as N
 from ..runtime.workspace import MoEForwardContext
 
+# When set (by a benchmark) it is called as EVENT_HOOK(name) -> (start_event, end_event) and
+# the pair is recorded around the grouped-GEMM launch of that name.
+EVENT_HOOK = None
+
+
+class _timed:
+    def __init__(self, name):
+        self.pair = EVENT_HOOK(name) if EVENT_HOOK is not None else None
+
+    def __enter__(self):
+        if self.pair is not None:
+            self.pair[0].record()
+
+    def __exit__(self, *exc):
+        if self.pair is not None:
+            self.pair[1].record()
+        return False
+
 
 def weight_operand(weight: torch.Tensor, k_dim: int, n_dim: int):
     """Describe a per-expert weight ``[E, *, *]`` as the B operand of ``A[rows, K] @ B[K, N]``.
@@ -72,43 +90,53 @@ def dispatch_rows(ctx: MoEForwardContext, src: torch.Tensor, weights, num_routes
         ctx.symm.peer_table("peer_mem").data_ptr(),
         ctx.symm.peer_table("routing_weight_mem").data_ptr() if weights is not None else None,
         N.stream_ptr()), "mm_dispatch_rows")
+    N.count_launches(1)
 
 
 def fc1_swiglu(ctx, desc, act_out, raw_out, row_weight, activation, beta, linear_beta, clamp):
-    N.check(N.lib().mm_fc1_swiglu(
-        C.byref(desc), act_out.data_ptr(), act_out.stride(0),
-        N.ptr(raw_out), raw_out.stride(0) if raw_out is not None else 0,
-        row_weight.data_ptr(), N.ACT_IDS[activation], float(beta),
-        float(linear_beta) if linear_beta is not None else 0.0, float(clamp),
-        N.stream_ptr()), "mm_fc1_swiglu")
+    with _timed("fc1_swiglu"):
+        N.check(N.lib().mm_fc1_swiglu(
+            C.byref(desc), act_out.data_ptr(), act_out.stride(0),
+            N.ptr(raw_out), raw_out.stride(0) if raw_out is not None else 0,
+            row_weight.data_ptr(), N.ACT_IDS[activation], float(beta),
+            float(linear_beta) if linear_beta is not None else 0.0, float(clamp),
+            N.stream_ptr()), "mm_fc1_swiglu")
+    N.count_launches(1)
 
 
-def grouped_gemm(desc, out):
-    N.check(N.lib().mm_grouped_gemm(C.byref(desc), out.data_ptr(), out.stride(0),
-                                    N.stream_ptr()), "mm_grouped_gemm")
+def grouped_gemm(desc, out, name="grouped_gemm"):
+    with _timed(name):
+        N.check(N.lib().mm_grouped_gemm(C.byref(desc), out.data_ptr(), out.stride(0),
+                                        N.stream_ptr()), "mm_grouped_gemm")
+    N.count_launches(1)
 
 
-def grouped_gemm_scatter(ctx, desc, region: str, ld_dst: int, plan=None):
+def grouped_gemm_scatter(ctx, desc, region: str, ld_dst: int, plan=None, name="gemm_scatter"):
     p = plan if plan is not None else ctx
-    N.check(N.lib().mm_grouped_gemm_scatter(
-        C.byref(desc), p.row_src_rank.data_ptr(), p.row_src_pos.data_ptr(),
-        ctx.symm.peer_table(region).data_ptr(), ld_dst, N.stream_ptr()),
-        "mm_grouped_gemm_scatter")
+    with _timed(name):
+        N.check(N.lib().mm_grouped_gemm_scatter(
+            C.byref(desc), p.row_src_rank.data_ptr(), p.row_src_pos.data_ptr(),
+            ctx.symm.peer_table(region).data_ptr(), ld_dst, N.stream_ptr()),
+            "mm_grouped_gemm_scatter")
+    N.count_launches(1)
 
 
-def grouped_wgrad(ctx, grad_out, orig_in, rows_cap, group_offs, num_groups, out):
+def grouped_wgrad(ctx, grad_out, orig_in, rows_cap, group_offs, num_groups, out, name="wgrad"):
     """out[g] [Mw, Nw] = grad_out[rows of g]^T @ orig_in[rows of g]."""
-    N.check(N.lib().mm_grouped_wgrad(
-        grad_out.data_ptr(), grad_out.stride(0), grad_out.shape[1],
-        orig_in.data_ptr(), orig_in.stride(0), orig_in.shape[1], rows_cap,
-        group_offs.data_ptr(), num_groups, out.data_ptr(), out.stride(1), out.stride(0),
-        ctx.status.data_ptr(), 0, N.stream_ptr()), "mm_grouped_wgrad")
+    with _timed(name):
+        N.check(N.lib().mm_grouped_wgrad(
+            grad_out.data_ptr(), grad_out.stride(0), grad_out.shape[1],
+            orig_in.data_ptr(), orig_in.stride(0), orig_in.shape[1], rows_cap,
+            group_offs.data_ptr(), num_groups, out.data_ptr(), out.stride(1), out.stride(0),
+            ctx.status.data_ptr(), 0, N.stream_ptr()), "mm_grouped_wgrad")
+    N.count_launches(1)
 
 
 def topk_reduce(rows, route_to_send, tokens, top_k, hidden, out, gate_in=None, gate_out=None):
     N.check(N.lib().mm_topk_reduce(
         rows.data_ptr(), rows.stride(0), route_to_send.data_ptr(), tokens, top_k, hidden,
         out.data_ptr(), N.ptr(gate_in), N.ptr(gate_out), N.stream_ptr()), "mm_topk_reduce")
+    N.count_launches(1)
 
 
 def swiglu_bwd(ctx, grad_act, fc1_out, row_scale, ffn, num_rows_dev, max_rows, grad_fc1,
@@ -125,3 +153,4 @@ def swiglu_bwd(ctx, grad_act, fc1_out, row_scale, ffn, num_rows_dev, max_rows, g
         p.row_src_pos.data_ptr() if push_gate else None,
         ctx.symm.peer_table("combine_gate_mem").data_ptr() if push_gate else None,
         N.stream_ptr()), "mm_swiglu_bwd")
+    N.count_launches(1)

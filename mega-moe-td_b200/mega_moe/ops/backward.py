@@ -90,7 +90,7 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     if m > 0:
         desc = L.make_desc(ctx, recv_dy, cap, hidden, fc2, k_dim=1, n_dim=2, n_out=ffn,
                            k_extent=hidden, **tiles)
-        L.grouped_gemm(desc, grad_swiglu)
+        L.grouped_gemm(desc, grad_swiglu, name="fc2_dgrad")
     grad_fc2_out_sorted = recv_dy[:m]
 
     # ---- stage 3: FC2 weight gradient (reads the receive buffer, so it runs before the
@@ -98,7 +98,7 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     act = saved["swiglu_out_weighted"]
     if m > 0:
         grad_fc2 = torch.empty(epr, hidden, ffn, dtype=dtype, device=device)
-        L.grouped_wgrad(ctx, recv_dy, act, m, group_offs, epr, grad_fc2)
+        L.grouped_wgrad(ctx, recv_dy, act, m, group_offs, epr, grad_fc2, name="fc2_wgrad")
     else:
         grad_fc2 = torch.zeros(epr, hidden, ffn, dtype=dtype, device=device)
 
@@ -114,7 +114,8 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     # ---- stage 5: FC1 weight gradient -------------------------------------------------
     if m > 0:
         grad_fc1 = torch.empty(epr, 2 * ffn, hidden, dtype=dtype, device=device)
-        L.grouped_wgrad(ctx, grad_fc1_output, recv_hidden_sorted, m, group_offs, epr, grad_fc1)
+        L.grouped_wgrad(ctx, grad_fc1_output, recv_hidden_sorted, m, group_offs, epr, grad_fc1,
+                        name="fc1_wgrad")
     else:
         grad_fc1 = torch.zeros(epr, 2 * ffn, hidden, dtype=dtype, device=device)
 
@@ -122,7 +123,7 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     if m > 0:
         desc = L.make_desc(ctx, grad_fc1_output, m, 2 * ffn, fc1_combined, k_dim=1, n_dim=2,
                            n_out=hidden, k_extent=2 * ffn, **tiles)
-        L.grouped_gemm_scatter(ctx, desc, "combine_mem", hidden, plan=plan)
+        L.grouped_gemm_scatter(ctx, desc, "combine_mem", hidden, plan=plan, name="fc1_dgrad_combine")
     ctx.rank_barrier()
     grad_hidden = torch.empty(tokens, hidden, dtype=dtype, device=device)
     grad_routing_weights = torch.empty(tokens, top_k, dtype=dtype, device=device)

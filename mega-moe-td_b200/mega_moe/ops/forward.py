@@ -412,7 +412,7 @@ class FusedMoEForward(torch.nn.Module):
             weights_copy = ctx.routing_weight_mem.to(torch.bfloat16)
         fc2_desc = L.make_desc(ctx, self._act_buf, cap, ffn_size, down_weight, k_dim=2, n_dim=1,
                                n_out=hidden, k_extent=ffn_size)
-        L.grouped_gemm_scatter(ctx, fc2_desc, "combine_mem", hidden)
+        L.grouped_gemm_scatter(ctx, fc2_desc, "combine_mem", hidden, name="fc2_combine")
         ctx.rank_barrier()
         L.topk_reduce(ctx.combine_mem, ctx.route_to_send, tokens, self.top_k, hidden, out)
         check_receive_capacity(ctx)

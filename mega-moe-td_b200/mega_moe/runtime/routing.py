@@ -84,6 +84,7 @@ def launch_routing_metadata(context: MoEForwardContext, selected_experts: torch.
         ctx.mtile_group.data_ptr(), ctx.mtile_row0.data_ptr(), ctx.num_mtiles.data_ptr(),
         ctx.row_src_rank.data_ptr(), ctx.row_src_pos.data_ptr(), ctx.status.data_ptr(), stream),
         "mm_route_finalize")
+    N.count_launches(5)  # histogram, scan, scatter, offsets, row tables
 
 
 def check_receive_capacity(context: MoEForwardContext) -> None:

@@ -156,6 +156,7 @@ class MoEForwardContext:
         N.check(N.lib().mm_rank_barrier(
             self.symm.peer_table("flags").data_ptr(), self.rank, self.world_size,
             self.barrier_epoch, self.status.data_ptr(), N.stream_ptr()), "mm_rank_barrier")
+        N.count_launches(1)
 
     def read_status(self) -> N.StatusRecord:
         rec = N.StatusRecord()
