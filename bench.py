@@ -20,10 +20,13 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import time
 from pathlib import Path
+
+# The headline workload fills ~170 of the 180 GB of one B200 at N=1; expandable segments keep
+# torch's caching allocator from fragmenting around the 26 GB and 52 GB gradient tensors.
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
 REPO = Path(__file__).resolve().parent
 for p in (REPO, REPO / "mega-moe-td_b200"):
@@ -37,6 +40,10 @@ WORKLOADS = {
     # the configuration the headline metric is quoted on
     "kimi_k3_e896_k16_t8192": dict(tokens=8192, hidden=7168, ffn=2048, experts=896, top_k=16,
                                    capacity=1.25, zipf=None),
+    # one rank's share of the headline layer at 8 GPUs (112 local experts, same rows per rank):
+    # the per-GPU GEMM shapes of the 8-GPU run on a single GPU, for kernel tuning and ncu
+    "kimi_k3_rank_share_e112_k16_t8192": dict(tokens=8192, hidden=7168, ffn=2048, experts=112,
+                                              top_k=16, capacity=1.25, zipf=None),
     # smaller shapes for quick checks and ncu captures (not bench lines)
     "qwen3_30b_e128_k8_t4096": dict(tokens=4096, hidden=2048, ffn=768, experts=128, top_k=8,
                                     capacity=1.25, zipf=None),
@@ -57,50 +64,67 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons through NVML on a background thread while the
+    timed region runs (reading only; no setting of the GPU is touched)."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {
+        "hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
+        "hw_thermal_slowdown": 0x40, "hw_power_brake_slowdown": 0x80,
+    }
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, period_s: float = 0.05):
         self.gpu_index = gpu_index
-        self.proc = None
+        self.period_s = period_s
+        self.samples = []
+        self.reason_bits = 0
+        self.max_clock = None
+        self.power_w_max = None
+        self._stop = None
+        self._thread = None
+        self.error = None
+
+    def _run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = torch.cuda.get_device_properties(self.gpu_index).uuid
+            try:
+                h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self.max_clock = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            while not self._stop.is_set():
+                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                try:
+                    self.reason_bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                except Exception:
+                    self.reason_bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                try:
+                    pw = pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0
+                    self.power_w_max = pw if self.power_w_max is None else max(self.power_w_max, pw)
+                except Exception:
+                    pass
+                self._stop.wait(self.period_s)
+        except Exception as exc:  # NVML missing: report it instead of failing the benchmark
+            self.error = repr(exc)[:200]
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "200", "-i", str(self.gpu_index)],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+        import threading
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        clocks, max_clock, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                clocks.append(float(f[1]))
-                max_clock = float(f[2])
-            except ValueError:
-                continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(clocks) if clocks else None,
-                "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks)}
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=5)
+        reasons = sorted(n for n, bit in self.REASONS.items() if self.reason_bits & bit)
+        out = {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+               "sm_max_mhz": self.max_clock, "reasons": reasons, "samples": len(self.samples),
+               "power_w_max": self.power_w_max}
+        if self.error:
+            out["error"] = self.error
+        return out
 
 
 def make_device_inputs(w, rank, world, device):
@@ -166,6 +190,8 @@ def run_ours(args, w, name):
     # symmetric buffers first: they are plain cudaMalloc blocks outside torch's allocator
     op = mega_moe.FusedMoEForward(group, max_tokens_per_rank=T, hidden_size=H, top_k=k,
                                   num_experts=E, config=cfg)
+    # expert-weight gradients land in buffers allocated once (the work per step is unchanged)
+    op.persistent_weight_grads = True
     x, dy, rw, sel, gate_up, down = make_device_inputs(w, rank, world, device)
     x.requires_grad_(True)
     rw.requires_grad_(True)
@@ -294,6 +320,7 @@ def run_ours(args, w, name):
             "roofline": roofline,
             "clocks": clocks,
             "device_status": status.code,
+            "peak_torch_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu

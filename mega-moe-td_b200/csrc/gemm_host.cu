@@ -77,12 +77,12 @@ bool prepare_kernel() {
   return true;
 }
 
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid_limit,
-           cudaStream_t stream) {
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+           const GemmParams& p, int grid_limit, cudaStream_t stream) {
   if (!prepare_kernel()) return MM_ERR_CUDA;
   int grid = g_num_sms;
   if (grid_limit > 0 && grid_limit < grid) grid = grid_limit;
-  grouped_gemm_kernel<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(tmA, tmB, p);
+  grouped_gemm_kernel<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(tmA, tmB, tmC, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("grouped_gemm_kernel launch: %s", cudaGetErrorString(e));
@@ -149,7 +149,8 @@ int grouped_rows_gemm(int epi, const mm_gemm_desc& d, GemmParams p, cudaStream_t
     p.n_tiles = (d.N + kBlockN - 1) / kBlockN;
     p.swiglu_F = 0;
   }
-  return launch(tmA, tmB, p, d.grid_limit, stream);
+  p.tma_store = 0;
+  return launch(tmA, tmB, tmA, p, d.grid_limit, stream);
 }
 
 }  // namespace mm
@@ -217,7 +218,17 @@ int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void
     set_error("mm_grouped_wgrad: extents/strides must be multiples of 8 (Nw of 32)");
     return MM_ERR_ARG;
   }
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
+  {
+    uint64_t dims[3] = {(uint64_t)Nw, (uint64_t)Mw, (uint64_t)num_groups};
+    uint64_t str[2] = {(uint64_t)ld_out * 2, (uint64_t)out_group_stride * 2};
+    uint32_t box[3] = {64, 32, 1};
+    if (!aligned16(out) || !encode_map(&tmC, out, 3, dims, str, box)) {
+      if (aligned16(out)) return MM_ERR_CUDA;
+      set_error("mm_grouped_wgrad: out must be 16-byte aligned");
+      return MM_ERR_ARG;
+    }
+  }
   {
     uint64_t dims[2] = {(uint64_t)Mw, (uint64_t)rows_cap};
     uint64_t str[1] = {(uint64_t)ld_go * 2};
@@ -246,7 +257,8 @@ int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void
   p.ld_out = ld_out;
   p.out_group_stride = out_group_stride;
   p.status = reinterpret_cast<StatusRecord*>(status);
-  return launch(tmA, tmB, p, grid_limit, stream);
+  p.tma_store = 1;
+  return launch(tmA, tmB, tmC, p, grid_limit, stream);
 }
 
 }  // extern "C"

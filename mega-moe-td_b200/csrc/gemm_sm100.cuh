@@ -28,7 +28,7 @@ constexpr int kStageBBytes = kBlockN * kBlockK * 2;               // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;          // 48 KB
 constexpr int kBoxBytes = 64 * 64 * 2;                            // one 64x64 MN-major box
 constexpr int kEpiWarps = 4;
-constexpr int kStagingPerWarp = 3 * 32 * 64;                      // three 32-row x 64-byte buffers
+constexpr int kStagingPerWarp = 2 * 32 * 128;                     // two 32-row x 128-byte buffers
 constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
 constexpr int kTmemCols = 512;
 constexpr int kGemmSmemBytes =
@@ -50,6 +50,7 @@ struct GemmParams {
   int32_t n_tiles;       // tiles along N (kEpiSwiglu: F / 128)
   int32_t m_tiles;       // kGroupedReduce: tiles along m'
   int32_t swiglu_F;      // column offset of the "up" half inside B and inside out2
+  int32_t tma_store;     // kGroupedReduce: output tiles leave through TMA tensor stores
   int32_t act;
   float act_beta;
   float act_linear_beta; // <= 0: no transform on up
@@ -130,35 +131,54 @@ __device__ __forceinline__ float gated_activation(float g, float u, const GemmPa
   }
 }
 
-// Write 32 bf16 values of this lane's row into a 32-row x 64-byte staging buffer
-// (16-byte chunks XOR-swizzled by row so that both phases are bank-conflict free).
-__device__ __forceinline__ void stage_row(uint8_t* stg, uint32_t lane, const uint32_t (&v)[16]) {
-  const uint32_t sw = (lane >> 1) & 3;
+// Staging buffers hold 32 rows x 128 bytes (64 bf16 columns); the 16-byte chunk c of row r
+// lives at r * 128 + ((c ^ (r & 7)) << 4).  That is the 128-byte TMA swizzle, so a buffer can
+// leave through a tensor store, and it keeps both the row-wise writes and the chunk-wise
+// reads free of bank conflicts.
+
+// Write 32 bf16 values (chunks first_chunk .. first_chunk + 3) of this lane's row.
+__device__ __forceinline__ void stage_half_row(uint8_t* stg, uint32_t lane, int first_chunk,
+                                               const uint32_t (&v)[16]) {
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     uint4 q = make_uint4(v[4 * c + 0], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-    *reinterpret_cast<uint4*>(stg + lane * 64 + ((c ^ sw) << 4)) = q;
+    *reinterpret_cast<uint4*>(stg + lane * 128 + ((((uint32_t)(first_chunk + c)) ^ (lane & 7)) << 4)) = q;
   }
 }
 
-// Store a staged 32 x 32 bf16 block: each warp instruction writes 8 rows x 64 bytes.
-// row_ptr is this lane's row base (already offset to the block's first column).
-__device__ __forceinline__ void flush_rows(const uint8_t* stg, uint32_t lane, uint8_t* row_ptr,
-                                           int valid) {
+// Convert 64 fp32 accumulator values of this lane's row to bf16 and stage them.
+__device__ __forceinline__ void stage_row_f32(uint8_t* stg, uint32_t lane, const uint32_t (&r)[64]) {
 #pragma unroll
-  for (int it = 0; it < 4; ++it) {
-    const uint32_t r = it * 8 + (lane >> 2);
-    const uint32_t c = lane & 3;
-    const uint4 q = *reinterpret_cast<const uint4*>(stg + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+  for (int c = 0; c < 8; ++c) {
+    uint4 q;
+    q.x = pack_bf16x2(__uint_as_float(r[8 * c + 0]), __uint_as_float(r[8 * c + 1]));
+    q.y = pack_bf16x2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3]));
+    q.z = pack_bf16x2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5]));
+    q.w = pack_bf16x2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]));
+    *reinterpret_cast<uint4*>(stg + lane * 128 + ((((uint32_t)c) ^ (lane & 7)) << 4)) = q;
+  }
+}
+
+// Store a staged 32-row x 64-column bf16 block with plain stores: each warp instruction
+// writes 4 rows x 128 bytes.  row_ptr is this lane's row base (already offset to the block's
+// first column); cols_valid masks the columns past the logical output width.
+__device__ __forceinline__ void flush_rows(const uint8_t* stg, uint32_t lane, uint8_t* row_ptr,
+                                           int valid, int cols_valid) {
+  const uint32_t c = lane & 7;
+  const bool col_ok = (int)(c * 8) < cols_valid;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const uint32_t r = it * 4 + (lane >> 3);
+    const uint4 q = *reinterpret_cast<const uint4*>(stg + r * 128 + ((c ^ (r & 7)) << 4));
     const uint64_t pr = __shfl_sync(0xffffffffu, (unsigned long long)row_ptr, r);
     const int ok = __shfl_sync(0xffffffffu, valid, r);
-    if (ok) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pr) + c * 16) = q;
+    if (ok && col_ok) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pr) + c * 16) = q;
   }
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -189,6 +209,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (p.tma_store) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(tmem_base_slot, kTmemCols);
@@ -326,9 +347,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // -------------------------------- epilogue --------------------------------
     const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
     const uint32_t ew = warp - 2;
-    uint8_t* stg = staging + ew * kStagingPerWarp;
+    uint8_t* stg = staging + ew * kStagingPerWarp;  // two 4 KB buffers, 1024-byte aligned
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t buf = 0;  // staging buffer the next chunk uses
     for (int32_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
       const TileInfo ti = decode_tile(p, t, nmt);
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, kSiteTmemFull, acc)) break;
@@ -338,40 +360,92 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t t_acc = tmem_base + acc * kBlockN + ((q * 32u) << 16);
 
       if (p.epi == kEpiSwiglu) {
+        // TMEM columns 0..127 hold gate, 128..255 up, for F columns n0 .. n0 + 127.
         const int64_t grow = (int64_t)ti.row0 + row;
         uint8_t* act_ptr = reinterpret_cast<uint8_t*>(p.out + grow * p.ld_out + ti.n0);
         uint8_t* raw_ptr =
             p.out2 ? reinterpret_cast<uint8_t*>(p.out2 + grow * p.ld_out2 + ti.n0) : nullptr;
         const float w = valid ? p.row_weight[grow] : 0.0f;
+        uint8_t* sa = stg;          // activation, 64 columns per pass
+        uint8_t* sg = stg + 4096;   // raw gate (first half of the pass), then raw up
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t rg[32], ru[32];
-          tmem_ld_32x32(t_acc + c * 32, rg);
-          tmem_ld_32x32(t_acc + 128 + c * 32, ru);
-          tmem_ld_wait();
-          uint32_t pa[16], pg[16], pu[16];
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            uint32_t rg[32], ru[32];
+            tmem_ld_32x32(t_acc + c * 64 + h * 32, rg);
+            tmem_ld_32x32(t_acc + 128 + c * 64 + h * 32, ru);
+            tmem_ld_wait_regs(rg);
+            tmem_ld_wait_regs(ru);
+            uint32_t pa[16], pg[16], pu[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float g0 = bf16_round(__uint_as_float(rg[2 * j]));
-            const float g1 = bf16_round(__uint_as_float(rg[2 * j + 1]));
-            const float u0 = bf16_round(__uint_as_float(ru[2 * j]));
-            const float u1 = bf16_round(__uint_as_float(ru[2 * j + 1]));
-            pg[j] = pack_bf16x2(g0, g1);
-            pu[j] = pack_bf16x2(u0, u1);
-            pa[j] = pack_bf16x2(gated_activation(g0, u0, p) * w, gated_activation(g1, u1, p) * w);
-          }
-          stage_row(stg, lane, pa);
-          if (raw_ptr) {
-            stage_row(stg + 2048, lane, pg);
-            stage_row(stg + 4096, lane, pu);
+            for (int j = 0; j < 16; ++j) {
+              const float g0 = bf16_round(__uint_as_float(rg[2 * j]));
+              const float g1 = bf16_round(__uint_as_float(rg[2 * j + 1]));
+              const float u0 = bf16_round(__uint_as_float(ru[2 * j]));
+              const float u1 = bf16_round(__uint_as_float(ru[2 * j + 1]));
+              pg[j] = pack_bf16x2(g0, g1);
+              pu[j] = pack_bf16x2(u0, u1);
+              pa[j] = pack_bf16x2(gated_activation(g0, u0, p) * w, gated_activation(g1, u1, p) * w);
+            }
+            stage_half_row(sa, lane, h * 4, pa);
+            if (raw_ptr) {
+              // raw rows are flushed 32 columns at a time: gate in chunks 0..3, up in 4..7
+              stage_half_row(sg, lane, 0, pg);
+              stage_half_row(sg, lane, 4, pu);
+              __syncwarp();
+              {
+                const uint32_t cc = lane & 7;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                  const uint32_t r = it * 4 + (lane >> 3);
+                  const uint4 qv =
+                      *reinterpret_cast<const uint4*>(sg + r * 128 + ((cc ^ (r & 7)) << 4));
+                  const uint64_t pr = __shfl_sync(0xffffffffu, (unsigned long long)raw_ptr, r);
+                  const int ok = __shfl_sync(0xffffffffu, valid, r);
+                  if (ok) {
+                    uint8_t* dst = reinterpret_cast<uint8_t*>(pr) + (c * 64 + h * 32) * 2 +
+                                   (cc < 4 ? cc * 16 : (int64_t)p.swiglu_F * 2 + (cc - 4) * 16);
+                    *reinterpret_cast<uint4*>(dst) = qv;
+                  }
+                }
+              }
+              __syncwarp();
+            }
           }
           __syncwarp();
-          flush_rows(stg, lane, act_ptr + c * 64, valid);
-          if (raw_ptr) {
-            flush_rows(stg + 2048, lane, raw_ptr + c * 64, valid);
-            flush_rows(stg + 4096, lane, raw_ptr + (int64_t)p.swiglu_F * 2 + c * 64, valid);
-          }
+          flush_rows(sa, lane, act_ptr + c * 128, valid, 64);
           __syncwarp();
+        }
+      } else if (p.tma_store) {
+        // Rectangular output tile (weight gradient): stage 32 x 64 blocks in the swizzled
+        // layout and let one lane issue a tensor store per block; the map clips the edges.
+        const bool zero_tile = (ti.num_kb == 0);
+        const int nch = min(kBlockN / 64, (p.N - ti.n0 + 63) / 64);
+        uint32_t ra[64];
+        if (!zero_tile && nch > 0) tmem_ld_32x64(t_acc, ra);
+#pragma unroll 1
+        for (int c = 0; c < nch; ++c) {
+          uint8_t* sb = stg + buf * 4096;
+          // the store issued two blocks ago from this buffer must have read it
+          if (lane == 0) bulk_wait_group_read<1>();
+          __syncwarp();
+          if (!zero_tile) {
+            tmem_ld_wait_regs(ra);
+            stage_row_f32(sb, lane, ra);
+            if (c + 1 < nch) tmem_ld_32x64(t_acc + (c + 1) * 64, ra);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              *reinterpret_cast<uint4*>(sb + lane * 128 + k * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && ti.row0 + (int32_t)q * 32 < p.Mw) {
+            tma_store_3d(&tmC, sb, ti.n0 + c * 64, ti.row0 + (int32_t)q * 32, ti.group);
+            bulk_commit_group();
+          }
+          buf ^= 1;
         }
       } else {
         uint8_t* row_ptr = nullptr;
@@ -390,25 +464,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         const bool zero_tile = (ti.num_kb == 0);
+        const int cols_left = p.N - ti.n0;
+        const int nch = min(kBlockN / 64, (cols_left + 63) / 64);
+        uint32_t ra[64];
+        if (!zero_tile && nch > 0) tmem_ld_32x64(t_acc, ra);
 #pragma unroll 1
-        for (int c = 0; c < kBlockN / 32; ++c) {
-          if (ti.n0 + c * 32 >= p.N) break;
-          uint32_t r[32];
-          uint32_t pk[16];
+        for (int c = 0; c < nch; ++c) {
+          uint8_t* sb = stg + buf * 4096;
           if (!zero_tile) {
-            tmem_ld_32x32(t_acc + c * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              pk[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            tmem_ld_wait_regs(ra);
+            stage_row_f32(sb, lane, ra);
+            // the next block's TMEM load overlaps the stores of this one
+            if (c + 1 < nch) tmem_ld_32x64(t_acc + (c + 1) * 64, ra);
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) pk[j] = 0u;
+            for (int k = 0; k < 8; ++k)
+              *reinterpret_cast<uint4*>(sb + lane * 128 + k * 16) = make_uint4(0, 0, 0, 0);
           }
-          stage_row(stg, lane, pk);
           __syncwarp();
-          flush_rows(stg, lane, row_ptr + c * 64, valid);
-          __syncwarp();
+          flush_rows(sb, lane, row_ptr + c * 128, valid, cols_left - c * 64);
+          buf ^= 1;
         }
       }
       tc_fence_before_sync();
@@ -416,6 +491,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    // every tensor store of this warp must have completed before the CTA retires
+    if (p.tma_store && lane == 0) bulk_wait_group_all();
   }
 
   tc_fence_before_sync();

@@ -81,6 +81,8 @@ def make_desc(ctx: MoEForwardContext, a: torch.Tensor, a_rows_cap: int, lda: int
 def dispatch_rows(ctx: MoEForwardContext, src: torch.Tensor, weights, num_routes: int, plan=None):
     """Push the send rows of ``src`` (and their routing weights) to the owning ranks."""
     p = plan if plan is not None else ctx
+    _t = _timed("dispatch_rows")
+    _t.__enter__()
     N.check(N.lib().mm_dispatch_rows(
         src.data_ptr(), ctx.hidden_size, N.ptr(weights),
         p.send_token_indices.data_ptr(), p.send_route_indices.data_ptr(),
@@ -90,6 +92,7 @@ def dispatch_rows(ctx: MoEForwardContext, src: torch.Tensor, weights, num_routes
         ctx.symm.peer_table("peer_mem").data_ptr(),
         ctx.symm.peer_table("routing_weight_mem").data_ptr() if weights is not None else None,
         N.stream_ptr()), "mm_dispatch_rows")
+    _t.__exit__()
     N.count_launches(1)
 
 
@@ -133,15 +136,20 @@ def grouped_wgrad(ctx, grad_out, orig_in, rows_cap, group_offs, num_groups, out,
 
 
 def topk_reduce(rows, route_to_send, tokens, top_k, hidden, out, gate_in=None, gate_out=None):
+    _t = _timed("topk_reduce")
+    _t.__enter__()
     N.check(N.lib().mm_topk_reduce(
         rows.data_ptr(), rows.stride(0), route_to_send.data_ptr(), tokens, top_k, hidden,
         out.data_ptr(), N.ptr(gate_in), N.ptr(gate_out), N.stream_ptr()), "mm_topk_reduce")
+    _t.__exit__()
     N.count_launches(1)
 
 
 def swiglu_bwd(ctx, grad_act, fc1_out, row_scale, ffn, num_rows_dev, max_rows, grad_fc1,
                grad_scale, activation, beta, linear_beta, clamp, plan=None, push_gate=True):
     p = plan if plan is not None else ctx
+    _t = _timed("swiglu_bwd")
+    _t.__enter__()
     N.check(N.lib().mm_swiglu_bwd(
         grad_act.data_ptr(), grad_act.stride(0), fc1_out.data_ptr(), fc1_out.stride(0),
         row_scale.data_ptr(), ffn, num_rows_dev.data_ptr(), max_rows,
@@ -153,4 +161,5 @@ def swiglu_bwd(ctx, grad_act, fc1_out, row_scale, ffn, num_rows_dev, max_rows, g
         p.row_src_pos.data_ptr() if push_gate else None,
         ctx.symm.peer_table("combine_gate_mem").data_ptr() if push_gate else None,
         N.stream_ptr()), "mm_swiglu_bwd")
+    _t.__exit__()
     N.count_launches(1)

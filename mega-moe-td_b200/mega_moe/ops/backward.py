@@ -96,8 +96,10 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     # ---- stage 3: FC2 weight gradient (reads the receive buffer, so it runs before the
     #      barrier of stage 4 lets peers dispatch into it again) ---------------------------
     act = saved["swiglu_out_weighted"]
+    grad_ws = saved.get("_grad_workspace")
     if m > 0:
-        grad_fc2 = torch.empty(epr, hidden, ffn, dtype=dtype, device=device)
+        grad_fc2 = (grad_ws["grad_fc2"] if grad_ws is not None
+                    else torch.empty(epr, hidden, ffn, dtype=dtype, device=device))
         L.grouped_wgrad(ctx, recv_dy, act, m, group_offs, epr, grad_fc2, name="fc2_wgrad")
     else:
         grad_fc2 = torch.zeros(epr, hidden, ffn, dtype=dtype, device=device)
@@ -113,7 +115,8 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
 
     # ---- stage 5: FC1 weight gradient -------------------------------------------------
     if m > 0:
-        grad_fc1 = torch.empty(epr, 2 * ffn, hidden, dtype=dtype, device=device)
+        grad_fc1 = (grad_ws["grad_fc1"] if grad_ws is not None
+                    else torch.empty(epr, 2 * ffn, hidden, dtype=dtype, device=device))
         L.grouped_wgrad(ctx, grad_fc1_output, recv_hidden_sorted, m, group_offs, epr, grad_fc1,
                         name="fc1_wgrad")
     else:

@@ -150,6 +150,12 @@ class FusedMoEForward(torch.nn.Module):
         self._act_buf = None
         self._fc1_buf = None
         self._routing_weights_keepalive = None
+        # When True, the backward writes the expert-weight gradients into buffers that are
+        # allocated once and handed out again every step (the caller must consume or
+        # accumulate them before the next backward), like the fixed-address saved-activation
+        # workspace of the reference (ops/forward.py:246-282).  Off by default.
+        self.persistent_weight_grads = False
+        self._grad_ws = None
 
         # All ranks must observe zeroed symmetric buffers before first use.
         torch.cuda.synchronize()
@@ -166,6 +172,17 @@ class FusedMoEForward(torch.nn.Module):
         if need_fc1 and self._fc1_buf is None:
             self._fc1_buf = torch.empty(cap, 2 * ffn, dtype=torch.bfloat16, device=dev)
 
+    def _get_grad_workspace(self, ffn: int):
+        if self._grad_ws is None or self._grad_ws["grad_fc2"].shape[2] != ffn:
+            dev = self.context.peer_mem.device
+            self._grad_ws = {
+                "grad_fc1": torch.empty(self.experts_per_rank, 2 * ffn, self.hidden_size,
+                                        dtype=torch.bfloat16, device=dev),
+                "grad_fc2": torch.empty(self.experts_per_rank, self.hidden_size, ffn,
+                                        dtype=torch.bfloat16, device=dev),
+            }
+        return self._grad_ws
+
     def sync(self):
         torch.cuda.synchronize()
 
@@ -177,6 +194,7 @@ class FusedMoEForward(torch.nn.Module):
             torch.distributed.barrier(group=self.ep_group)
         self._act_buf = None
         self._fc1_buf = None
+        self._grad_ws = None
         self._route_to_send = None
         self._forward_stream = None
         self._routing_weights_keepalive = None
@@ -464,6 +482,8 @@ class FusedMoEForward(torch.nn.Module):
             "output": out, "dy": None,
             "_plan": plan,
         }
+        if self.persistent_weight_grads:
+            saved["_grad_workspace"] = self._get_grad_workspace(ffn_size)
         return out, saved
 
 

@@ -61,6 +61,9 @@ def launch_routing_metadata(context: MoEForwardContext, selected_experts: torch.
     ctx = context
     num_routes = selected_experts.numel()
     stream = N.stream_ptr()
+    from ..ops import _launch as L
+    timer = L._timed("routing_metadata")
+    timer.__enter__()
     N.check(lib.mm_route_local(
         selected_experts.data_ptr(), num_routes, ctx.top_k, ctx.num_experts,
         ctx.metadata_num_bins, ctx.send_route_indices.data_ptr(),
@@ -84,6 +87,7 @@ def launch_routing_metadata(context: MoEForwardContext, selected_experts: torch.
         ctx.mtile_group.data_ptr(), ctx.mtile_row0.data_ptr(), ctx.num_mtiles.data_ptr(),
         ctx.row_src_rank.data_ptr(), ctx.row_src_pos.data_ptr(), ctx.status.data_ptr(), stream),
         "mm_route_finalize")
+    timer.__exit__()
     N.count_launches(5)  # histogram, scan, scatter, offsets, row tables
 
 
