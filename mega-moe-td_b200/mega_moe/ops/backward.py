@@ -167,6 +167,8 @@ class MegaMoEBackwardFunction(torch.autograd.Function):
             out, saved = op.forward(
                 hidden_states, selected_experts.to(torch.int32).contiguous(), gate_up, fc2,
                 routing_weights.float().contiguous(), return_saved=True)
+        saved = dict(saved)
+        saved["output"] = None   # see MegaMoEFunction.forward: avoids a node <-> output cycle
         ctx.saved = saved
         ctx.peer_mem = peer_mem
         ctx.rw_dtype = routing_weights.dtype

@@ -38,6 +38,11 @@ class MegaMoEFunction(torch.autograd.Function):
                 routing_weights,
                 return_saved=True,
             )
+        # The output tensor becomes the autograd node's own result: keeping it inside the
+        # node's saved dict would close a reference cycle (node -> saved -> output -> node)
+        # that only the cyclic garbage collector could free, pinning every step's activations.
+        saved = dict(saved)
+        saved["output"] = None
         ctx.op = op
         ctx.saved = saved
         ctx.peer_mem = peer_mem
