@@ -129,9 +129,12 @@ def main():
     except ValueError as exc:
         raised = "peer buffer capacity" in str(exc)
     check("capacity overflow raises", raised)
-    out = op(inp["hidden"][rank].to(dev), inp["selected"][rank].to(dev), gate_up,
+    # perfectly balanced routes fill every rank's buffer exactly to its capacity
+    balanced = [((torch.arange(tokens * top_k) + r) % experts).to(torch.int32).view(tokens, top_k)
+                for r in range(world)]
+    out = op(inp["hidden"][rank].to(dev), balanced[rank].to(dev), gate_up,
              inp["w_down"][rank].to(dev), inp["routing_weights"][rank].to(dev))
-    want_out = O.forward_golden(inp["hidden"], inp["routing_weights"], inp["selected"],
+    want_out = O.forward_golden(inp["hidden"], inp["routing_weights"], balanced,
                                 inp["w_gate"], inp["w_up"], inp["w_down"], experts)[rank]
     torch.testing.assert_close(out.cpu().float(), want_out.float(), rtol=O.OUTPUT_RTOL,
                                atol=O.OUTPUT_ATOL)
