@@ -96,6 +96,19 @@ int mm_route_local(const int32_t* selected, int num_routes, int top_k, int num_e
                    int32_t* route_to_send, int32_t* count_row, int32_t* local_stats, void* scratch,
                    size_t scratch_bytes, cudaStream_t stream);
 
+/* Same work and outputs as mm_route_local for callers that cannot allocate device memory
+ * (a server with a frozen memory pool, a plugin that owns no allocator): the scratch lives
+ * in a 1 MiB array inside the library's device image instead of being passed in.  No
+ * counterpart in the reference, whose callers always allocate through the framework.
+ * Returns MM_ERR_LIMIT when mm_route_scratch_bytes(num_routes, bins) exceeds 1 MiB.  The first
+ * call on a device resolves the array's address; make it before any stream capture.  Calls
+ * on one device share the array, so calls that may overlap on the GPU must be ordered.  The
+ * call itself allocates nothing. */
+int mm_route_local_static(const int32_t* selected, int num_routes, int top_k, int num_experts,
+                          int bins, int32_t* send_route, int32_t* send_token,
+                          int32_t* send_bucket, int32_t* route_to_send, int32_t* count_row,
+                          int32_t* local_stats, cudaStream_t stream);
+
 /* Offsets from the replicated count cube [world, bins]
  * (reference: runtime/routing.py:93-140,318-416; kernels/fused_forward.py:241-304,337-358,
  * 450-480).  Also builds the 128-row tile table of the grouped GEMMs (the counterpart of

@@ -8,6 +8,8 @@
 //   3. every block revisits its chunk in order and ranks each route among the equal
 //      keys that precede it (warp match + per-warp counts), so ties keep ascending
 //      route order exactly like a stable sort.
+#include <mutex>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -457,6 +459,77 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
                                                       pull_dst_start, world, epr, capacity_rows,
                                                       row_src_rank, row_src_pos);
   return check_launch("route_row_tables_kernel");
+}
+
+// ---------------------------------------------------------------------------------------
+// mm_route_local_static: mm_route_local for callers that may not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc (or any allocating routine) on their
+// hot path: an inference server whose memory pool was sized and frozen at start-up, code
+// running under a memory budget that forbids growth after initialisation, or a plugin that
+// is handed input and output buffers but owns no allocator.  mm_route_local needs a scratch
+// buffer from its caller; this variant instead works in a fixed array that lives in the
+// library's own device image, so the caller passes only inputs and outputs.
+//
+//  * The array is kRouteStaticScratchBytes (1 MiB) per GPU that loads the library, held
+//    until the process exits.  Requests whose scratch need (mm_route_scratch_bytes) exceeds it
+//    are rejected with MM_ERR_LIMIT; 1 MiB covers 262 144 routes at 1024 bins.
+//  * The first call on each device looks the array's device address up
+//    (cudaGetSymbolAddress, with that device current) and caches it; make that first call
+//    outside any stream capture.  Later calls on the device do no set-up.
+//  * Nothing in the array has to start at zero: every word a call reads was written earlier
+//    by the same call (the histogram pass writes all per-block counts, the scan pass all
+//    bucket starts), so stale contents of a previous call are never observed.
+//  * All calls on one device share the array.  Two calls whose kernels may overlap on the GPU
+//    (different streams without an ordering between them) race; order them.
+// ---------------------------------------------------------------------------------------
+namespace {
+constexpr size_t kRouteStaticScratchBytes = 1u << 20;
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_route_static_scratch[kRouteStaticScratchBytes];
+void* g_route_static_ptr[kMaxDevices] = {};
+std::mutex g_route_static_mutex;
+}  // namespace
+
+int mm_route_local_static(const int32_t* selected, int num_routes, int top_k, int num_experts,
+                          int bins, int32_t* send_route, int32_t* send_token,
+                          int32_t* send_bucket, int32_t* route_to_send, int32_t* count_row,
+                          int32_t* local_stats, cudaStream_t stream) {
+  if (num_routes < 0 || bins <= 0) {
+    set_error("mm_route_local_static: bad sizes (routes=%d bins=%d)", num_routes, bins);
+    return MM_ERR_ARG;
+  }
+  const size_t need = mm_route_scratch_bytes(num_routes, bins);
+  if (need > kRouteStaticScratchBytes) {
+    set_error("mm_route_local_static: %d routes at %d bins need %zu bytes of scratch, the built-in "
+              "array holds %zu; use mm_route_local with caller-provided scratch",
+              num_routes, bins, need, kRouteStaticScratchBytes);
+    return MM_ERR_LIMIT;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error("mm_route_local_static: cudaGetDevice: %s (device %d)", cudaGetErrorString(e), dev);
+    return MM_ERR_CUDA;
+  }
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_route_static_mutex);
+    if (g_route_static_ptr[dev] == nullptr) {
+      // The array's name is only a host-side handle: kernels need its device address.
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_route_static_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        set_error("mm_route_local_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        return MM_ERR_CUDA;
+      }
+      g_route_static_ptr[dev] = p;
+    }
+    scratch = g_route_static_ptr[dev];
+  }
+  return mm_route_local(selected, num_routes, top_k, num_experts, bins, send_route, send_token,
+                        send_bucket, route_to_send, count_row, local_stats, scratch,
+                        kRouteStaticScratchBytes, stream);
 }
 
 }  // extern "C"

@@ -52,6 +52,8 @@ SIGNATURES = {
     "mm_route_scratch_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "mm_route_local": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, _c_i32p, _c_i32p,
                                  _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_ptr, C.c_size_t, _c_ptr]),
+    "mm_route_local_static": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, _c_i32p,
+                                        _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_ptr]),
     "mm_route_finalize": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int] +
                           [_c_i32p] * 13 + [_c_ptr, _c_ptr]),
     "mm_dispatch_rows": (C.c_int, [_c_ptr, C.c_int, _c_ptr, _c_i32p, _c_i32p, _c_i32p, _c_i32p,
