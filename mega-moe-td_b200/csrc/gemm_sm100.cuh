@@ -91,11 +91,20 @@ __device__ __forceinline__ int32_t total_tiles(const GemmParams& p) {
 __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int32_t t, int32_t nmt) {
   TileInfo ti;
   if (p.kind == kGroupedRows) {
-    const int32_t nt = t / nmt;
-    const int32_t mt = t - nt * nmt;
-    ti.group = p.mtile_group[mt];
-    ti.row0 = p.mtile_row0[mt];
+    // Group-major order: all tiles of one expert are consecutive (n-tile outer, 128-row tile
+    // inner), so the CTAs running at the same time share one expert's rows and weights in L2.
+    // Tile t lies in the group of 128-row tile t / n_tiles because group g owns the tile
+    // range [first_g * n_tiles, (first_g + cnt_g) * n_tiles).
+    const int32_t u = t / p.n_tiles;
+    ti.group = p.mtile_group[u];
+    const int32_t g0 = p.group_offs[ti.group];
     const int32_t end = p.group_offs[ti.group + 1];
+    const int32_t first = u - ((p.mtile_row0[u] - g0) >> 7);
+    const int32_t cnt = (end - g0 + kBlockM - 1) >> 7;
+    const int32_t local = t - first * p.n_tiles;
+    const int32_t nt = local / cnt;
+    const int32_t mj = local - nt * cnt;
+    ti.row0 = g0 + mj * kBlockM;
     ti.rows_valid = min(kBlockM, end - ti.row0);
     ti.n0 = nt * (p.epi == kEpiSwiglu ? kBlockN / 2 : kBlockN);
     ti.num_kb = (p.K + kBlockK - 1) / kBlockK;
