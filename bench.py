@@ -192,6 +192,9 @@ def run_ours(args, w, name):
                                   num_experts=E, config=cfg)
     # expert-weight gradients land in buffers allocated once (the work per step is unchanged)
     op.persistent_weight_grads = True
+    # no host synchronisation inside a step; saved activations are views of fixed buffers
+    op.host_sync_free = True
+    op.saved_views = True
     x, dy, rw, sel, gate_up, down = make_device_inputs(w, rank, world, device)
     x.requires_grad_(True)
     rw.requires_grad_(True)

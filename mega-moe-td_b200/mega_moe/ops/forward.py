@@ -156,6 +156,21 @@ class FusedMoEForward(torch.nn.Module):
         # workspace of the reference (ops/forward.py:246-282).  Off by default.
         self.persistent_weight_grads = False
         self._grad_ws = None
+        # When True, `forward` never waits for the device: the receive-capacity check is
+        # deferred (an overflow raises ValueError from the next call, `sync()` or
+        # `finalize()` instead of from the call that overflowed), and the saved dict carries
+        # capacity-sized activation buffers with the row counts left on the device
+        # (`saved["M"]`, `total_recv`, `total_send` are None).  The default (False) keeps the
+        # reference's behaviour: immediate ValueError and exact-size saved tensors, at the
+        # price of host synchronisations inside every call.
+        self.host_sync_free = False
+        # When True, `saved["fc1_output"]` / `saved["swiglu_out_weighted"]` are views of this
+        # operator's fixed buffers instead of copies (valid until its next forward), like the
+        # reference's fixed-address saved workspace (ops/forward.py:246-282).
+        self.saved_views = False
+        self._pending_check = []
+        self._host_stats_ring = [torch.zeros(2, dtype=torch.int32).pin_memory() for _ in range(8)]
+        self._host_stats_next = 0
 
         # All ranks must observe zeroed symmetric buffers before first use.
         torch.cuda.synchronize()
@@ -183,13 +198,44 @@ class FusedMoEForward(torch.nn.Module):
             }
         return self._grad_ws
 
+    def _check_pending_capacity(self, wait: bool) -> None:
+        """Raise the deferred receive-capacity error of an earlier sync-free forward."""
+        while self._pending_check:
+            host_stats, event = self._pending_check[0]
+            if wait:
+                event.synchronize()
+            elif not event.query():
+                return
+            self._pending_check.pop(0)
+            required = int(host_stats[1])
+            if (self.receive_capacity_factor < self.world_size
+                    and required > self.context.max_received_routes):
+                self._pending_check.clear()
+                self.context.reset_status()
+                raise ValueError(
+                    f"peer buffer capacity {self.context.max_received_routes} routes is "
+                    f"smaller than the required receive size {required}")
+
+    def _defer_capacity_check(self) -> None:
+        """Queue an asynchronous copy of {M, max required rows} for a later host-side check."""
+        if len(self._pending_check) >= len(self._host_stats_ring):
+            self._check_pending_capacity(wait=True)
+        slot = self._host_stats_ring[self._host_stats_next % len(self._host_stats_ring)]
+        self._host_stats_next += 1
+        slot.copy_(self.context.metadata_stats[:2], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._pending_check.append((slot, event))
+
     def sync(self):
         torch.cuda.synchronize()
+        self._check_pending_capacity(wait=True)
 
     def finalize(self):
         """Drain the device, then release the symmetric block and all workspaces."""
         if self.context.peer_mem is not None:
             torch.cuda.synchronize(self.context.peer_mem.device)
+        self._pending_check = []
         if self.world_size > 1 and self.context.symm is not None:
             torch.distributed.barrier(group=self.ep_group)
         self._act_buf = None
@@ -403,6 +449,7 @@ class FusedMoEForward(torch.nn.Module):
             raise ValueError("expert FFN size must be a multiple of 128")
 
         ctx = self.context
+        self._check_pending_capacity(wait=False)
         tokens = hidden_states.shape[0]
         num_routes = tokens * self.top_k
         hidden = self.hidden_size
@@ -433,15 +480,24 @@ class FusedMoEForward(torch.nn.Module):
         L.grouped_gemm_scatter(ctx, fc2_desc, "combine_mem", hidden, name="fc2_combine")
         ctx.rank_barrier()
         L.topk_reduce(ctx.combine_mem, ctx.route_to_send, tokens, self.top_k, hidden, out)
-        check_receive_capacity(ctx)
+        if self.host_sync_free:
+            self._defer_capacity_check()
+        else:
+            check_receive_capacity(ctx)
         if not return_saved:
             return out
 
         plan = snapshot_plan(ctx)
-        num_received_routes = int(ctx.metadata_stats[0].item())
-        num_sent_routes = int(ctx.metadata_local_stats[0].item())
-        m = num_received_routes
-        fc1_output = self._fc1_buf[:m].clone()
+        if self.host_sync_free:
+            num_received_routes = num_sent_routes = None
+            m = cap
+            sent = num_routes
+        else:
+            num_received_routes = int(ctx.metadata_stats[0].item())
+            num_sent_routes = int(ctx.metadata_local_stats[0].item())
+            m = num_received_routes
+            sent = num_sent_routes
+        fc1_output = self._fc1_buf[:m] if self.saved_views else self._fc1_buf[:m].clone()
         saved = {
             # minimal contract of the reference's single-launch forward
             # (ops/forward.py:1813-1873)
@@ -452,8 +508,8 @@ class FusedMoEForward(torch.nn.Module):
             "routing_weights": routing_weights,
             "recv_expert_offsets": plan.metadata_recv_expert_offs,
             "recv_counts_by_source_expert": plan.metadata_recv_counts_re,
-            "send_token_indices": plan.send_token_indices[:num_sent_routes],
-            "send_route_indices": plan.send_route_indices[:num_sent_routes],
+            "send_token_indices": plan.send_token_indices[:sent],
+            "send_route_indices": plan.send_route_indices[:sent],
             "total_send": num_sent_routes,
             "total_recv": m,
             "M": m,
@@ -463,7 +519,8 @@ class FusedMoEForward(torch.nn.Module):
             # activation section and scalars of the full backward contract
             # (ops/_torch_forward.py:294-320)
             "recv_hidden_sorted": recv_copy[:m],
-            "swiglu_out_weighted": self._act_buf[:m].clone(),
+            "swiglu_out_weighted": (self._act_buf[:m] if self.saved_views
+                                    else self._act_buf[:m].clone()),
             "gate": fc1_output[:, :ffn_size],
             "up": fc1_output[:, ffn_size:],
             "expert_counts": plan.metadata_recv_per_expert,

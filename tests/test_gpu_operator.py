@@ -269,3 +269,40 @@ def test_validation_errors_and_capacity_overflow():
         op.finalize()
     # World size 1 always fits its own routes (factor 1.0 == world size), so overflow is
     # exercised at the C ABI level in test_gpu_kernels.py::test_routing_capacity_overflow_sets_status.
+
+
+def test_host_sync_free_mode_matches_and_defers_capacity_error():
+    """host_sync_free + saved_views: same results without host waits inside the call."""
+    import mega_moe
+    tokens, hidden, ffn, experts, top_k = 384, 256, 256, 8, 2
+    inp = O.make_inputs(1, tokens, hidden, ffn, experts, top_k, seed=21, weight_std=0.05)
+    want_out = O.forward_golden(inp["hidden"], inp["routing_weights"], inp["selected"],
+                                inp["w_gate"], inp["w_up"], inp["w_down"], experts)[0]
+    _, saved = O.forward_saved(inp["hidden"], inp["routing_weights"], inp["selected"],
+                               inp["w_gate"], inp["w_up"], inp["w_down"], top_k)
+    want = O.backward(saved, inp["dy"])[0]
+    op = _make_op(tokens, hidden, top_k, experts)
+    op.host_sync_free = True
+    op.saved_views = True
+    op.persistent_weight_grads = True
+    try:
+        for _ in range(3):  # repeated steps reuse every workspace
+            x = inp["hidden"][0].to(DEV).requires_grad_(True)
+            rw = inp["routing_weights"][0].to(DEV).requires_grad_(True)
+            gate_up = mega_moe.pack_gate_up_weights(
+                inp["w_gate"][0].to(DEV), inp["w_up"][0].to(DEV)).requires_grad_(True)
+            down = inp["w_down"][0].to(DEV).requires_grad_(True)
+            out = mega_moe.MegaMoEFunction.apply(op, x, rw, inp["selected"][0].to(DEV), gate_up,
+                                                 down, op.context.peer_mem, None)
+            gx, grw, ggu, gd = torch.autograd.grad(out, [x, rw, gate_up, down],
+                                                   inp["dy"][0].to(DEV))
+            _check_out(out.detach(), want_out)
+            _check_grad("grad_hidden", gx, want["grad_hidden"])
+            _check_grad("grad_routing_weights", grw, want["grad_routing_weights"])
+            _check_grad("grad_down", gd, want["grad_fc2"])
+            _check_grad("grad_gate_up", ggu, torch.cat(
+                (want["grad_fc1_1"], want["grad_fc1_2"]), dim=1).transpose(1, 2))
+        op.sync()
+        assert op.context.read_status().code == 0
+    finally:
+        op.finalize()
