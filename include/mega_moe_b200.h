@@ -73,9 +73,11 @@ int mm_symm_free(void* dptr);
 /* Cross-rank barrier through flag words in symmetric memory: writes `epoch` into slot
  * [rank] of every peer's flag array, then waits (bounded) until all `world` slots of the
  * local array hold a value >= epoch.  peer_flags: device array of `world` pointers.
+ * phase 0 does both halves; phase 1 only signals and phase 2 only waits, so that work which
+ * touches no peer-written memory can run between the two.
  * Stands in for libshmem_device.barrier_all_vec() (runtime/routing.py:91,142). */
-int mm_rank_barrier(int32_t* const* peer_flags, int rank, int world, int epoch, void* status,
-                    cudaStream_t stream);
+int mm_rank_barrier(int32_t* const* peer_flags, int rank, int world, int epoch, int phase,
+                    void* status, cudaStream_t stream);
 
 /* ---- routing metadata --------------------------------------------------------- */
 /* Scratch bytes mm_route_local needs for `num_routes` routes and `bins` count bins. */

@@ -2,6 +2,8 @@
 // four C-ABI entry points that use it (declared in include/mega_moe_b200.h).
 #include <cudaTypedefs.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "gemm_sm100.cuh"
@@ -202,6 +204,10 @@ int mm_grouped_gemm_scatter(const mm_gemm_desc* d, const int32_t* row_dst_rank,
   p.row_dst_pos = row_dst_pos;
   p.peer_bases = reinterpret_cast<__nv_bfloat16* const*>(peer_bases);
   p.ld_dst = ld_dst;
+  {
+    const char* env = getenv("MM_SCATTER_WIDE");
+    p.wide_store = (env == nullptr || env[0] != '0') ? 1 : 0;
+  }
   return grouped_rows_gemm(kEpiScatter, *d, p, stream);
 }
 

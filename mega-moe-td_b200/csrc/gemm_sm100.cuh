@@ -51,6 +51,7 @@ struct GemmParams {
   int32_t m_tiles;       // kGroupedReduce: tiles along m'
   int32_t swiglu_F;      // column offset of the "up" half inside B and inside out2
   int32_t tma_store;     // kGroupedReduce: output tiles leave through TMA tensor stores
+  int32_t wide_store;    // row stores in 256-byte pieces (scatter over NVLink)
   int32_t act;
   float act_beta;
   float act_linear_beta; // <= 0: no transform on up
@@ -182,6 +183,37 @@ __device__ __forceinline__ void flush_rows(const uint8_t* stg, uint32_t lane, ui
     const uint64_t pr = __shfl_sync(0xffffffffu, (unsigned long long)row_ptr, r);
     const int ok = __shfl_sync(0xffffffffu, valid, r);
     if (ok && col_ok) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pr) + c * 16) = q;
+  }
+}
+
+// Wide variant: the warp's whole 8 KB staging area holds 32 rows x 256 bytes (128 columns),
+// chunk cc of row r at r * 256 + ((cc ^ (r & 15)) << 4); a warp instruction then writes
+// 2 rows x 256 contiguous bytes, which suits stores that cross NVLink.
+__device__ __forceinline__ void stage_row_f32_wide(uint8_t* stg, uint32_t lane, int half,
+                                                   const uint32_t (&r)[64]) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 q;
+    q.x = pack_bf16x2(__uint_as_float(r[8 * c + 0]), __uint_as_float(r[8 * c + 1]));
+    q.y = pack_bf16x2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3]));
+    q.z = pack_bf16x2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5]));
+    q.w = pack_bf16x2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]));
+    const uint32_t cc = (uint32_t)(half * 8 + c);
+    *reinterpret_cast<uint4*>(stg + lane * 256 + ((cc ^ (lane & 15)) << 4)) = q;
+  }
+}
+
+__device__ __forceinline__ void flush_rows_wide(const uint8_t* stg, uint32_t lane,
+                                                uint8_t* row_ptr, int valid, int cols_valid) {
+  const uint32_t cc = lane & 15;
+  const bool col_ok = (int)(cc * 8) < cols_valid;
+#pragma unroll
+  for (int it = 0; it < 16; ++it) {
+    const uint32_t r = it * 2 + (lane >> 4);
+    const uint4 q = *reinterpret_cast<const uint4*>(stg + r * 256 + ((cc ^ (r & 15)) << 4));
+    const uint64_t pr = __shfl_sync(0xffffffffu, (unsigned long long)row_ptr, r);
+    const int ok = __shfl_sync(0xffffffffu, valid, r);
+    if (ok && col_ok) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pr) + cc * 16) = q;
   }
 }
 
@@ -477,22 +509,45 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int nch = min(kBlockN / 64, (cols_left + 63) / 64);
         uint32_t ra[64];
         if (!zero_tile && nch > 0) tmem_ld_32x64(t_acc, ra);
+        if (p.wide_store) {
 #pragma unroll 1
-        for (int c = 0; c < nch; ++c) {
-          uint8_t* sb = stg + buf * 4096;
-          if (!zero_tile) {
-            tmem_ld_wait_regs(ra);
-            stage_row_f32(sb, lane, ra);
-            // the next block's TMEM load overlaps the stores of this one
-            if (c + 1 < nch) tmem_ld_32x64(t_acc + (c + 1) * 64, ra);
-          } else {
+          for (int c = 0; c < nch; c += 2) {
+            if (!zero_tile) {
+              tmem_ld_wait_regs(ra);
+              stage_row_f32_wide(stg, lane, 0, ra);
+              if (c + 1 < nch) {
+                tmem_ld_32x64(t_acc + (c + 1) * 64, ra);
+                tmem_ld_wait_regs(ra);
+                stage_row_f32_wide(stg, lane, 1, ra);
+              }
+              if (c + 2 < nch) tmem_ld_32x64(t_acc + (c + 2) * 64, ra);
+            } else {
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-              *reinterpret_cast<uint4*>(sb + lane * 128 + k * 16) = make_uint4(0, 0, 0, 0);
+              for (int k = 0; k < 16; ++k)
+                *reinterpret_cast<uint4*>(stg + lane * 256 + k * 16) = make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();
+            flush_rows_wide(stg, lane, row_ptr + c * 128, valid, cols_left - c * 64);
+            __syncwarp();
           }
-          __syncwarp();
-          flush_rows(sb, lane, row_ptr + c * 128, valid, cols_left - c * 64);
-          buf ^= 1;
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < nch; ++c) {
+            uint8_t* sb = stg + buf * 4096;
+            if (!zero_tile) {
+              tmem_ld_wait_regs(ra);
+              stage_row_f32(sb, lane, ra);
+              // the next block's TMEM load overlaps the stores of this one
+              if (c + 1 < nch) tmem_ld_32x64(t_acc + (c + 1) * 64, ra);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 8; ++k)
+                *reinterpret_cast<uint4*>(sb + lane * 128 + k * 16) = make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();
+            flush_rows(sb, lane, row_ptr + c * 128, valid, cols_left - c * 64);
+            buf ^= 1;
+          }
         }
       }
       tc_fence_before_sync();

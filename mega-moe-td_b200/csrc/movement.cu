@@ -200,14 +200,17 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ grad_act, int64_t ld_ga,
 // Cross-rank barrier through flag words in symmetric memory.
 // ---------------------------------------------------------------------------------
 __global__ void rank_barrier_kernel(int32_t* const* __restrict__ peer_flags, int rank, int world,
-                                    int epoch, StatusRecord* status) {
+                                    int epoch, int phase, StatusRecord* status) {
   const int s = threadIdx.x;
   if (s >= world) return;
-  // Make every earlier store of this GPU (issued by preceding kernels of the stream)
-  // visible system-wide before the flag that announces them.
-  __threadfence_system();
-  int32_t* remote = peer_flags[s] + rank;
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  if (phase != 2) {
+    // Make every earlier store of this GPU (issued by preceding kernels of the stream)
+    // visible system-wide before the flag that announces them.
+    __threadfence_system();
+    int32_t* remote = peer_flags[s] + rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  }
+  if (phase == 1) return;
   const int32_t* mine = peer_flags[rank] + s;
   const uint64_t t0 = globaltimer_ns();
   int32_t seen;
@@ -305,14 +308,15 @@ int mm_swiglu_bwd(const void* grad_act, int64_t ld_ga, const void* fc1_out, int6
   return check_launch("swiglu_bwd_kernel");
 }
 
-int mm_rank_barrier(int32_t* const* peer_flags, int rank, int world, int epoch, void* status,
-                    cudaStream_t stream) {
-  if (!peer_flags || world <= 0 || world > 1024 || rank < 0 || rank >= world) {
+int mm_rank_barrier(int32_t* const* peer_flags, int rank, int world, int epoch, int phase,
+                    void* status, cudaStream_t stream) {
+  if (!peer_flags || world <= 0 || world > 1024 || rank < 0 || rank >= world || phase < 0 ||
+      phase > 2) {
     set_error("mm_rank_barrier: bad arguments");
     return MM_ERR_ARG;
   }
   rank_barrier_kernel<<<1, ((world + 31) / 32) * 32, 0, stream>>>(
-      peer_flags, rank, world, epoch, reinterpret_cast<StatusRecord*>(status));
+      peer_flags, rank, world, epoch, phase, reinterpret_cast<StatusRecord*>(status));
   return check_launch("rank_barrier_kernel");
 }
 

@@ -48,7 +48,7 @@ SIGNATURES = {
     "mm_symm_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "mm_symm_close": (C.c_int, [_c_ptr]),
     "mm_symm_free": (C.c_int, [_c_ptr]),
-    "mm_rank_barrier": (C.c_int, [_c_ptr, C.c_int, C.c_int, C.c_int, _c_ptr, _c_ptr]),
+    "mm_rank_barrier": (C.c_int, [_c_ptr, C.c_int, C.c_int, C.c_int, C.c_int, _c_ptr, _c_ptr]),
     "mm_route_scratch_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "mm_route_local": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, _c_i32p, _c_i32p,
                                  _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_ptr, C.c_size_t, _c_ptr]),

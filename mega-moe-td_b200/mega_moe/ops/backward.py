@@ -113,6 +113,16 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
                      saved.get("activation", "swiglu") or "swiglu", saved.get("situ_beta"),
                      saved.get("situ_linear_beta"), saved.get("clamp_limit"), plan=plan)
 
+    # ---- stage 4: FC1 input gradient -> source ranks, then gather-sum -------------------
+    if m > 0:
+        desc = L.make_desc(ctx, grad_fc1_output, m, 2 * ffn, fc1_combined, k_dim=1, n_dim=2,
+                           n_out=hidden, k_extent=2 * ffn, **tiles)
+        L.grouped_gemm_scatter(ctx, desc, "combine_mem", hidden, plan=plan, name="fc1_dgrad_combine")
+    # Peers may read what this rank stored as soon as it has signalled; the FC1 weight
+    # gradient touches no peer-written memory, so it runs between the signal and the wait
+    # and absorbs the ranks' skew.
+    ctx.rank_signal()
+
     # ---- stage 5: FC1 weight gradient -------------------------------------------------
     if m > 0:
         grad_fc1 = (grad_ws["grad_fc1"] if grad_ws is not None
@@ -122,12 +132,7 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     else:
         grad_fc1 = torch.zeros(epr, 2 * ffn, hidden, dtype=dtype, device=device)
 
-    # ---- stage 4: FC1 input gradient -> source ranks, then gather-sum -------------------
-    if m > 0:
-        desc = L.make_desc(ctx, grad_fc1_output, m, 2 * ffn, fc1_combined, k_dim=1, n_dim=2,
-                           n_out=hidden, k_extent=2 * ffn, **tiles)
-        L.grouped_gemm_scatter(ctx, desc, "combine_mem", hidden, plan=plan, name="fc1_dgrad_combine")
-    ctx.rank_barrier()
+    ctx.rank_wait()
     grad_hidden = torch.empty(tokens, hidden, dtype=dtype, device=device)
     grad_routing_weights = torch.empty(tokens, top_k, dtype=dtype, device=device)
     L.topk_reduce(ctx.combine_mem, plan.route_to_send, tokens, top_k, hidden, grad_hidden,

@@ -146,17 +146,36 @@ class MoEForwardContext:
     _extra: dict = field(default_factory=dict)
 
     # ---- device helpers -------------------------------------------------------------
+    def _barrier(self, phase: int) -> None:
+        N.check(N.lib().mm_rank_barrier(
+            self.symm.peer_table("flags").data_ptr(), self.rank, self.world_size,
+            self.barrier_epoch, phase, self.status.data_ptr(), N.stream_ptr()), "mm_rank_barrier")
+        N.count_launches(1)
+
+    def _next_epoch(self) -> None:
+        self.barrier_epoch += 1
+        if self.barrier_epoch >= 2**31 - 1:
+            raise RuntimeError("barrier epoch exhausted; recreate the operator")
+
     def rank_barrier(self) -> None:
         """All ranks' earlier stores into this rank's symmetric memory are visible after it."""
         if self.world_size == 1:
             return
-        self.barrier_epoch += 1
-        if self.barrier_epoch >= 2**31 - 1:
-            raise RuntimeError("barrier epoch exhausted; recreate the operator")
-        N.check(N.lib().mm_rank_barrier(
-            self.symm.peer_table("flags").data_ptr(), self.rank, self.world_size,
-            self.barrier_epoch, self.status.data_ptr(), N.stream_ptr()), "mm_rank_barrier")
-        N.count_launches(1)
+        self._next_epoch()
+        self._barrier(0)
+
+    def rank_signal(self) -> None:
+        """First half of a barrier: announce that this rank's earlier stores are done."""
+        if self.world_size == 1:
+            return
+        self._next_epoch()
+        self._barrier(1)
+
+    def rank_wait(self) -> None:
+        """Second half: wait until every rank has announced the epoch of `rank_signal`."""
+        if self.world_size == 1:
+            return
+        self._barrier(2)
 
     def read_status(self) -> N.StatusRecord:
         rec = N.StatusRecord()
