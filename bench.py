@@ -235,15 +235,45 @@ def run_ours(args, w, name):
     def resident_step():
         step(x, rw, sel, dy)
 
+    # End-to-end step: this step's inputs come from pinned host memory and its results go back
+    # to pinned host memory, every step.  Copies run on their own streams so that the upload
+    # of step i+1 and the download of step i-1 overlap the kernels of step i, as an input
+    # pipeline of a training loop would.
+    copy_in = torch.cuda.Stream(device)
+    copy_out = torch.cuda.Stream(device)
+    staged = []
+
+    def stage_inputs():
+        with torch.cuda.stream(copy_in):
+            tensors = (host["x"].to(device, non_blocking=True),
+                       host["rw"].to(device, non_blocking=True),
+                       host["sel"].to(device, non_blocking=True),
+                       host["dy"].to(device, non_blocking=True))
+            ev = torch.cuda.Event()
+            ev.record(copy_in)
+        staged.append((tensors, ev))
+
     def e2e_step():
-        xx = host["x"].to(device, non_blocking=True).requires_grad_(True)
-        rr = host["rw"].to(device, non_blocking=True).requires_grad_(True)
-        ss = host["sel"].to(device, non_blocking=True)
-        dd = host["dy"].to(device, non_blocking=True)
+        main = torch.cuda.current_stream(device)
+        if not staged:
+            stage_inputs()
+        (xx, rr, ss, dd), ev = staged.pop(0)
+        main.wait_event(ev)
+        for t in (xx, rr, ss, dd):
+            t.record_stream(main)
+        stage_inputs()
+        xx.requires_grad_(True)
+        rr.requires_grad_(True)
         out, grads = step(xx, rr, ss, dd)
-        host_out.copy_(out.detach(), non_blocking=True)
-        host_gh.copy_(grads[0], non_blocking=True)
-        host_grw.copy_(grads[1], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(done)
+            host_out.copy_(out.detach(), non_blocking=True)
+            host_gh.copy_(grads[0], non_blocking=True)
+            host_grw.copy_(grads[1], non_blocking=True)
+        for t in (out, grads[0], grads[1]):
+            t.record_stream(copy_out)
 
     for _ in range(args.warmup):
         resident_step()

@@ -122,6 +122,9 @@ int mm_route_local_static(const int32_t* selected, int num_routes, int top_k, in
  *   stats [2 + world] = {M, max over destinations, per-destination totals}
  *   mtile_group / mtile_row0 [capacity_rows / 128 + epr]   num_mtiles [1]
  *   row_src_rank / row_src_pos [capacity_rows]
+ *   order_prefix [world * epr + 1]: prefix of the local counts in dispatch order (local expert
+ *     slot outermost, destination rank rotated by `rank`), bucket_done [world * epr]: zeroed
+ *     delivery counters; both feed mm_dispatch_desc
  * If M exceeds capacity_rows the status record gets code 2 and num_mtiles is 0. */
 int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, int bins,
                       int capacity_rows, int32_t* send_bucket_starts,
@@ -129,8 +132,8 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
                       int32_t* recv_per_expert, int32_t* recv_expert_offs,
                       int32_t* recv_seg_starts, int32_t* pull_dst_start, int32_t* stats,
                       int32_t* mtile_group, int32_t* mtile_row0, int32_t* num_mtiles,
-                      int32_t* row_src_rank, int32_t* row_src_pos, void* status,
-                      cudaStream_t stream);
+                      int32_t* row_src_rank, int32_t* row_src_pos, int32_t* order_prefix,
+                      int32_t* bucket_done, void* status, cudaStream_t stream);
 
 /* ---- dispatch / combine data movement ---------------------------------------------- */
 /* Push send row i (= src[send_token[i]]) to rank send_bucket[i] / epr at row
@@ -173,19 +176,46 @@ typedef struct mm_gemm_desc {
   void* status;
 } mm_gemm_desc;
 
+/* Optional fused dispatch of mm_fc1_swiglu / mm_grouped_gemm: two extra warps of every CTA push
+ * this rank's send rows (row i = src[send_token[i]]) into the owning ranks' receive buffers
+ * in dispatch order, flag each (source, expert) bucket as complete in the destination's
+ * `flags` array (st.release.sys of `epoch`), and the GEMM waits per expert until all `world`
+ * sources have flagged it instead of waiting for a rank barrier
+ * (reference: dispatch overlapped with FC1, kernels/dispatch_fc1.py:365-508 and
+ * kernels/fused_forward.py:483-534,1106-1158).  `epoch` must grow with every fused launch. */
+typedef struct mm_dispatch_desc {
+  const void* src;                    /* [tokens, hidden] bf16 rows to send */
+  const float* weights;               /* [tokens * top_k] fp32, sent alongside; may be null */
+  const int32_t* send_token;
+  const int32_t* send_route;
+  const int32_t* send_bucket_starts;
+  const int32_t* send_bucket_dst_starts;
+  const int32_t* count_row;           /* rows per bucket (local count row) */
+  const int32_t* order_prefix;        /* from mm_route_finalize */
+  const int32_t* local_stats;         /* [0] = number of send rows */
+  int32_t* bucket_done;               /* zeroed [world * epr] */
+  void* const* peer_rows;             /* device array of `world` receive-buffer bases */
+  float* const* peer_weights;         /* device array of `world` weight-buffer bases */
+  int32_t* const* peer_flags;         /* device array of `world` flag-array bases */
+  const int32_t* my_flags;            /* this rank's flag array [world * epr] */
+  int32_t hidden, rank, world, epr, capacity_rows, epoch;
+} mm_dispatch_desc;
+
 /* FC1 with the weighted gated activation fused in the epilogue
  * (reference: kernels/fused_forward.py:551-876).  b is the packed [E, H, 2F] table
  * (b_k_major = 0, b_cols_total = 2F, N = F).
  *   act_out [rows, F] = bf16(f(bf16(gate), bf16(up)) * row_weight)
- *   raw_out [rows, 2F] = bf16 gate | up (may be null) */
-int mm_fc1_swiglu(const mm_gemm_desc* d, void* act_out, int64_t ld_act, void* raw_out,
+ *   raw_out [rows, 2F] = bf16 gate | up (may be null)
+ *   dispatch: null for rows already resident in `a`, else the fused dispatch above */
+int mm_fc1_swiglu(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void* act_out, int64_t ld_act, void* raw_out,
                   int64_t ld_raw, const float* row_weight, int activation, float beta,
                   float linear_beta, float clamp_limit, cudaStream_t stream);
 
 /* out[rows of g, 0:N] = bf16(A[rows of g] * B_g)
  * (reference: kernels/dispatch_fc1.py:580-751 for FC1 without activation,
  *  kernels/dispatch_fc2_bwd.py:309-485 for the FC2 input gradient). */
-int mm_grouped_gemm(const mm_gemm_desc* d, void* out, int64_t ld_out, cudaStream_t stream);
+int mm_grouped_gemm(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void* out,
+                    int64_t ld_out, cudaStream_t stream);
 
 /* Same product, but each output row is stored into rank row_dst_rank[row]'s buffer at row
  * row_dst_pos[row] (reference: FC2 + return, kernels/fused_forward.py:1010-1025,1161-1279;

@@ -35,6 +35,7 @@ enum WaitSite : int32_t {
   kSiteTmemFull = 4,
   kSiteRankBarrier = 5,
   kSiteDrain = 6,
+  kSiteDispatchFlag = 7,
 };
 
 // Wall-clock budget of one device-side wait.
@@ -298,6 +299,28 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_bf16(int m, int n, int a
   d |= (uint32_t)(m >> 4) << 24;
   return d;
 }
+
+// Dispatch order: local expert slot outermost, destination rank rotated by the sender's rank,
+// so every destination sees its experts complete one after the other and no two senders
+// start on the same destination.
+__device__ __forceinline__ int32_t dispatch_order_bucket(int32_t q, int32_t rank, int32_t world,
+                                                         int32_t epr) {
+  const int32_t le = q / world;
+  const int32_t dd = q - le * world;
+  int32_t dst = rank + 1 + dd;
+  if (dst >= world) dst -= world;
+  return dst * epr + le;
+}
+
+struct TileInfo {
+  int32_t group;
+  int32_t row0;        // kGroupedRows: first A row; kGroupedReduce: first m' index
+  int32_t rows_valid;  // rows of the 128-row tile that carry output
+  int32_t n0;          // first output column (kEpiSwiglu: first F column)
+  int32_t num_kb;      // k-blocks of 64
+  int32_t krow0;       // kGroupedReduce: first reduction row
+  int32_t kcnt;        // kGroupedReduce: number of reduction rows
+};
 
 // ---------------------------------------------------------------------------
 // Small numeric helpers

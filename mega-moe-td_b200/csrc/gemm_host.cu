@@ -99,6 +99,39 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 // A rows [a_rows_cap, K] (K contiguous, leading dimension lda elements).
 // B per group: b_k_major != 0 -> [N_total, K] with K contiguous; else [K, N_total] with N contiguous.
+bool fill_dispatch(const mm_dispatch_desc* x, GemmParams& p) {
+  if (x == nullptr) return true;
+  if (!x->src || !x->send_token || !x->send_route || !x->send_bucket_starts ||
+      !x->send_bucket_dst_starts || !x->count_row || !x->order_prefix || !x->local_stats ||
+      !x->bucket_done || !x->peer_rows || !x->peer_flags || !x->my_flags ||
+      (x->weights && !x->peer_weights) || x->hidden <= 0 || (x->hidden % 8) || x->world <= 0 ||
+      x->rank < 0 || x->rank >= x->world || x->epr <= 0 || x->epoch <= 0) {
+    set_error("fused dispatch descriptor is incomplete or inconsistent");
+    return false;
+  }
+  p.disp_src = reinterpret_cast<const uint8_t*>(x->src);
+  p.disp_row_bytes = x->hidden * 2;
+  p.disp_rank = x->rank;
+  p.disp_world = x->world;
+  p.disp_epr = x->epr;
+  p.disp_capacity = x->capacity_rows;
+  p.disp_epoch = x->epoch;
+  p.disp_weights = x->weights;
+  p.disp_send_token = x->send_token;
+  p.disp_send_route = x->send_route;
+  p.disp_bucket_starts = x->send_bucket_starts;
+  p.disp_dst_starts = x->send_bucket_dst_starts;
+  p.disp_counts = x->count_row;
+  p.disp_order_prefix = x->order_prefix;
+  p.disp_num_send = x->local_stats;
+  p.disp_bucket_done = x->bucket_done;
+  p.disp_peer_rows = x->peer_rows;
+  p.disp_peer_weights = x->peer_weights;
+  p.disp_peer_flags = x->peer_flags;
+  p.disp_my_flags = x->my_flags;
+  return true;
+}
+
 int grouped_rows_gemm(int epi, const mm_gemm_desc& d, GemmParams p, cudaStream_t stream) {
   if (!aligned16(d.a) || !aligned16(d.b) || (d.lda % 8) || (d.b_ld % 8) || (d.b_group_stride % 8)) {
     set_error("grouped GEMM operands must be 16-byte aligned with strides that are multiples of 8");
@@ -161,7 +194,8 @@ using namespace mm;
 
 extern "C" {
 
-int mm_fc1_swiglu(const mm_gemm_desc* d, void* act_out, int64_t ld_act, void* raw_out,
+int mm_fc1_swiglu(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void* act_out,
+                  int64_t ld_act, void* raw_out,
                   int64_t ld_raw, const float* row_weight, int activation, float beta,
                   float linear_beta, float clamp_limit, cudaStream_t stream) {
   if (!d || !act_out || !row_weight) {
@@ -178,10 +212,12 @@ int mm_fc1_swiglu(const mm_gemm_desc* d, void* act_out, int64_t ld_act, void* ra
   p.act_beta = beta;
   p.act_linear_beta = linear_beta;
   p.act_clamp = clamp_limit;
+  if (!fill_dispatch(dispatch, p)) return MM_ERR_ARG;
   return grouped_rows_gemm(kEpiSwiglu, *d, p, stream);
 }
 
-int mm_grouped_gemm(const mm_gemm_desc* d, void* out, int64_t ld_out, cudaStream_t stream) {
+int mm_grouped_gemm(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void* out,
+                    int64_t ld_out, cudaStream_t stream) {
   if (!d || !out) {
     set_error("mm_grouped_gemm: null argument");
     return MM_ERR_ARG;
@@ -189,6 +225,7 @@ int mm_grouped_gemm(const mm_gemm_desc* d, void* out, int64_t ld_out, cudaStream
   GemmParams p{};
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.ld_out = ld_out;
+  if (!fill_dispatch(dispatch, p)) return MM_ERR_ARG;
   return grouped_rows_gemm(kEpiStore, *d, p, stream);
 }
 

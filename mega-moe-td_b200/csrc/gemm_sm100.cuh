@@ -29,7 +29,8 @@ constexpr int kStageBytes = kStageABytes + kStageBBytes;          // 48 KB
 constexpr int kBoxBytes = 64 * 64 * 2;                            // one 64x64 MN-major box
 constexpr int kEpiWarps = 4;
 constexpr int kStagingPerWarp = 2 * 32 * 128;                     // two 32-row x 128-byte buffers
-constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
+constexpr int kDispatchWarps = 2;                                  // row-push warps of a fused launch
+constexpr int kGemmThreads = 32 * (2 + kEpiWarps + kDispatchWarps);
 constexpr int kTmemCols = 512;
 constexpr int kGemmSmemBytes =
     kStages * kStageBytes + kEpiWarps * kStagingPerWarp + 256 /*barriers*/ + 1024 /*alignment*/;
@@ -72,16 +73,25 @@ struct GemmParams {
   __nv_bfloat16* const* peer_bases;  // kEpiScatter: base pointer of the destination buffer per rank
   int64_t ld_dst;
   StatusRecord* status;
-};
-
-struct TileInfo {
-  int32_t group;
-  int32_t row0;        // kGroupedRows: first A row; kGroupedReduce: first m' index
-  int32_t rows_valid;  // rows of the 128-row tile that carry output
-  int32_t n0;          // first output column (kEpiSwiglu: first F column)
-  int32_t num_kb;      // k-blocks of 64
-  int32_t krow0;       // kGroupedReduce: first reduction row
-  int32_t kcnt;        // kGroupedReduce: number of reduction rows
+  // ---- fused dispatch (FC1 and the FC2 input gradient): two extra warps per CTA push this
+  // rank's send rows into the owning ranks' receive buffers while the GEMM roles consume the
+  // experts whose rows have arrived.  disp_src == nullptr: plain GEMM on resident rows.
+  const uint8_t* disp_src;            // [tokens, row_bytes] rows to send
+  int32_t disp_row_bytes;
+  int32_t disp_rank, disp_world, disp_epr, disp_capacity, disp_epoch;
+  const float* disp_weights;          // per-route fp32 weight sent alongside, may be null
+  const int32_t* disp_send_token;     // send row -> token
+  const int32_t* disp_send_route;     // send row -> flat route
+  const int32_t* disp_bucket_starts;  // first send row of each bucket
+  const int32_t* disp_dst_starts;     // first destination row of each bucket
+  const int32_t* disp_counts;         // rows per bucket (local count row)
+  const int32_t* disp_order_prefix;   // [buckets + 1] prefix of the counts in dispatch order
+  const int32_t* disp_num_send;       // device scalar: number of send rows
+  int32_t* disp_bucket_done;          // [buckets] rows delivered so far (zeroed before launch)
+  void* const* disp_peer_rows;        // receive buffer base per rank
+  float* const* disp_peer_weights;    // routing-weight buffer base per rank
+  int32_t* const* disp_peer_flags;    // arrival flags base per rank: [world * epr] per rank
+  const int32_t* disp_my_flags;       // this rank's arrival flags
 };
 
 __device__ __forceinline__ int32_t total_tiles(const GemmParams& p) {
@@ -270,8 +280,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
+      int32_t ready_group = -1;
       for (int32_t t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
         const TileInfo ti = decode_tile(p, t, nmt);
+        if (p.disp_src != nullptr && ti.group != ready_group) {
+          // Rows of this expert are pushed by every rank's dispatch warps: wait (bounded)
+          // until each source has flagged its bucket complete for this launch's epoch.
+          const uint64_t t0 = globaltimer_ns();
+          for (int32_t src = 0; src < p.disp_world && alive; ++src) {
+            const int32_t* flag = p.disp_my_flags + src * p.disp_epr + ti.group;
+            uint32_t spins = 0;
+            while (true) {
+              int32_t seen;
+              asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+              if (seen >= p.disp_epoch) break;
+              if ((++spins & 0x3f) == 0) {
+                if (*abort_flag) { alive = false; break; }
+                if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+                  report_status(p.status, kWaitTimeout, kSiteDispatchFlag, src * p.disp_epr + ti.group,
+                                p.disp_epoch, seen);
+                  *abort_flag = 1;
+                  alive = false;
+                  break;
+                }
+              }
+            }
+          }
+          if (!alive) break;
+          // order the tensor-map (async proxy) reads after the flags just acquired
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          ready_group = ti.group;
+        }
         for (int kb = 0; kb < ti.num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kSiteSmemEmpty, stage)) {
             alive = false;
@@ -383,6 +422,99 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       __syncwarp();
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+    }
+  } else if (warp >= 2 + kEpiWarps) {
+    // ----------------------------- dispatch warps -----------------------------
+    if (p.disp_src != nullptr) {
+      const int32_t gid = blockIdx.x * kDispatchWarps + (int32_t)(warp - 2 - kEpiWarps);
+      const int32_t nd = gridDim.x * kDispatchWarps;
+      const int32_t nb = p.disp_world * p.disp_epr;
+      // buckets without rows are complete from the start
+      for (int32_t q = gid * 32 + (int32_t)lane; q < nb; q += nd * 32) {
+        const int32_t b = dispatch_order_bucket(q, p.disp_rank, p.disp_world, p.disp_epr);
+        if (p.disp_counts[b] == 0) {
+          int32_t* flag = p.disp_peer_flags[b / p.disp_epr] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch) : "memory");
+        }
+      }
+      const int32_t n_send = *p.disp_num_send;
+      const int32_t chunks = p.disp_row_bytes >> 4;
+      constexpr int kRowsPerFence = 4;   // rows pushed between two system-scope fences
+      constexpr int kBatch = 14;         // 16-byte loads in flight per lane
+      for (int32_t j0 = gid * kRowsPerFence; j0 < n_send; j0 += nd * kRowsPerFence) {
+        // Lanes 0..3 resolve one row each (their dependent table lookups overlap), then the
+        // warp copies the rows one after the other.
+        int32_t my_b = -1, my_dst = 0, my_row = 0, my_tok = 0;
+        float my_w = 0.0f;
+        if ((int32_t)lane < kRowsPerFence && j0 + (int32_t)lane < n_send) {
+          const int32_t j = j0 + (int32_t)lane;
+          // largest q with order_prefix[q] <= j (empty buckets share their successor's prefix)
+          int32_t lo = 0, hi = nb;
+          while (hi - lo > 1) {
+            const int32_t mid = (lo + hi) >> 1;
+            if (p.disp_order_prefix[mid] <= j) lo = mid; else hi = mid;
+          }
+          my_b = dispatch_order_bucket(lo, p.disp_rank, p.disp_world, p.disp_epr);
+          const int32_t in_bucket = j - p.disp_order_prefix[lo];
+          const int32_t i = p.disp_bucket_starts[my_b] + in_bucket;
+          my_dst = my_b / p.disp_epr;
+          my_row = p.disp_dst_starts[my_b] + in_bucket;
+          my_tok = p.disp_send_token[i];
+          if (p.disp_weights != nullptr) my_w = p.disp_weights[p.disp_send_route[i]];
+        }
+        int32_t bucket_of[kRowsPerFence];
+        int32_t dst_of[kRowsPerFence];
+#pragma unroll
+        for (int r = 0; r < kRowsPerFence; ++r) {
+          const int32_t b = __shfl_sync(0xffffffffu, my_b, r);
+          const int32_t dst_rank = __shfl_sync(0xffffffffu, my_dst, r);
+          const int32_t dst_row = __shfl_sync(0xffffffffu, my_row, r);
+          const int32_t tok = __shfl_sync(0xffffffffu, my_tok, r);
+          const float wgt = __shfl_sync(0xffffffffu, my_w, r);
+          bucket_of[r] = b;
+          dst_of[r] = dst_rank;
+          if (b < 0 || dst_row >= p.disp_capacity) continue;  // overflow: metadata kernel reports
+          const uint8_t* src = p.disp_src + (size_t)tok * p.disp_row_bytes;
+          uint8_t* dst = reinterpret_cast<uint8_t*>(p.disp_peer_rows[dst_rank]) +
+                         (size_t)dst_row * p.disp_row_bytes;
+          for (int32_t c0 = 0; c0 < chunks; c0 += 32 * kBatch) {
+            uint4 v[kBatch];
+#pragma unroll
+            for (int k = 0; k < kBatch; ++k) {
+              const int32_t c = c0 + k * 32 + (int32_t)lane;
+              if (c < chunks) {
+                asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v[k].x), "=r"(v[k].y), "=r"(v[k].z), "=r"(v[k].w)
+                             : "l"(src + (size_t)c * 16));
+              }
+            }
+#pragma unroll
+            for (int k = 0; k < kBatch; ++k) {
+              const int32_t c = c0 + k * 32 + (int32_t)lane;
+              if (c < chunks) *reinterpret_cast<uint4*>(dst + (size_t)c * 16) = v[k];
+            }
+          }
+          if (p.disp_weights != nullptr && lane == 0) p.disp_peer_weights[dst_rank][dst_row] = wgt;
+        }
+        // every lane's stores must be visible system-wide before the rows are counted
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (int r = 0; r < kRowsPerFence; ++r) {
+            const int32_t b = bucket_of[r];
+            if (b < 0) continue;
+            const int32_t done = atomicAdd(&p.disp_bucket_done[b], 1) + 1;
+            if (done == p.disp_counts[b]) {
+              __threadfence_system();
+              int32_t* flag =
+                  p.disp_peer_flags[dst_of[r]] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
+              asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch)
+                           : "memory");
+            }
+          }
+        }
+      }
     }
   } else {
     // -------------------------------- epilogue --------------------------------

@@ -161,13 +161,13 @@ route_finalize_kernel(const int32_t* __restrict__ cube, int rank, int world, int
                       int32_t* __restrict__ recv_expert_offs, int32_t* __restrict__ recv_seg_starts,
                       int32_t* __restrict__ pull_dst_start, int32_t* __restrict__ stats,
                       int32_t* __restrict__ mtile_group, int32_t* __restrict__ mtile_row0,
-                      int32_t* __restrict__ num_mtiles, StatusRecord* status) {
+                      int32_t* __restrict__ num_mtiles, int32_t* __restrict__ order_prefix,
+                      int32_t* __restrict__ bucket_done, StatusRecord* status) {
   extern __shared__ int32_t sm[];
   const int nb = world * epr;
   int32_t* tot = sm;
   int32_t* pre = sm + nb;
   int32_t* loc = sm + 2 * nb;
-  int32_t* tiles = sm + 3 * nb;  // [epr + 1] exclusive tile offsets of the local experts
   __shared__ int warp_sums[32];
   __shared__ int scan_total;
   const int tid = threadIdx.x;
@@ -199,6 +199,26 @@ route_finalize_kernel(const int32_t* __restrict__ cube, int rank, int world, int
         off += loc[first + j];
       }
     }
+  }
+  __syncthreads();
+
+  // Prefix of the local counts in dispatch order (see dispatch_order_bucket) and the
+  // per-bucket delivery counters of the fused dispatch, cleared for the next launch.
+  {
+    const int per = (nb + 1023) / 1024;
+    const int first = tid * per;
+    int local = 0;
+    for (int j = 0; j < per; ++j)
+      if (first + j < nb) local += loc[dispatch_order_bucket(first + j, rank, world, epr)];
+    int off = block_exclusive_scan_1024(local, warp_sums, &scan_total);
+    for (int j = 0; j < per; ++j) {
+      if (first + j < nb) {
+        order_prefix[first + j] = off;
+        off += loc[dispatch_order_bucket(first + j, rank, world, epr)];
+      }
+    }
+    if (tid == 0) order_prefix[nb] = scan_total;
+    for (int b = tid; b < nb; b += 1024) bucket_done[b] = 0;
   }
   __syncthreads();
 
@@ -422,8 +442,12 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
                       int32_t* recv_per_expert, int32_t* recv_expert_offs,
                       int32_t* recv_seg_starts, int32_t* pull_dst_start, int32_t* stats,
                       int32_t* mtile_group, int32_t* mtile_row0, int32_t* num_mtiles,
-                      int32_t* row_src_rank, int32_t* row_src_pos, void* status,
-                      cudaStream_t stream) {
+                      int32_t* row_src_rank, int32_t* row_src_pos, int32_t* order_prefix,
+                      int32_t* bucket_done, void* status, cudaStream_t stream) {
+  if (!order_prefix || !bucket_done) {
+    set_error("mm_route_finalize: null argument");
+    return MM_ERR_ARG;
+  }
   if (!count_cube || !send_bucket_starts || !send_bucket_dst_starts || !recv_counts_re ||
       !recv_per_expert || !recv_expert_offs || !recv_seg_starts || !pull_dst_start || !stats ||
       !mtile_group || !mtile_row0 || !num_mtiles || !row_src_rank || !row_src_pos) {
@@ -451,7 +475,8 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
   route_finalize_kernel<<<1, 1024, smem, stream>>>(
       count_cube, rank, world, epr, bins, capacity_rows, send_bucket_starts, send_bucket_dst_starts,
       recv_counts_re, recv_per_expert, recv_expert_offs, recv_seg_starts, pull_dst_start, stats,
-      mtile_group, mtile_row0, num_mtiles, reinterpret_cast<StatusRecord*>(status));
+      mtile_group, mtile_row0, num_mtiles, order_prefix, bucket_done,
+      reinterpret_cast<StatusRecord*>(status));
   if (int rc = check_launch("route_finalize_kernel")) return rc;
   const int nseg = world * epr;
   const int blocks = (nseg + 7) / 8;

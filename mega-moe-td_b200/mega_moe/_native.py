@@ -37,6 +37,14 @@ class GemmDesc(C.Structure):
     ]
 
 
+class DispatchDesc(C.Structure):
+    _fields_ = [(name, C.c_void_p) for name in (
+        "src", "weights", "send_token", "send_route", "send_bucket_starts",
+        "send_bucket_dst_starts", "count_row", "order_prefix", "local_stats", "bucket_done",
+        "peer_rows", "peer_weights", "peer_flags", "my_flags")] + [
+        (name, C.c_int32) for name in ("hidden", "rank", "world", "epr", "capacity_rows", "epoch")]
+
+
 # name -> (restype, argtypes); must list every symbol of include/mega_moe_b200.h
 SIGNATURES = {
     "mm_abi_version": (C.c_int, []),
@@ -55,15 +63,16 @@ SIGNATURES = {
     "mm_route_local_static": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, _c_i32p,
                                         _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_ptr]),
     "mm_route_finalize": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int] +
-                          [_c_i32p] * 13 + [_c_ptr, _c_ptr]),
+                          [_c_i32p] * 15 + [_c_ptr, _c_ptr]),
     "mm_dispatch_rows": (C.c_int, [_c_ptr, C.c_int, _c_ptr, _c_i32p, _c_i32p, _c_i32p, _c_i32p,
                                    _c_i32p, _c_i32p, C.c_int, C.c_int, C.c_int, _c_ptr, _c_ptr,
                                    _c_ptr]),
     "mm_topk_reduce": (C.c_int, [_c_ptr, C.c_int64, _c_i32p, C.c_int, C.c_int, C.c_int, _c_ptr,
                                  _c_ptr, _c_ptr, _c_ptr]),
-    "mm_fc1_swiglu": (C.c_int, [C.POINTER(GemmDesc), _c_ptr, C.c_int64, _c_ptr, C.c_int64, _c_ptr,
+    "mm_fc1_swiglu": (C.c_int, [C.POINTER(GemmDesc), C.POINTER(DispatchDesc), _c_ptr, C.c_int64, _c_ptr, C.c_int64, _c_ptr,
                                 C.c_int, C.c_float, C.c_float, C.c_float, _c_ptr]),
-    "mm_grouped_gemm": (C.c_int, [C.POINTER(GemmDesc), _c_ptr, C.c_int64, _c_ptr]),
+    "mm_grouped_gemm": (C.c_int, [C.POINTER(GemmDesc), C.POINTER(DispatchDesc), _c_ptr,
+                                  C.c_int64, _c_ptr]),
     "mm_grouped_gemm_scatter": (C.c_int, [C.POINTER(GemmDesc), _c_i32p, _c_i32p, _c_ptr,
                                           C.c_int64, _c_ptr]),
     "mm_grouped_wgrad": (C.c_int, [_c_ptr, C.c_int64, C.c_int32, _c_ptr, C.c_int64, C.c_int32,

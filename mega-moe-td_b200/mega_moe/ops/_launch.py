@@ -78,6 +78,44 @@ def make_desc(ctx: MoEForwardContext, a: torch.Tensor, a_rows_cap: int, lda: int
     return d
 
 
+def fused_dispatch_enabled() -> bool:
+    """MOE_FUSED_DISPATCH=0 selects the separate row-push kernel followed by a rank barrier
+    instead of the dispatch warps inside the GEMM launch (default: fused)."""
+    import os
+    return os.environ.get("MOE_FUSED_DISPATCH", "1") != "0"
+
+
+def make_dispatch_desc(ctx: MoEForwardContext, src: torch.Tensor, weights, plan=None,
+                       reset_counters: bool = False) -> N.DispatchDesc:
+    """Descriptor of the dispatch fused into the next grouped GEMM (rows of ``src``)."""
+    p = plan if plan is not None else ctx
+    if reset_counters:
+        ctx.disp_bucket_done.zero_()
+    d = N.DispatchDesc()
+    d.src = src.data_ptr()
+    d.weights = N.ptr(weights)
+    d.send_token = p.send_token_indices.data_ptr()
+    d.send_route = p.send_route_indices.data_ptr()
+    d.send_bucket_starts = p.metadata_send_bucket_starts.data_ptr()
+    d.send_bucket_dst_starts = p.metadata_send_bucket_dst_starts.data_ptr()
+    d.count_row = p.metadata_count_row.data_ptr()
+    d.order_prefix = p.disp_order_prefix.data_ptr()
+    d.local_stats = p.metadata_local_stats.data_ptr()
+    d.bucket_done = ctx.disp_bucket_done.data_ptr()
+    d.peer_rows = ctx.symm.peer_table("peer_mem").data_ptr()
+    d.peer_weights = (ctx.symm.peer_table("routing_weight_mem").data_ptr()
+                      if weights is not None else None)
+    d.peer_flags = ctx.symm.peer_table("dispatch_flags").data_ptr()
+    d.my_flags = ctx.dispatch_flags.data_ptr()
+    d.hidden = ctx.hidden_size
+    d.rank = ctx.rank
+    d.world = ctx.world_size
+    d.epr = ctx.experts_per_rank
+    d.capacity_rows = ctx.max_received_routes
+    d.epoch = ctx.next_dispatch_epoch()
+    return d
+
+
 def dispatch_rows(ctx: MoEForwardContext, src: torch.Tensor, weights, num_routes: int, plan=None):
     """Push the send rows of ``src`` (and their routing weights) to the owning ranks."""
     p = plan if plan is not None else ctx
@@ -96,10 +134,12 @@ def dispatch_rows(ctx: MoEForwardContext, src: torch.Tensor, weights, num_routes
     N.count_launches(1)
 
 
-def fc1_swiglu(ctx, desc, act_out, raw_out, row_weight, activation, beta, linear_beta, clamp):
+def fc1_swiglu(ctx, desc, act_out, raw_out, row_weight, activation, beta, linear_beta, clamp,
+               dispatch=None):
     with _timed("fc1_swiglu"):
         N.check(N.lib().mm_fc1_swiglu(
-            C.byref(desc), act_out.data_ptr(), act_out.stride(0),
+            C.byref(desc), C.byref(dispatch) if dispatch is not None else None,
+            act_out.data_ptr(), act_out.stride(0),
             N.ptr(raw_out), raw_out.stride(0) if raw_out is not None else 0,
             row_weight.data_ptr(), N.ACT_IDS[activation], float(beta),
             float(linear_beta) if linear_beta is not None else 0.0, float(clamp),
@@ -107,10 +147,11 @@ def fc1_swiglu(ctx, desc, act_out, raw_out, row_weight, activation, beta, linear
     N.count_launches(1)
 
 
-def grouped_gemm(desc, out, name="grouped_gemm"):
+def grouped_gemm(desc, out, name="grouped_gemm", dispatch=None):
     with _timed(name):
-        N.check(N.lib().mm_grouped_gemm(C.byref(desc), out.data_ptr(), out.stride(0),
-                                        N.stream_ptr()), "mm_grouped_gemm")
+        N.check(N.lib().mm_grouped_gemm(
+            C.byref(desc), C.byref(dispatch) if dispatch is not None else None,
+            out.data_ptr(), out.stride(0), N.stream_ptr()), "mm_grouped_gemm")
     N.count_launches(1)
 
 

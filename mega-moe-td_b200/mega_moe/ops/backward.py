@@ -83,14 +83,20 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
                  mtile_row0=plan.mtile_row0, num_mtiles=plan.num_mtiles)
 
     # ---- stage 1: dispatch dy + FC2 input gradient ------------------------------------
-    L.dispatch_rows(ctx, dy, None, num_routes, plan=plan)
-    ctx.rank_barrier()
+    # The dy dispatch is fused into the GEMM launch (it runs even when this rank received
+    # nothing, because its rows are other ranks' input).
     recv_dy = ctx.peer_mem.view(cap, hidden)
-    grad_swiglu = torch.empty(m, ffn, dtype=dtype, device=device)
-    if m > 0:
-        desc = L.make_desc(ctx, recv_dy, cap, hidden, fc2, k_dim=1, n_dim=2, n_out=ffn,
-                           k_extent=hidden, **tiles)
-        L.grouped_gemm(desc, grad_swiglu, name="fc2_dgrad")
+    grad_swiglu = torch.empty(max(m, 1), ffn, dtype=dtype, device=device)[:m]
+    desc = L.make_desc(ctx, recv_dy, cap, hidden, fc2, k_dim=1, n_dim=2, n_out=ffn,
+                       k_extent=hidden, **tiles)
+    if L.fused_dispatch_enabled():
+        disp = L.make_dispatch_desc(ctx, dy, None, plan=plan, reset_counters=True)
+    else:
+        disp = None
+        L.dispatch_rows(ctx, dy, None, num_routes, plan=plan)
+        ctx.rank_barrier()
+    L.grouped_gemm(desc, grad_swiglu if m > 0 else grad_swiglu.new_empty(1, ffn),
+                   name="fc2_dgrad", dispatch=disp)
     grad_fc2_out_sorted = recv_dy[:m]
 
     # ---- stage 3: FC2 weight gradient (reads the receive buffer, so it runs before the

@@ -51,7 +51,7 @@ _PLAN_FIELDS = (
     "metadata_send_bucket_starts", "metadata_send_bucket_dst_starts", "metadata_local_stats",
     "metadata_stats", "metadata_recv_expert_offs", "metadata_recv_counts_re",
     "metadata_recv_per_expert", "mtile_group", "mtile_row0", "num_mtiles", "row_src_rank",
-    "row_src_pos",
+    "row_src_pos", "metadata_count_row", "disp_order_prefix",
 )
 
 
@@ -382,14 +382,20 @@ class FusedMoEForward(torch.nn.Module):
                                      device=hidden_states.device)
         elif fc1_output.shape != (m, n_out) or fc1_output.dtype != self.activation_dtype:
             raise ValueError(f"fc1_output must be BF16 with shape {(m, n_out)}")
-        num_routes = selected_experts.numel()
-        L.dispatch_rows(ctx, hidden_states, routing_weights, num_routes)
-        ctx.rank_barrier()
-        if m > 0:
-            recv = ctx.peer_mem.view(ctx.max_received_routes, self.hidden_size)
-            desc = L.make_desc(ctx, recv, ctx.max_received_routes, self.hidden_size, fc1_weight,
-                               k_dim=1, n_dim=2, n_out=n_out, k_extent=self.hidden_size)
-            L.grouped_gemm(desc, fc1_output)
+        # dispatch runs inside the GEMM launch (it must run even when this rank receives
+        # nothing: its rows are someone else's input)
+        recv = ctx.peer_mem.view(ctx.max_received_routes, self.hidden_size)
+        desc = L.make_desc(ctx, recv, ctx.max_received_routes, self.hidden_size, fc1_weight,
+                           k_dim=1, n_dim=2, n_out=n_out, k_extent=self.hidden_size)
+        if L.fused_dispatch_enabled():
+            disp = L.make_dispatch_desc(ctx, hidden_states, routing_weights)
+        else:
+            disp = None
+            L.dispatch_rows(ctx, hidden_states, routing_weights, selected_experts.numel())
+            ctx.rank_barrier()
+        out_buf = fc1_output if m > 0 else torch.empty(
+            1, n_out, dtype=self.activation_dtype, device=hidden_states.device)
+        L.grouped_gemm(desc, out_buf, dispatch=disp)
         if final_barrier:
             ctx.rank_barrier()
         recv_rows = ctx.peer_mem.view(ctx.max_received_routes, self.hidden_size)[:m]
@@ -460,14 +466,20 @@ class FusedMoEForward(torch.nn.Module):
         launch_routing_metadata(ctx, selected_experts)
         self._routing_generation += 1
         self._routing_weights_keepalive = routing_weights
-        L.dispatch_rows(ctx, hidden_states, routing_weights, num_routes)
-        ctx.rank_barrier()
+        # Dispatch is fused into the FC1 launch: extra warps push the rows while the GEMM
+        # consumes each expert as soon as every source has flagged it complete.
         recv = ctx.peer_mem.view(cap, hidden)
         fc1_desc = L.make_desc(ctx, recv, cap, hidden, gate_up_weight, k_dim=1, n_dim=2,
                                n_out=ffn_size, k_extent=hidden)
+        if L.fused_dispatch_enabled():
+            disp = L.make_dispatch_desc(ctx, hidden_states, routing_weights)
+        else:
+            disp = None
+            L.dispatch_rows(ctx, hidden_states, routing_weights, num_routes)
+            ctx.rank_barrier()
         L.fc1_swiglu(ctx, fc1_desc, self._act_buf, self._fc1_buf if return_saved else None,
                      ctx.routing_weight_mem, self.activation, self.situ_beta,
-                     self.situ_linear_beta, self.clamp_limit)
+                     self.situ_linear_beta, self.clamp_limit, dispatch=disp)
         saved = None
         if return_saved:
             # The receive buffer is rewritten by the next dispatch (forward or backward), so

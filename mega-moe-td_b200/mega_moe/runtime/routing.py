@@ -85,7 +85,9 @@ def launch_routing_metadata(context: MoEForwardContext, selected_experts: torch.
         ctx.metadata_recv_expert_offs.data_ptr(), ctx.metadata_recv_seg_starts.data_ptr(),
         ctx.metadata_pull_dst_start.data_ptr(), ctx.metadata_stats.data_ptr(),
         ctx.mtile_group.data_ptr(), ctx.mtile_row0.data_ptr(), ctx.num_mtiles.data_ptr(),
-        ctx.row_src_rank.data_ptr(), ctx.row_src_pos.data_ptr(), ctx.status.data_ptr(), stream),
+        ctx.row_src_rank.data_ptr(), ctx.row_src_pos.data_ptr(),
+        ctx.disp_order_prefix.data_ptr(), ctx.disp_bucket_done.data_ptr(),
+        ctx.status.data_ptr(), stream),
         "mm_route_finalize")
     timer.__exit__()
     N.count_launches(5)  # histogram, scan, scatter, offsets, row tables

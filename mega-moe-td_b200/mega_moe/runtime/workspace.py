@@ -141,6 +141,10 @@ class MoEForwardContext:
     row_src_rank: Optional[torch.Tensor] = None
     row_src_pos: Optional[torch.Tensor] = None
     status: Optional[torch.Tensor] = None
+    dispatch_flags: Optional[torch.Tensor] = None
+    disp_order_prefix: Optional[torch.Tensor] = None
+    disp_bucket_done: Optional[torch.Tensor] = None
+    dispatch_epoch: int = 0
     barrier_epoch: int = 0
     ep_group: object = None
     _extra: dict = field(default_factory=dict)
@@ -176,6 +180,13 @@ class MoEForwardContext:
         if self.world_size == 1:
             return
         self._barrier(2)
+
+    def next_dispatch_epoch(self) -> int:
+        """Epoch of the next fused dispatch; arrival flags only ever grow."""
+        self.dispatch_epoch += 1
+        if self.dispatch_epoch >= 2**31 - 1:
+            raise RuntimeError("dispatch epoch exhausted; recreate the operator")
+        return self.dispatch_epoch
 
     def read_status(self) -> N.StatusRecord:
         rec = N.StatusRecord()
@@ -280,6 +291,7 @@ def create_moe_forward_context(
         "routing_weight_mem": max_received_routes * 4,
         "combine_mem": num_routes * hidden_size * 2,
         "combine_gate_mem": num_routes * 2,
+        "dispatch_flags": world_size * experts_per_rank * 4,
     }
     ctx.symm = SymmetricBlock(regions, rank, world_size, ep_group, device)
     ctx.peer_mem = ctx.symm.local("peer_mem", torch.bfloat16)
@@ -287,6 +299,7 @@ def create_moe_forward_context(
     ctx.signal_mem = ctx.symm.local("flags", torch.int32)
     ctx.combine_mem = ctx.symm.local("combine_mem", torch.bfloat16).view(num_routes, hidden_size)
     ctx.combine_gate_mem = ctx.symm.local("combine_gate_mem", torch.bfloat16)
+    ctx.dispatch_flags = ctx.symm.local("dispatch_flags", torch.int32)
 
     num_buckets = world_size * experts_per_rank
     bins = next_power_of_2(num_buckets)
@@ -318,6 +331,8 @@ def create_moe_forward_context(
     ctx.row_src_rank = torch.zeros(max(max_received_routes, 1), **i32)
     ctx.row_src_pos = torch.zeros(max(max_received_routes, 1), **i32)
     ctx.status = torch.zeros(8, **i32)
+    ctx.disp_order_prefix = torch.zeros(num_buckets + 1, **i32)
+    ctx.disp_bucket_done = torch.zeros(num_buckets, **i32)
     register_context(ctx)
     return ctx
 

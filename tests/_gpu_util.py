@@ -60,7 +60,7 @@ def run_grouped_gemm(a, weight, k_dim, n_dim, counts):
     n_out = weight.shape[n_dim]
     d, keep = gemm_desc(a, weight, k_dim, n_dim, n_out, weight.shape[k_dim], counts, status)
     out = torch.full((a.shape[0], n_out), float("nan"), dtype=torch.bfloat16, device=a.device)
-    N.check(N.lib().mm_grouped_gemm(C.byref(d), out.data_ptr(), out.stride(0), N.stream_ptr()),
+    N.check(N.lib().mm_grouped_gemm(C.byref(d), None, out.data_ptr(), out.stride(0), N.stream_ptr()),
             "mm_grouped_gemm")
     torch.cuda.synchronize()
     assert int(status[0]) == 0, status.tolist()
@@ -76,7 +76,7 @@ def run_fc1_swiglu(a, gate_up, row_weight, counts, activation="swiglu", beta=1.0
     raw = torch.full((a.shape[0], 2 * ffn), float("nan"), dtype=torch.bfloat16,
                      device=a.device) if want_raw else None
     N.check(N.lib().mm_fc1_swiglu(
-        C.byref(d), act.data_ptr(), act.stride(0), N.ptr(raw), raw.stride(0) if want_raw else 0,
+        C.byref(d), None, act.data_ptr(), act.stride(0), N.ptr(raw), raw.stride(0) if want_raw else 0,
         row_weight.data_ptr(), N.ACT_IDS[activation], float(beta),
         float(linear_beta) if linear_beta is not None else 0.0, float(clamp), N.stream_ptr()),
         "mm_fc1_swiglu")

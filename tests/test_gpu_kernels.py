@@ -55,11 +55,14 @@ def _finalize(cube_np, rank, world, epr, bins, capacity):
              mtile_row0=torch.full((capacity // 128 + epr + 1,), -7, **i32),
              num_mtiles=torch.full((1,), -7, **i32),
              row_src_rank=torch.full((max(capacity, 1),), -7, **i32),
-             row_src_pos=torch.full((max(capacity, 1),), -7, **i32))
+             row_src_pos=torch.full((max(capacity, 1),), -7, **i32),
+             order_prefix=torch.full((nb + 1,), -7, **i32),
+             bucket_done=torch.full((nb,), -7, **i32))
     status = torch.zeros(8, **i32)
     order = ["send_bucket_starts", "send_bucket_dst_starts", "recv_counts_re", "recv_per_expert",
              "recv_expert_offs", "recv_seg_starts", "pull_dst_start", "stats", "mtile_group",
-             "mtile_row0", "num_mtiles", "row_src_rank", "row_src_pos"]
+             "mtile_row0", "num_mtiles", "row_src_rank", "row_src_pos", "order_prefix",
+             "bucket_done"]
     N.check(lib.mm_route_finalize(cube.data_ptr(), rank, world, epr, bins, capacity,
                                   *[t[k].data_ptr() for k in order], status.data_ptr(),
                                   N.stream_ptr()), "mm_route_finalize")
@@ -121,6 +124,12 @@ def test_routing_metadata_bit_exact(tokens, top_k, experts, world, drop):
             for r0 in range(0, int(want["recv_per_expert"][e]), 128):
                 exp_groups.append(e)
                 exp_rows.append(int(want["recv_expert_offs"][e]) + r0)
+        # dispatch order: local expert slot outermost, destinations rotated by the rank
+        order = [((r + 1 + dd) % world) * epr + le for le in range(epr) for dd in range(world)]
+        local_row = cube[r, :world * epr]
+        np.testing.assert_array_equal(got["order_prefix"],
+                                      np.r_[0, np.cumsum(local_row[order])])
+        assert (got["bucket_done"] == 0).all()
         nt = int(got["num_mtiles"][0])
         assert nt == len(exp_groups)
         np.testing.assert_array_equal(got["mtile_group"][:nt], exp_groups)
