@@ -120,7 +120,9 @@ int mm_route_local_static(const int32_t* selected, int num_routes, int top_k, in
  *   recv_counts_re [world, epr]   recv_per_expert [epr]   recv_expert_offs [epr + 1]
  *   recv_seg_starts [epr, world + 1]   pull_dst_start [epr * world]
  *   stats [2 + world] = {M, max over destinations, per-destination totals}
- *   mtile_group / mtile_row0 [capacity_rows / 128 + epr]   num_mtiles [1]
+ *   mtile_group / mtile_row0 [capacity_rows / 128 + epr]   num_mtiles [1]   (128-row tiles)
+ *   mtile2_group / mtile2_row0 [capacity_rows / 256 + epr]  num_mtiles2 [1]  (256-row tiles of
+ *     the CTA-pair GEMM, mm_gemm_desc.pair = 1)
  *   row_src_rank / row_src_pos [capacity_rows]
  *   order_prefix [world * epr + 1]: prefix of the local counts in dispatch order (local expert
  *     slot outermost, destination rank rotated by `rank`), bucket_done [world * epr]: zeroed
@@ -132,6 +134,7 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
                       int32_t* recv_per_expert, int32_t* recv_expert_offs,
                       int32_t* recv_seg_starts, int32_t* pull_dst_start, int32_t* stats,
                       int32_t* mtile_group, int32_t* mtile_row0, int32_t* num_mtiles,
+                      int32_t* mtile2_group, int32_t* mtile2_row0, int32_t* num_mtiles2,
                       int32_t* row_src_rank, int32_t* row_src_pos, int32_t* order_prefix,
                       int32_t* bucket_done, void* status, cudaStream_t stream);
 
@@ -169,6 +172,9 @@ typedef struct mm_gemm_desc {
   int32_t N;                  /* output columns (fused FC1: F) */
   int32_t K;                  /* reduction extent */
   int32_t grid_limit;         /* 0: one CTA per SM */
+  int32_t pair;               /* 1: tcgen05 cta_group::2 - clusters of two CTAs share 256-row tiles
+                                 (pass the 256-row tile table); 0: one CTA per 128-row tile */
+  int32_t reserved;
   const int32_t* group_offs;  /* [num_groups + 1] */
   const int32_t* mtile_group; /* from mm_route_finalize */
   const int32_t* mtile_row0;
@@ -230,7 +236,7 @@ int mm_grouped_gemm_scatter(const mm_gemm_desc* d, const int32_t* row_dst_rank,
 int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void* orig_in,
                      int64_t ld_in, int32_t Nw, int64_t rows_cap, const int32_t* group_offs,
                      int32_t num_groups, void* out, int64_t ld_out, int64_t out_group_stride,
-                     void* status, int32_t grid_limit, cudaStream_t stream);
+                     void* status, int32_t grid_limit, int32_t pair, cudaStream_t stream);
 
 /* ---- backward stage 2 ------------------------------------------------------------- */
 /* Gated-activation backward per received row (reference: kernels/swiglu_bwd.py:15-83):

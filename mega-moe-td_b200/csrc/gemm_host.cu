@@ -84,8 +84,38 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   if (!prepare_kernel()) return MM_ERR_CUDA;
   int grid = g_num_sms;
   if (grid_limit > 0 && grid_limit < grid) grid = grid_limit;
-  grouped_gemm_kernel<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(tmA, tmB, tmC, p);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = kGemmSmemBytes;
+  cfg.stream = stream;
+  // The kernel contains cta_group::2 instructions, so every launch uses clusters of two CTAs
+  // (in single-CTA mode the two CTAs of a cluster simply work on different tiles).  The grid
+  // must be even and no larger than what can be co-resident.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  static int max_pairs = -1;
+  if (max_pairs < 0) {
+    cudaLaunchConfig_t probe = cfg;
+    probe.gridDim = dim3(g_num_sms & ~1, 1, 1);
+    int n = 0;
+    cudaError_t pe = cudaOccupancyMaxActiveClusters(&n, grouped_gemm_kernel, &probe);
+    if (pe != cudaSuccess || n <= 0) {
+      set_error("cudaOccupancyMaxActiveClusters: %s (clusters=%d)", cudaGetErrorString(pe), n);
+      return MM_ERR_CUDA;
+    }
+    max_pairs = n;
+  }
+  grid &= ~1;
+  if (grid > 2 * max_pairs) grid = 2 * max_pairs;
+  if (grid < 2) grid = 2;
+  cfg.gridDim = dim3(grid, 1, 1);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, grouped_gemm_kernel, tmA, tmB, tmC, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("grouped_gemm_kernel launch: %s", cudaGetErrorString(e));
     return MM_ERR_CUDA;
@@ -152,7 +182,7 @@ int grouped_rows_gemm(int epi, const mm_gemm_desc& d, GemmParams p, cudaStream_t
   if (d.b_k_major) {
     uint64_t dims[3] = {(uint64_t)d.K, (uint64_t)b_cols, (uint64_t)d.num_groups};
     uint64_t str[2] = {(uint64_t)d.b_ld * 2, (uint64_t)d.b_group_stride * 2};
-    uint32_t box[3] = {64, (uint32_t)kBlockN, 1};
+    uint32_t box[3] = {64, (uint32_t)(d.pair ? kBlockN / 2 : kBlockN), 1};
     if (!encode_map(&tmB, d.b, 3, dims, str, box)) return MM_ERR_CUDA;
   } else {
     uint64_t dims[3] = {(uint64_t)b_cols, (uint64_t)d.K, (uint64_t)d.num_groups};
@@ -167,7 +197,8 @@ int grouped_rows_gemm(int epi, const mm_gemm_desc& d, GemmParams p, cudaStream_t
   p.K = d.K;
   p.a_mn = 0;
   p.b_mn = d.b_k_major ? 0 : 1;
-  p.idesc = make_idesc_bf16(kBlockM, kBlockN, 0, p.b_mn);
+  p.pair = d.pair ? 1 : 0;
+  p.idesc = make_idesc_bf16(p.pair ? 2 * kBlockM : kBlockM, kBlockN, 0, p.b_mn);
   p.group_offs = d.group_offs;
   p.mtile_group = d.mtile_group;
   p.mtile_row0 = d.mtile_row0;
@@ -251,7 +282,7 @@ int mm_grouped_gemm_scatter(const mm_gemm_desc* d, const int32_t* row_dst_rank,
 int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void* orig_in,
                      int64_t ld_in, int32_t Nw, int64_t rows_cap, const int32_t* group_offs,
                      int32_t num_groups, void* out, int64_t ld_out, int64_t out_group_stride,
-                     void* status, int32_t grid_limit, cudaStream_t stream) {
+                     void* status, int32_t grid_limit, int32_t pair, cudaStream_t stream) {
   if (!grad_out || !orig_in || !group_offs || !out) {
     set_error("mm_grouped_wgrad: null argument");
     return MM_ERR_ARG;
@@ -292,8 +323,9 @@ int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void
   p.Mw = Mw;
   p.a_mn = 1;
   p.b_mn = 1;
-  p.idesc = make_idesc_bf16(kBlockM, kBlockN, 1, 1);
-  p.m_tiles = (Mw + kBlockM - 1) / kBlockM;
+  p.pair = pair ? 1 : 0;
+  p.idesc = make_idesc_bf16(p.pair ? 2 * kBlockM : kBlockM, kBlockN, 1, 1);
+  p.m_tiles = p.pair ? (Mw + 2 * kBlockM - 1) / (2 * kBlockM) : (Mw + kBlockM - 1) / kBlockM;
   p.n_tiles = (Nw + kBlockN - 1) / kBlockN;
   p.group_offs = group_offs;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);

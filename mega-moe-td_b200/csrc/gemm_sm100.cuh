@@ -22,10 +22,15 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockK = 64;
 constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
+constexpr int kStages = 4;                                        // one CTA per tile
 constexpr int kStageABytes = kBlockM * kBlockK * 2;               // 16 KB
 constexpr int kStageBBytes = kBlockN * kBlockK * 2;               // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;          // 48 KB
+// Pair mode (cta_group::2): two CTAs of a cluster share one 256x256 tile; each loads its own
+// 128 rows of A and half of B (128 columns), so a stage is 32 KB and six stages fit.
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = kStageABytes + kStageBBytes / 2;  // 32 KB
+constexpr int kMaxStages = 6;
 constexpr int kBoxBytes = 64 * 64 * 2;                            // one 64x64 MN-major box
 constexpr int kEpiWarps = 4;
 constexpr int kStagingPerWarp = 2 * 32 * 128;                     // two 32-row x 128-byte buffers
@@ -53,6 +58,7 @@ struct GemmParams {
   int32_t swiglu_F;      // column offset of the "up" half inside B and inside out2
   int32_t tma_store;     // kGroupedReduce: output tiles leave through TMA tensor stores
   int32_t wide_store;    // row stores in 256-byte pieces (scatter over NVLink)
+  int32_t pair;          // 1: cta_group::2, clusters of two CTAs, 256-row tiles
   int32_t act;
   float act_beta;
   float act_linear_beta; // <= 0: no transform on up
@@ -99,24 +105,28 @@ __device__ __forceinline__ int32_t total_tiles(const GemmParams& p) {
   return p.num_groups * p.m_tiles * p.n_tiles;
 }
 
-__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int32_t t, int32_t nmt) {
+// Tile t of the launch as seen by CTA `cta_rank` of its pair (always 0 without pairing).
+// A tile spans 128 rows, or 256 in pair mode with 128 rows per CTA.
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int32_t t, int32_t cta_rank) {
   TileInfo ti;
+  const int32_t shift = p.pair ? 8 : 7;
+  const int32_t tile_rows = 1 << shift;
   if (p.kind == kGroupedRows) {
-    // Group-major order: all tiles of one expert are consecutive (n-tile outer, 128-row tile
+    // Group-major order: all tiles of one expert are consecutive (n-tile outer, row tile
     // inner), so the CTAs running at the same time share one expert's rows and weights in L2.
-    // Tile t lies in the group of 128-row tile t / n_tiles because group g owns the tile
+    // Tile t lies in the group of row tile t / n_tiles because group g owns the tile
     // range [first_g * n_tiles, (first_g + cnt_g) * n_tiles).
     const int32_t u = t / p.n_tiles;
     ti.group = p.mtile_group[u];
     const int32_t g0 = p.group_offs[ti.group];
     const int32_t end = p.group_offs[ti.group + 1];
-    const int32_t first = u - ((p.mtile_row0[u] - g0) >> 7);
-    const int32_t cnt = (end - g0 + kBlockM - 1) >> 7;
+    const int32_t first = u - ((p.mtile_row0[u] - g0) >> shift);
+    const int32_t cnt = (end - g0 + tile_rows - 1) >> shift;
     const int32_t local = t - first * p.n_tiles;
     const int32_t nt = local / cnt;
     const int32_t mj = local - nt * cnt;
-    ti.row0 = g0 + mj * kBlockM;
-    ti.rows_valid = min(kBlockM, end - ti.row0);
+    ti.row0 = g0 + mj * tile_rows + cta_rank * kBlockM;
+    ti.rows_valid = max(0, min(kBlockM, end - ti.row0));
     ti.n0 = nt * (p.epi == kEpiSwiglu ? kBlockN / 2 : kBlockN);
     ti.num_kb = (p.K + kBlockK - 1) / kBlockK;
     ti.krow0 = 0;
@@ -127,8 +137,8 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int32_t t, 
     const int32_t r = t - ti.group * per_group;
     const int32_t nt = r / p.m_tiles;
     const int32_t mt = r - nt * p.m_tiles;
-    ti.row0 = mt * kBlockM;
-    ti.rows_valid = min(kBlockM, p.Mw - ti.row0);
+    ti.row0 = mt * tile_rows + cta_rank * kBlockM;
+    ti.rows_valid = max(0, min(kBlockM, p.Mw - ti.row0));
     ti.n0 = nt * kBlockN;
     ti.krow0 = p.group_offs[ti.group];
     ti.kcnt = p.group_offs[ti.group + 1] - ti.krow0;
@@ -234,26 +244,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* stages = smem;
-  uint8_t* staging = smem + kStages * kStageBytes;
+  uint8_t* staging = smem + kStages * kStageBytes;   // == kPairStages * kPairStageBytes
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpiWarps * kStagingPerWarp);
-  uint64_t* full_bar = bars;                  // [kStages]
-  uint64_t* empty_bar = bars + kStages;       // [kStages]
-  uint64_t* tmem_full = bars + 2 * kStages;   // [2]
-  uint64_t* tmem_empty = tmem_full + 2;       // [2]
+  uint64_t* full_bar = bars;                         // [kMaxStages] this CTA's loads landed
+  uint64_t* empty_bar = bars + kMaxStages;           // [kMaxStages] stage consumed by the MMA
+  uint64_t* ready_bar = bars + 2 * kMaxStages;       // [kMaxStages] pair mode: both CTAs' stage ready
+  uint64_t* tmem_full = bars + 3 * kMaxStages;       // [2]
+  uint64_t* tmem_empty = tmem_full + 2;              // [2]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
+  const int pair = p.pair;
+  const uint32_t cta_rank = pair ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int nstages = pair ? kPairStages : kStages;
+  const int stage_bytes = pair ? kPairStageBytes : kStageBytes;
+  const int b_boxes = pair ? 2 : 4;                  // 64-column boxes of an MN-major B stage
+  const int32_t b_col_off = pair ? (int32_t)cta_rank * (kBlockN / 2) : 0;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      mbar_init(&ready_bar[s], 2);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], kEpiWarps * 32);
+      mbar_init(&tmem_empty[a], (pair ? 2 : 1) * kEpiWarps * 32);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -263,16 +282,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (p.tma_store) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_base_slot, kTmemCols);
-    tmem_relinquish();
+    if (pair) {
+      tmem_alloc_pair(tmem_base_slot, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_base_slot, kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (pair) cluster_sync();   // the peer's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  const int32_t nmt = (p.kind == kGroupedRows) ? *p.num_mtiles : 0;
   const int32_t ntiles = total_tiles(p);
+  const int32_t tile0 = pair ? (int32_t)(blockIdx.x >> 1) : (int32_t)blockIdx.x;
+  const int32_t tile_step = pair ? (int32_t)(gridDim.x >> 1) : (int32_t)gridDim.x;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -281,8 +307,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       bool alive = true;
       int32_t ready_group = -1;
-      for (int32_t t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
-        const TileInfo ti = decode_tile(p, t, nmt);
+      for (int32_t t = tile0; t < ntiles && alive; t += tile_step) {
+        const TileInfo ti = decode_tile(p, t, cta_rank);
         if (p.disp_src != nullptr && ti.group != ready_group) {
           // Rows of this expert are pushed by every rank's dispatch warps: wait (bounded)
           // until each source has flagged its bucket complete for this launch's epoch.
@@ -316,22 +342,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             alive = false;
             break;
           }
-          uint8_t* sA = stages + stage * kStageBytes;
+          uint8_t* sA = stages + stage * stage_bytes;
           uint8_t* sB = sA + kStageABytes;
-          mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+          mbar_arrive_expect_tx(&full_bar[stage], stage_bytes);
           if (p.kind == kGroupedRows) {
             const int32_t k0 = kb * kBlockK;
             tma_load_2d(sA, &tmA, &full_bar[stage], k0, ti.row0);
             if (!p.b_mn) {
-              tma_load_3d(sB, &tmB, &full_bar[stage], k0, ti.n0, ti.group);
+              // K-major weights: one box of 256 (or, per CTA of a pair, 128) output columns
+              tma_load_3d(sB, &tmB, &full_bar[stage], k0, ti.n0 + b_col_off, ti.group);
             } else {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
+              for (int i = 0; i < b_boxes; ++i) {
                 int32_t col;
                 if (p.epi == kEpiSwiglu) {
-                  col = (i < 2) ? (ti.n0 + 64 * i) : (p.swiglu_F + ti.n0 + 64 * (i - 2));
+                  // gate columns fill the first half of the 256-wide tile, up columns the second
+                  const int half = pair ? (int)cta_rank : (i >> 1);
+                  const int sub = pair ? i : (i & 1);
+                  col = (half ? p.swiglu_F : 0) + ti.n0 + 64 * sub;
                 } else {
-                  col = ti.n0 + 64 * i;
+                  col = ti.n0 + b_col_off + 64 * i;
                 }
                 tma_load_3d(sB + i * kBoxBytes, &tmB, &full_bar[stage], col, k0, ti.group);
               }
@@ -341,11 +370,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 2; ++i)
               tma_load_2d(sA + i * kBoxBytes, &tmA, &full_bar[stage], ti.row0 + 64 * i, kr);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              tma_load_3d(sB + i * kBoxBytes, &tmB, &full_bar[stage], ti.n0 + 64 * i, kr, 0);
+            for (int i = 0; i < b_boxes; ++i)
+              tma_load_3d(sB + i * kBoxBytes, &tmB, &full_bar[stage], ti.n0 + b_col_off + 64 * i,
+                          kr, 0);
           }
-          if (++stage == kStages) {
+          if (++stage == nstages) {
             stage = 0;
             phase ^= 1;
           }
@@ -369,13 +398,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t b_lbo = p.b_mn ? (uint32_t)kBoxBytes : 16u;
     const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
     const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
-    for (int32_t t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
-      const TileInfo ti = decode_tile(p, t, nmt);
-      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kSiteTmemEmpty, acc)) {
-        alive = false;
-        break;
+    for (int32_t t = tile0; t < ntiles && alive; t += tile_step) {
+      const TileInfo ti = decode_tile(p, t, cta_rank);
+      // In pair mode only the leader CTA owns the accumulator hand-shake and issues MMAs; the
+      // peer's warp still walks the stages to prepare its half of every stage.
+      if (leader) {
+        const bool ok = pair ? mbar_wait_cluster(&tmem_empty[acc], acc_phase ^ 1, abort_flag,
+                                                 p.status, kSiteTmemEmpty, acc)
+                             : mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status,
+                                         kSiteTmemEmpty, acc);
+        if (!ok) {
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
       }
-      tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * kBlockN;
       for (int kb = 0; kb < ti.num_kb; ++kb) {
         if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kSiteSmemFull, stage)) {
@@ -383,14 +420,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           break;
         }
         tc_fence_after_sync();
-        uint8_t* sA = stages + stage * kStageBytes;
+        uint8_t* sA = stages + stage * stage_bytes;
         if (p.kind == kGroupedReduce) {
           const int32_t valid = ti.kcnt - kb * kBlockK;
           if (valid < kBlockK) {
-            // Rows past the end of the group belong to the next group: clear them in
-            // all six 64x64 boxes (K rows are 128 contiguous bytes in this layout).
+            // Rows past the end of the group belong to the next group: clear them in every
+            // 64x64 box of the stage (K rows are 128 contiguous bytes in this layout).
             const int32_t first = valid * 128;
-            for (int b = 0; b < 6; ++b) {
+            for (int b = 0; b < 2 + b_boxes; ++b) {
               uint8_t* box = sA + b * kBoxBytes;
               for (int32_t off = first + lane * 16; off < kBoxBytes; off += 32 * 16)
                 *reinterpret_cast<uint4*>(box + off) = make_uint4(0, 0, 0, 0);
@@ -399,26 +436,45 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             __syncwarp();
           }
         }
-        if (lane == 0) {
+        if (pair) {
+          // both CTAs report their half of the stage to the leader
+          if (lane == 0) mbar_arrive_cluster(&ready_bar[stage], 0);
+          if (leader) {
+            if (!mbar_wait_cluster(&ready_bar[stage], phase, abort_flag, p.status, kSitePairReady,
+                                   stage)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after_sync();
+          }
+        }
+        if (lane == 0 && leader) {
           const uint32_t a_addr = smem_u32(sA);
           const uint32_t b_addr = a_addr + kStageABytes;
           const uint64_t a_desc = make_smem_desc(a_addr, a_lbo, 1024);
           const uint64_t b_desc = make_smem_desc(b_addr, b_lbo, 1024);
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            umma_f16(d_tmem, a_desc + (uint64_t)(k * a_kstep), b_desc + (uint64_t)(k * b_kstep),
-                     p.idesc, (kb | k) != 0 ? 1u : 0u);
+            if (pair) {
+              umma_f16_pair(d_tmem, a_desc + (uint64_t)(k * a_kstep),
+                            b_desc + (uint64_t)(k * b_kstep), p.idesc, (kb | k) != 0 ? 1u : 0u);
+            } else {
+              umma_f16(d_tmem, a_desc + (uint64_t)(k * a_kstep), b_desc + (uint64_t)(k * b_kstep),
+                       p.idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
-          umma_commit(&empty_bar[stage]);
+          if (pair) umma_commit_pair(&empty_bar[stage]); else umma_commit(&empty_bar[stage]);
         }
         __syncwarp();
-        if (++stage == kStages) {
+        if (++stage == nstages) {
           stage = 0;
           phase ^= 1;
         }
       }
       if (!alive) break;
-      if (lane == 0) umma_commit(&tmem_full[acc]);
+      if (lane == 0 && leader) {
+        if (pair) umma_commit_pair(&tmem_full[acc]); else umma_commit(&tmem_full[acc]);
+      }
       __syncwarp();
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
@@ -524,8 +580,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t buf = 0;  // staging buffer the next chunk uses
-    for (int32_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
-      const TileInfo ti = decode_tile(p, t, nmt);
+    for (int32_t t = tile0; t < ntiles; t += tile_step) {
+      const TileInfo ti = decode_tile(p, t, cta_rank);
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, kSiteTmemFull, acc)) break;
       tc_fence_after_sync();
       const int32_t row = q * 32 + lane;
@@ -683,7 +739,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       tc_fence_before_sync();
-      mbar_arrive(&tmem_empty[acc]);
+      if (pair) mbar_arrive_cluster(&tmem_empty[acc], 0); else mbar_arrive(&tmem_empty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
@@ -693,9 +749,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   tc_fence_before_sync();
   __syncthreads();
+  if (pair) cluster_sync();   // no arrival or commit may target a CTA that has already left
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (pair) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 

@@ -161,8 +161,10 @@ route_finalize_kernel(const int32_t* __restrict__ cube, int rank, int world, int
                       int32_t* __restrict__ recv_expert_offs, int32_t* __restrict__ recv_seg_starts,
                       int32_t* __restrict__ pull_dst_start, int32_t* __restrict__ stats,
                       int32_t* __restrict__ mtile_group, int32_t* __restrict__ mtile_row0,
-                      int32_t* __restrict__ num_mtiles, int32_t* __restrict__ order_prefix,
-                      int32_t* __restrict__ bucket_done, StatusRecord* status) {
+                      int32_t* __restrict__ num_mtiles, int32_t* __restrict__ mtile2_group,
+                      int32_t* __restrict__ mtile2_row0, int32_t* __restrict__ num_mtiles2,
+                      int32_t* __restrict__ order_prefix, int32_t* __restrict__ bucket_done,
+                      StatusRecord* status) {
   extern __shared__ int32_t sm[];
   const int nb = world * epr;
   int32_t* tot = sm;
@@ -302,43 +304,52 @@ route_finalize_kernel(const int32_t* __restrict__ cube, int rank, int world, int
   }
   __syncthreads();
 
-  // 128-row tile table of the local experts, receive total and capacity check.
-  {
+  // Row-tile tables of the local experts (128 rows per tile, and 256 for CTA pairs), receive
+  // total and capacity check.
+  int total_tiles[2] = {0, 0};
+  for (int pass = 0; pass < 2; ++pass) {
+    const int shift = pass == 0 ? 7 : 8;
+    const int rows_per_tile = 1 << shift;
+    int32_t* tg = pass == 0 ? mtile_group : mtile2_group;
+    int32_t* tr = pass == 0 ? mtile_row0 : mtile2_row0;
     const int per = (epr + 1023) / 1024;
     const int first = tid * per;
     int local_tiles = 0, local_rows = 0;
     for (int j = 0; j < per; ++j) {
       if (first + j < epr) {
         const int c = tot[rank * epr + first + j];
-        local_tiles += (c + 127) >> 7;
+        local_tiles += (c + rows_per_tile - 1) >> shift;
         local_rows += c;
       }
     }
     int toff = block_exclusive_scan_1024(local_tiles, warp_sums, &scan_total);
-    const int total_tiles = scan_total;
+    total_tiles[pass] = scan_total;
     int roff = block_exclusive_scan_1024(local_rows, warp_sums, &scan_total);
     for (int j = 0; j < per; ++j) {
       if (first + j < epr) {
         const int c = tot[rank * epr + first + j];
-        const int nt = (c + 127) >> 7;
+        const int nt = (c + rows_per_tile - 1) >> shift;
         for (int i = 0; i < nt; ++i) {
-          mtile_group[toff + i] = first + j;
-          mtile_row0[toff + i] = roff + i * 128;
+          tg[toff + i] = first + j;
+          tr[toff + i] = roff + i * rows_per_tile;
         }
         toff += nt;
         roff += c;
       }
     }
-    if (tid == 0) {
-      int max_required = 0;
-      for (int d = 0; d < world; ++d) max_required = max(max_required, stats[2 + d]);
-      stats[1] = max_required;
-      if (max_required > capacity_rows) {
-        report_status(status, kCapacityOverflow, 0, 0, capacity_rows, max_required);
-        *num_mtiles = 0;
-      } else {
-        *num_mtiles = total_tiles;
-      }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    int max_required = 0;
+    for (int d = 0; d < world; ++d) max_required = max(max_required, stats[2 + d]);
+    stats[1] = max_required;
+    if (max_required > capacity_rows) {
+      report_status(status, kCapacityOverflow, 0, 0, capacity_rows, max_required);
+      *num_mtiles = 0;
+      *num_mtiles2 = 0;
+    } else {
+      *num_mtiles = total_tiles[0];
+      *num_mtiles2 = total_tiles[1];
     }
   }
 }
@@ -442,9 +453,10 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
                       int32_t* recv_per_expert, int32_t* recv_expert_offs,
                       int32_t* recv_seg_starts, int32_t* pull_dst_start, int32_t* stats,
                       int32_t* mtile_group, int32_t* mtile_row0, int32_t* num_mtiles,
+                      int32_t* mtile2_group, int32_t* mtile2_row0, int32_t* num_mtiles2,
                       int32_t* row_src_rank, int32_t* row_src_pos, int32_t* order_prefix,
                       int32_t* bucket_done, void* status, cudaStream_t stream) {
-  if (!order_prefix || !bucket_done) {
+  if (!order_prefix || !bucket_done || !mtile2_group || !mtile2_row0 || !num_mtiles2) {
     set_error("mm_route_finalize: null argument");
     return MM_ERR_ARG;
   }
@@ -475,7 +487,8 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
   route_finalize_kernel<<<1, 1024, smem, stream>>>(
       count_cube, rank, world, epr, bins, capacity_rows, send_bucket_starts, send_bucket_dst_starts,
       recv_counts_re, recv_per_expert, recv_expert_offs, recv_seg_starts, pull_dst_start, stats,
-      mtile_group, mtile_row0, num_mtiles, order_prefix, bucket_done,
+      mtile_group, mtile_row0, num_mtiles, mtile2_group, mtile2_row0, num_mtiles2, order_prefix,
+      bucket_done,
       reinterpret_cast<StatusRecord*>(status));
   if (int rc = check_launch("route_finalize_kernel")) return rc;
   const int nseg = world * epr;

@@ -32,6 +32,7 @@ class GemmDesc(C.Structure):
         ("b", C.c_void_p), ("b_k_major", C.c_int32), ("b_cols_total", C.c_int32),
         ("b_ld", C.c_int64), ("b_group_stride", C.c_int64),
         ("num_groups", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("grid_limit", C.c_int32),
+        ("pair", C.c_int32), ("reserved", C.c_int32),
         ("group_offs", C.c_void_p), ("mtile_group", C.c_void_p), ("mtile_row0", C.c_void_p),
         ("num_mtiles", C.c_void_p), ("status", C.c_void_p),
     ]
@@ -63,7 +64,7 @@ SIGNATURES = {
     "mm_route_local_static": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, _c_i32p,
                                         _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_ptr]),
     "mm_route_finalize": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int] +
-                          [_c_i32p] * 15 + [_c_ptr, _c_ptr]),
+                          [_c_i32p] * 18 + [_c_ptr, _c_ptr]),
     "mm_dispatch_rows": (C.c_int, [_c_ptr, C.c_int, _c_ptr, _c_i32p, _c_i32p, _c_i32p, _c_i32p,
                                    _c_i32p, _c_i32p, C.c_int, C.c_int, C.c_int, _c_ptr, _c_ptr,
                                    _c_ptr]),
@@ -77,7 +78,7 @@ SIGNATURES = {
                                           C.c_int64, _c_ptr]),
     "mm_grouped_wgrad": (C.c_int, [_c_ptr, C.c_int64, C.c_int32, _c_ptr, C.c_int64, C.c_int32,
                                    C.c_int64, _c_i32p, C.c_int32, _c_ptr, C.c_int64, C.c_int64,
-                                   _c_ptr, C.c_int32, _c_ptr]),
+                                   _c_ptr, C.c_int32, C.c_int32, _c_ptr]),
     "mm_swiglu_bwd": (C.c_int, [_c_ptr, C.c_int64, _c_ptr, C.c_int64, _c_ptr, C.c_int, _c_i32p,
                                 C.c_int, _c_ptr, C.c_int64, _c_ptr, C.c_int, C.c_float, C.c_float,
                                 C.c_float, _c_i32p, _c_i32p, _c_ptr, _c_ptr]),

@@ -51,10 +51,16 @@ def weight_operand(weight: torch.Tensor, k_dim: int, n_dim: int):
     return b_k_major, ld, weight.stride(0), weight.shape[n_dim]
 
 
+def pair_mode_enabled() -> bool:
+    """MOE_GEMM_PAIR=0 selects one CTA per 128-row tile (tcgen05 cta_group::1) instead of
+    clusters of two CTAs sharing 256-row tiles (cta_group::2, the default)."""
+    import os
+    return os.environ.get("MOE_GEMM_PAIR", "1") != "0"
+
+
 def make_desc(ctx: MoEForwardContext, a: torch.Tensor, a_rows_cap: int, lda: int,
               weight: torch.Tensor, k_dim: int, n_dim: int, n_out: int, k_extent: int,
-              *, group_offs=None, mtile_group=None, mtile_row0=None, num_mtiles=None,
-              grid_limit: int = 0) -> N.GemmDesc:
+              *, plan=None, grid_limit: int = 0) -> N.GemmDesc:
     b_k_major, ld, gs, n_total = weight_operand(weight, k_dim, n_dim)
     d = N.GemmDesc()
     d.a = a.data_ptr()
@@ -69,11 +75,17 @@ def make_desc(ctx: MoEForwardContext, a: torch.Tensor, a_rows_cap: int, lda: int
     d.N = n_out
     d.K = k_extent
     d.grid_limit = grid_limit
-    d.group_offs = (group_offs if group_offs is not None
-                    else ctx.metadata_recv_expert_offs).data_ptr()
-    d.mtile_group = (mtile_group if mtile_group is not None else ctx.mtile_group).data_ptr()
-    d.mtile_row0 = (mtile_row0 if mtile_row0 is not None else ctx.mtile_row0).data_ptr()
-    d.num_mtiles = (num_mtiles if num_mtiles is not None else ctx.num_mtiles).data_ptr()
+    d.pair = 1 if pair_mode_enabled() else 0
+    src = plan if plan is not None else ctx
+    d.group_offs = src.metadata_recv_expert_offs.data_ptr()
+    if d.pair:
+        d.mtile_group = src.mtile2_group.data_ptr()
+        d.mtile_row0 = src.mtile2_row0.data_ptr()
+        d.num_mtiles = src.num_mtiles2.data_ptr()
+    else:
+        d.mtile_group = src.mtile_group.data_ptr()
+        d.mtile_row0 = src.mtile_row0.data_ptr()
+        d.num_mtiles = src.num_mtiles.data_ptr()
     d.status = ctx.status.data_ptr()
     return d
 
@@ -172,7 +184,8 @@ def grouped_wgrad(ctx, grad_out, orig_in, rows_cap, group_offs, num_groups, out,
             grad_out.data_ptr(), grad_out.stride(0), grad_out.shape[1],
             orig_in.data_ptr(), orig_in.stride(0), orig_in.shape[1], rows_cap,
             group_offs.data_ptr(), num_groups, out.data_ptr(), out.stride(1), out.stride(0),
-            ctx.status.data_ptr(), 0, N.stream_ptr()), "mm_grouped_wgrad")
+            ctx.status.data_ptr(), 0, 1 if pair_mode_enabled() else 0, N.stream_ptr()),
+            "mm_grouped_wgrad")
     N.count_launches(1)
 
 

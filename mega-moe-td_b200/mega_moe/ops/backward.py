@@ -79,8 +79,7 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     cap = ctx.max_received_routes
     num_routes = tokens * top_k
     group_offs = plan.metadata_recv_expert_offs
-    tiles = dict(group_offs=group_offs, mtile_group=plan.mtile_group,
-                 mtile_row0=plan.mtile_row0, num_mtiles=plan.num_mtiles)
+    tiles = dict(plan=plan)
 
     # ---- stage 1: dispatch dy + FC2 input gradient ------------------------------------
     # The dy dispatch is fused into the GEMM launch (it runs even when this rank received

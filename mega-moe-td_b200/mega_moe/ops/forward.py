@@ -51,7 +51,8 @@ _PLAN_FIELDS = (
     "metadata_send_bucket_starts", "metadata_send_bucket_dst_starts", "metadata_local_stats",
     "metadata_stats", "metadata_recv_expert_offs", "metadata_recv_counts_re",
     "metadata_recv_per_expert", "mtile_group", "mtile_row0", "num_mtiles", "row_src_rank",
-    "row_src_pos", "metadata_count_row", "disp_order_prefix",
+    "row_src_pos", "metadata_count_row", "disp_order_prefix", "mtile2_group", "mtile2_row0",
+    "num_mtiles2",
 )
 
 

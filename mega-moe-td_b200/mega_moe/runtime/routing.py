@@ -85,6 +85,7 @@ def launch_routing_metadata(context: MoEForwardContext, selected_experts: torch.
         ctx.metadata_recv_expert_offs.data_ptr(), ctx.metadata_recv_seg_starts.data_ptr(),
         ctx.metadata_pull_dst_start.data_ptr(), ctx.metadata_stats.data_ptr(),
         ctx.mtile_group.data_ptr(), ctx.mtile_row0.data_ptr(), ctx.num_mtiles.data_ptr(),
+        ctx.mtile2_group.data_ptr(), ctx.mtile2_row0.data_ptr(), ctx.num_mtiles2.data_ptr(),
         ctx.row_src_rank.data_ptr(), ctx.row_src_pos.data_ptr(),
         ctx.disp_order_prefix.data_ptr(), ctx.disp_bucket_done.data_ptr(),
         ctx.status.data_ptr(), stream),

@@ -138,6 +138,9 @@ class MoEForwardContext:
     mtile_group: Optional[torch.Tensor] = None
     mtile_row0: Optional[torch.Tensor] = None
     num_mtiles: Optional[torch.Tensor] = None
+    mtile2_group: Optional[torch.Tensor] = None
+    mtile2_row0: Optional[torch.Tensor] = None
+    num_mtiles2: Optional[torch.Tensor] = None
     row_src_rank: Optional[torch.Tensor] = None
     row_src_pos: Optional[torch.Tensor] = None
     status: Optional[torch.Tensor] = None
@@ -328,6 +331,10 @@ def create_moe_forward_context(
     ctx.mtile_group = torch.zeros(max_tiles, **i32)
     ctx.mtile_row0 = torch.zeros(max_tiles, **i32)
     ctx.num_mtiles = torch.zeros(1, **i32)
+    max_tiles2 = max_received_routes // 256 + experts_per_rank + 1
+    ctx.mtile2_group = torch.zeros(max_tiles2, **i32)
+    ctx.mtile2_row0 = torch.zeros(max_tiles2, **i32)
+    ctx.num_mtiles2 = torch.zeros(1, **i32)
     ctx.row_src_rank = torch.zeros(max(max_received_routes, 1), **i32)
     ctx.row_src_pos = torch.zeros(max(max_received_routes, 1), **i32)
     ctx.status = torch.zeros(8, **i32)

@@ -10,13 +10,16 @@ from mega_moe import _native as N
 from mega_moe.ops import _launch as L
 
 
-def tile_tables(counts, device):
-    """group_offs / 128-row tile tables for per-group row counts (what mm_route_finalize builds)."""
+PAIR = 1   # GEMM mode under test: 1 = CTA pairs (cta_group::2), 0 = one CTA per tile
+
+
+def tile_tables(counts, device, tile_rows=128):
+    """group_offs / row-tile tables for per-group row counts (what mm_route_finalize builds)."""
     counts = [int(c) for c in counts]
     offs = np.r_[0, np.cumsum(counts)].astype(np.int32)
     groups, rows = [], []
     for g, c in enumerate(counts):
-        for r0 in range(0, c, 128):
+        for r0 in range(0, c, tile_rows):
             groups.append(g)
             rows.append(int(offs[g]) + r0)
     t = lambda a: torch.tensor(np.asarray(a, dtype=np.int32).reshape(-1), dtype=torch.int32,
@@ -26,7 +29,7 @@ def tile_tables(counts, device):
 
 def gemm_desc(a, weight, k_dim, n_dim, n_out, k_extent, counts, status):
     dev = a.device
-    offs, mg, mr, nm = tile_tables(counts, dev)
+    offs, mg, mr, nm = tile_tables(counts, dev, 256 if PAIR else 128)
     b_k_major, ld, gs, n_total = L.weight_operand(weight, k_dim, n_dim)
     d = N.GemmDesc()
     d.a = a.data_ptr()
@@ -41,6 +44,7 @@ def gemm_desc(a, weight, k_dim, n_dim, n_out, k_extent, counts, status):
     d.N = n_out
     d.K = k_extent
     d.grid_limit = 0
+    d.pair = PAIR
     d.group_offs = offs.data_ptr()
     d.mtile_group = mg.data_ptr()
     d.mtile_row0 = mr.data_ptr()
@@ -96,7 +100,8 @@ def run_wgrad(grad_out, orig_in, counts):
     N.check(N.lib().mm_grouped_wgrad(
         grad_out.data_ptr(), grad_out.stride(0), grad_out.shape[1], orig_in.data_ptr(),
         orig_in.stride(0), orig_in.shape[1], rows, offs.data_ptr(), groups, out.data_ptr(),
-        out.stride(1), out.stride(0), status.data_ptr(), 0, N.stream_ptr()), "mm_grouped_wgrad")
+        out.stride(1), out.stride(0), status.data_ptr(), 0, PAIR, N.stream_ptr()),
+        "mm_grouped_wgrad")
     torch.cuda.synchronize()
     assert int(status[0]) == 0, status.tolist()
     return out

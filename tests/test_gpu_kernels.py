@@ -54,6 +54,9 @@ def _finalize(cube_np, rank, world, epr, bins, capacity):
              mtile_group=torch.full((capacity // 128 + epr + 1,), -7, **i32),
              mtile_row0=torch.full((capacity // 128 + epr + 1,), -7, **i32),
              num_mtiles=torch.full((1,), -7, **i32),
+             mtile2_group=torch.full((capacity // 256 + epr + 1,), -7, **i32),
+             mtile2_row0=torch.full((capacity // 256 + epr + 1,), -7, **i32),
+             num_mtiles2=torch.full((1,), -7, **i32),
              row_src_rank=torch.full((max(capacity, 1),), -7, **i32),
              row_src_pos=torch.full((max(capacity, 1),), -7, **i32),
              order_prefix=torch.full((nb + 1,), -7, **i32),
@@ -61,7 +64,8 @@ def _finalize(cube_np, rank, world, epr, bins, capacity):
     status = torch.zeros(8, **i32)
     order = ["send_bucket_starts", "send_bucket_dst_starts", "recv_counts_re", "recv_per_expert",
              "recv_expert_offs", "recv_seg_starts", "pull_dst_start", "stats", "mtile_group",
-             "mtile_row0", "num_mtiles", "row_src_rank", "row_src_pos", "order_prefix",
+             "mtile_row0", "num_mtiles", "mtile2_group", "mtile2_row0", "num_mtiles2",
+             "row_src_rank", "row_src_pos", "order_prefix",
              "bucket_done"]
     N.check(lib.mm_route_finalize(cube.data_ptr(), rank, world, epr, bins, capacity,
                                   *[t[k].data_ptr() for k in order], status.data_ptr(),
@@ -134,6 +138,14 @@ def test_routing_metadata_bit_exact(tokens, top_k, experts, world, drop):
         assert nt == len(exp_groups)
         np.testing.assert_array_equal(got["mtile_group"][:nt], exp_groups)
         np.testing.assert_array_equal(got["mtile_row0"][:nt], exp_rows)
+        g2, r2 = [], []
+        for e in range(epr):
+            for r0 in range(0, int(want["recv_per_expert"][e]), 256):
+                g2.append(e)
+                r2.append(int(want["recv_expert_offs"][e]) + r0)
+        assert int(got["num_mtiles2"][0]) == len(g2)
+        np.testing.assert_array_equal(got["mtile2_group"][:len(g2)], g2)
+        np.testing.assert_array_equal(got["mtile2_row0"][:len(g2)], r2)
 
 
 def test_routing_capacity_overflow_sets_status():
@@ -143,8 +155,18 @@ def test_routing_capacity_overflow_sets_status():
     got, bins = _route_local(sel, 8, 2)
     out, status = _finalize(got["count_row"][None, :], 0, 1, 8, bins, 100)
     assert status[0] == 2 and status[3] == 100 and status[4] == 512
-    assert out["num_mtiles"][0] == 0
+    assert out["num_mtiles"][0] == 0 and out["num_mtiles2"][0] == 0
     assert out["stats"][1] == meta[0]["stats"][1]
+
+
+@pytest.fixture(params=[1, 0], ids=["pair", "single"])
+def gemm_mode(request):
+    """Run a GEMM test in both tcgen05 modes: CTA pairs (cta_group::2) and single CTAs."""
+    import _gpu_util
+    old = _gpu_util.PAIR
+    _gpu_util.PAIR = request.param
+    yield request.param
+    _gpu_util.PAIR = old
 
 
 GEMM_CASES = [
@@ -159,7 +181,7 @@ GEMM_CASES = [
 
 @pytest.mark.parametrize("counts,K,N", GEMM_CASES)
 @pytest.mark.parametrize("layout", ["k_major", "mn_major"])
-def test_grouped_gemm_matches_fp32(counts, K, N, layout):
+def test_grouped_gemm_matches_fp32(counts, K, N, layout, gemm_mode):
     from _gpu_util import ref_grouped, rel_err, run_grouped_gemm
     g = torch.Generator(device="cpu").manual_seed(K + N)
     rows = sum(counts)
@@ -182,7 +204,7 @@ def test_grouped_gemm_matches_fp32(counts, K, N, layout):
 @pytest.mark.parametrize("counts,H,F", [([128], 64, 128), ([70, 200, 0, 129], 256, 256),
                                         ([513, 31], 512, 384)])
 @pytest.mark.parametrize("activation", ["swiglu", "clamp_swiglu", "situglu"])
-def test_fc1_swiglu_matches_oracle_rounding(counts, H, F, activation):
+def test_fc1_swiglu_matches_oracle_rounding(counts, H, F, activation, gemm_mode):
     from _gpu_util import rel_err, run_fc1_swiglu
     g = torch.Generator(device="cpu").manual_seed(H + F)
     rows = sum(counts)
@@ -212,7 +234,7 @@ def test_fc1_swiglu_matches_oracle_rounding(counts, H, F, activation):
 @pytest.mark.parametrize("counts,Mw,Nw", [([64], 128, 256), ([128, 70], 256, 256),
                                           ([5, 0, 300, 64, 1], 384, 128),
                                           ([1000, 0, 37], 512, 768)])
-def test_grouped_wgrad_matches_fp32(counts, Mw, Nw):
+def test_grouped_wgrad_matches_fp32(counts, Mw, Nw, gemm_mode):
     from _gpu_util import rel_err, run_wgrad
     g = torch.Generator(device="cpu").manual_seed(Mw + Nw)
     rows = sum(counts)
