@@ -44,6 +44,9 @@ WORKLOADS = {
     # the per-GPU GEMM shapes of the 8-GPU run on a single GPU, for kernel tuning and ncu
     "kimi_k3_rank_share_e112_k16_t8192": dict(tokens=8192, hidden=7168, ffn=2048, experts=112,
                                               top_k=16, capacity=1.25, zipf=None),
+    # a slice of that share small enough for multi-pass ncu captures (16 experts, 1170 rows each)
+    "kimi_k3_rank_share_slice_e16_t1170": dict(tokens=1170, hidden=7168, ffn=2048, experts=16,
+                                               top_k=16, capacity=1.25, zipf=None),
     # smaller shapes for quick checks and ncu captures (not bench lines)
     "qwen3_30b_e128_k8_t4096": dict(tokens=4096, hidden=2048, ffn=768, experts=128, top_k=8,
                                     capacity=1.25, zipf=None),

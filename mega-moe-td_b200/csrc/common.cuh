@@ -153,6 +153,35 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Pair-mode loads: the data lands in this CTA's shared memory while the transaction bytes are
+// counted on the mbarrier at the same offset in the leader CTA (rank 0) of the pair, so the
+// leader's MMA warp waits on one barrier for both halves of a stage.  No multicast.
+__device__ __forceinline__ uint32_t leader_bar_addr(uint64_t* bar) {
+  return smem_u32(bar) & 0xFEFFFFFFu;   // shared::cluster address with the peer-CTA bit cleared
+}
+
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map,
+                                                 uint64_t* bar, int32_t c0, int32_t c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(leader_bar_addr(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map,
+                                                 uint64_t* bar, int32_t c0, int32_t c1,
+                                                 int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(leader_bar_addr(bar)), "r"(c0), "r"(c1),
+        "r"(c2)
+      : "memory");
+}
+
 // Tiled bulk tensor store shared -> global (3-D map), tracked by the bulk async-group.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src,
                                              int32_t c0, int32_t c1, int32_t c2) {

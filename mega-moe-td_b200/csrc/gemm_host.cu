@@ -2,6 +2,7 @@
 // four C-ABI entry points that use it (declared in include/mega_moe_b200.h).
 #include <cudaTypedefs.h>
 
+#include <stdio.h>
 #include <stdlib.h>
 
 #include <mutex>
@@ -63,8 +64,11 @@ int g_num_sms = 0;
 bool prepare_kernel() {
   static bool ok = false;
   std::call_once(g_attr_once, [] {
-    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel,
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(grouped_gemm_kernel<true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
     if (e != cudaSuccess) {
       set_error("cudaFuncSetAttribute(grouped_gemm_kernel): %s", cudaGetErrorString(e));
       return;
@@ -88,33 +92,37 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
   cfg.dynamicSmemBytes = kGemmSmemBytes;
   cfg.stream = stream;
-  // The kernel contains cta_group::2 instructions, so every launch uses clusters of two CTAs
-  // (in single-CTA mode the two CTAs of a cluster simply work on different tiles).  The grid
-  // must be even and no larger than what can be co-resident.
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  static int max_pairs = -1;
-  if (max_pairs < 0) {
-    cudaLaunchConfig_t probe = cfg;
-    probe.gridDim = dim3(g_num_sms & ~1, 1, 1);
-    int n = 0;
-    cudaError_t pe = cudaOccupancyMaxActiveClusters(&n, grouped_gemm_kernel, &probe);
-    if (pe != cudaSuccess || n <= 0) {
-      set_error("cudaOccupancyMaxActiveClusters: %s (clusters=%d)", cudaGetErrorString(pe), n);
-      return MM_ERR_CUDA;
+  cudaError_t e;
+  if (p.pair) {
+    // clusters of two CTAs: the grid must be even and no larger than what can be co-resident
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static int max_pairs = -1;
+    if (max_pairs < 0) {
+      cudaLaunchConfig_t probe = cfg;
+      probe.gridDim = dim3(g_num_sms & ~1, 1, 1);
+      int n = 0;
+      cudaError_t pe = cudaOccupancyMaxActiveClusters(&n, grouped_gemm_kernel<true>, &probe);
+      if (pe != cudaSuccess || n <= 0) {
+        set_error("cudaOccupancyMaxActiveClusters: %s (clusters=%d)", cudaGetErrorString(pe), n);
+        return MM_ERR_CUDA;
+      }
+      max_pairs = n;
     }
-    max_pairs = n;
+    grid &= ~1;
+    if (grid > 2 * max_pairs) grid = 2 * max_pairs;
+    if (grid < 2) grid = 2;
+    cfg.gridDim = dim3(grid, 1, 1);
+    e = cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<true>, tmA, tmB, tmC, p);
+  } else {
+    cfg.gridDim = dim3(grid, 1, 1);
+    e = cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<false>, tmA, tmB, tmC, p);
   }
-  grid &= ~1;
-  if (grid > 2 * max_pairs) grid = 2 * max_pairs;
-  if (grid < 2) grid = 2;
-  cfg.gridDim = dim3(grid, 1, 1);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, grouped_gemm_kernel, tmA, tmB, tmC, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("grouped_gemm_kernel launch: %s", cudaGetErrorString(e));

@@ -237,6 +237,34 @@ __device__ __forceinline__ void flush_rows_wide(const uint8_t* stg, uint32_t lan
   }
 }
 
+template <bool kPair>
+__device__ __forceinline__ void load2d(bool direct, void* dst, const CUtensorMap* map,
+                                       uint64_t* bar, int32_t c0, int32_t c1) {
+  if constexpr (kPair) {
+    if (direct) {
+      tma_load_2d_pair(dst, map, bar, c0, c1);
+      return;
+    }
+  }
+  tma_load_2d(dst, map, bar, c0, c1);
+}
+
+template <bool kPair>
+__device__ __forceinline__ void load3d(bool direct, void* dst, const CUtensorMap* map,
+                                       uint64_t* bar, int32_t c0, int32_t c1, int32_t c2) {
+  if constexpr (kPair) {
+    if (direct) {
+      tma_load_3d_pair(dst, map, bar, c0, c1, c2);
+      return;
+    }
+  }
+  tma_load_3d(dst, map, bar, c0, c1, c2);
+}
+
+// kPair selects the tile mode at compile time: the single-CTA instance contains no cluster or
+// cta_group::2 instruction and is launched without clusters; the pair instance needs clusters
+// of two.
+template <bool kPair>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
@@ -256,23 +284,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
-  const int pair = p.pair;
-  const uint32_t cta_rank = pair ? cluster_ctarank() : 0u;
+  constexpr bool pair = kPair;
+  uint32_t cta_rank = 0;
+  if constexpr (kPair) cta_rank = cluster_ctarank();
   const bool leader = cta_rank == 0;
-  const int nstages = pair ? kPairStages : kStages;
-  const int stage_bytes = pair ? kPairStageBytes : kStageBytes;
-  const int b_boxes = pair ? 2 : 4;                  // 64-column boxes of an MN-major B stage
-  const int32_t b_col_off = pair ? (int32_t)cta_rank * (kBlockN / 2) : 0;
+  constexpr int nstages = kPair ? kPairStages : kStages;
+  constexpr int stage_bytes = kPair ? kPairStageBytes : kStageBytes;
+  constexpr int b_boxes = kPair ? 2 : 4;             // 64-column boxes of an MN-major B stage
+  const int32_t b_col_off = kPair ? (int32_t)cta_rank * (kBlockN / 2) : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
-      mbar_init(&ready_bar[s], 2);
+      mbar_init(&ready_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], (pair ? 2 : 1) * kEpiWarps * 32);
+      mbar_init(&tmem_empty[a], (pair ? 2 : 1) * kEpiWarps);   // one arrival per epilogue warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -282,7 +311,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (p.tma_store) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
-    if (pair) {
+    if constexpr (kPair) {
       tmem_alloc_pair(tmem_base_slot, kTmemCols);
       tmem_relinquish_pair();
     } else {
@@ -292,7 +321,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (pair) cluster_sync();   // the peer's barriers exist before anything arrives on them
+  if constexpr (kPair) cluster_sync();   // the peer's barriers exist before anything arrives
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
 
@@ -344,14 +373,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           uint8_t* sA = stages + stage * stage_bytes;
           uint8_t* sB = sA + kStageABytes;
-          mbar_arrive_expect_tx(&full_bar[stage], stage_bytes);
+          // Pair mode: both CTAs' loads count on the leader's barrier, except for the last
+          // k-block of a ragged reduction whose tail rows each CTA must clear itself first;
+          // that block lands on the CTA's own barrier and is handed over through ready_bar.
+          const bool tail = p.kind == kGroupedReduce && ti.kcnt - kb * kBlockK < kBlockK;
+          const bool direct = pair && !tail;
+          if (direct) {
+            if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * stage_bytes);
+          } else {
+            mbar_arrive_expect_tx(&full_bar[stage], stage_bytes);
+          }
+          uint64_t* fb = &full_bar[stage];
           if (p.kind == kGroupedRows) {
             const int32_t k0 = kb * kBlockK;
-            tma_load_2d(sA, &tmA, &full_bar[stage], k0, ti.row0);
+            load2d<kPair>(direct, sA, &tmA, fb, k0, ti.row0);
             if (!p.b_mn) {
               // K-major weights: one box of 256 (or, per CTA of a pair, 128) output columns
-              tma_load_3d(sB, &tmB, &full_bar[stage], k0, ti.n0 + b_col_off, ti.group);
+              load3d<kPair>(direct, sB, &tmB, fb, k0, ti.n0 + b_col_off, ti.group);
             } else {
+#pragma unroll
               for (int i = 0; i < b_boxes; ++i) {
                 int32_t col;
                 if (p.epi == kEpiSwiglu) {
@@ -362,17 +402,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 } else {
                   col = ti.n0 + b_col_off + 64 * i;
                 }
-                tma_load_3d(sB + i * kBoxBytes, &tmB, &full_bar[stage], col, k0, ti.group);
+                load3d<kPair>(direct, sB + i * kBoxBytes, &tmB, fb, col, k0, ti.group);
               }
             }
           } else {
             const int32_t kr = ti.krow0 + kb * kBlockK;
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
-              tma_load_2d(sA + i * kBoxBytes, &tmA, &full_bar[stage], ti.row0 + 64 * i, kr);
-            for (int i = 0; i < b_boxes; ++i)
-              tma_load_3d(sB + i * kBoxBytes, &tmB, &full_bar[stage], ti.n0 + b_col_off + 64 * i,
-                          kr, 0);
+            for (int i = 0; i < 2; ++i) {
+              load2d<kPair>(direct, sA + i * kBoxBytes, &tmA, fb, ti.row0 + 64 * i, kr);
+            }
+#pragma unroll
+            for (int i = 0; i < b_boxes; ++i) {
+              const int32_t col = ti.n0 + b_col_off + 64 * i;
+              load3d<kPair>(direct, sB + i * kBoxBytes, &tmB, fb, col, kr, 0);
+            }
           }
           if (++stage == nstages) {
             stage = 0;
@@ -394,6 +437,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     bool alive = true;
+    uint32_t peer_full_phase = 0;   // per-stage parity of the peer CTA's own full barrier
+    uint32_t ready_phase = 0;       // per-stage parity of the leader's hand-over barrier
     const uint32_t a_lbo = p.a_mn ? (uint32_t)kBoxBytes : 16u;
     const uint32_t b_lbo = p.b_mn ? (uint32_t)kBoxBytes : 16u;
     const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
@@ -403,10 +448,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // In pair mode only the leader CTA owns the accumulator hand-shake and issues MMAs; the
       // peer's warp still walks the stages to prepare its half of every stage.
       if (leader) {
-        const bool ok = pair ? mbar_wait_cluster(&tmem_empty[acc], acc_phase ^ 1, abort_flag,
-                                                 p.status, kSiteTmemEmpty, acc)
-                             : mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status,
-                                         kSiteTmemEmpty, acc);
+        bool ok = true;
+        if constexpr (kPair) {
+          // cluster-scope acquire: one lane polls, the warp follows
+          if (lane == 0)
+            ok = mbar_wait_cluster(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status,
+                                   kSiteTmemEmpty, acc);
+          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        } else {
+          ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kSiteTmemEmpty, acc);
+        }
         if (!ok) {
           alive = false;
           break;
@@ -415,33 +466,46 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       const uint32_t d_tmem = tmem_base + acc * kBlockN;
       for (int kb = 0; kb < ti.num_kb; ++kb) {
-        if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kSiteSmemFull, stage)) {
-          alive = false;
-          break;
-        }
-        tc_fence_after_sync();
+        const bool tail = p.kind == kGroupedReduce && ti.kcnt - kb * kBlockK < kBlockK;
+        const bool handover = pair && tail;   // the peer prepares its half itself, then reports
         uint8_t* sA = stages + stage * stage_bytes;
-        if (p.kind == kGroupedReduce) {
-          const int32_t valid = ti.kcnt - kb * kBlockK;
-          if (valid < kBlockK) {
-            // Rows past the end of the group belong to the next group: clear them in every
-            // 64x64 box of the stage (K rows are 128 contiguous bytes in this layout).
-            const int32_t first = valid * 128;
-            for (int b = 0; b < 2 + b_boxes; ++b) {
-              uint8_t* box = sA + b * kBoxBytes;
-              for (int32_t off = first + lane * 16; off < kBoxBytes; off += 32 * 16)
-                *reinterpret_cast<uint4*>(box + off) = make_uint4(0, 0, 0, 0);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
+        if (leader || handover) {
+          // The peer's own barrier only sees the hand-over blocks, so it keeps its phases per stage.
+          uint32_t par = phase;
+          if (!leader) {
+            par = (peer_full_phase >> stage) & 1u;
+            peer_full_phase ^= 1u << stage;
           }
+          if (!mbar_wait(&full_bar[stage], par, abort_flag, p.status, kSiteSmemFull, stage)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after_sync();
         }
-        if (pair) {
-          // both CTAs report their half of the stage to the leader
-          if (lane == 0) mbar_arrive_cluster(&ready_bar[stage], 0);
-          if (leader) {
-            if (!mbar_wait_cluster(&ready_bar[stage], phase, abort_flag, p.status, kSitePairReady,
-                                   stage)) {
+        if (tail) {
+          // Rows past the end of the group belong to the next group: clear them in every
+          // 64x64 box of the stage (K rows are 128 contiguous bytes in this layout).
+          const int32_t first = (ti.kcnt - kb * kBlockK) * 128;
+          for (int b = 0; b < 2 + b_boxes; ++b) {
+            uint8_t* box = sA + b * kBoxBytes;
+            for (int32_t off = first + lane * 16; off < kBoxBytes; off += 32 * 16)
+              *reinterpret_cast<uint4*>(box + off) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+        }
+        if constexpr (kPair) if (handover) {
+          if (!leader) {
+            if (lane == 0) mbar_arrive_cluster(&ready_bar[stage], 0);
+          } else {
+            bool ok = true;
+            if (lane == 0) {
+              ok = mbar_wait_cluster(&ready_bar[stage], (ready_phase >> stage) & 1u, abort_flag,
+                                     p.status, kSitePairReady, stage);
+            }
+            ready_phase ^= 1u << stage;
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            if (!ok) {
               alive = false;
               break;
             }
@@ -455,7 +519,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint64_t b_desc = make_smem_desc(b_addr, b_lbo, 1024);
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            if (pair) {
+            if constexpr (kPair) {
               umma_f16_pair(d_tmem, a_desc + (uint64_t)(k * a_kstep),
                             b_desc + (uint64_t)(k * b_kstep), p.idesc, (kb | k) != 0 ? 1u : 0u);
             } else {
@@ -463,7 +527,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                        p.idesc, (kb | k) != 0 ? 1u : 0u);
             }
           }
-          if (pair) umma_commit_pair(&empty_bar[stage]); else umma_commit(&empty_bar[stage]);
+          if constexpr (kPair) umma_commit_pair(&empty_bar[stage]); else umma_commit(&empty_bar[stage]);
         }
         __syncwarp();
         if (++stage == nstages) {
@@ -473,7 +537,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       if (!alive) break;
       if (lane == 0 && leader) {
-        if (pair) umma_commit_pair(&tmem_full[acc]); else umma_commit(&tmem_full[acc]);
+        if constexpr (kPair) umma_commit_pair(&tmem_full[acc]); else umma_commit(&tmem_full[acc]);
       }
       __syncwarp();
       acc ^= 1;
@@ -739,7 +803,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       tc_fence_before_sync();
-      if (pair) mbar_arrive_cluster(&tmem_empty[acc], 0); else mbar_arrive(&tmem_empty[acc]);
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kPair) mbar_arrive_cluster(&tmem_empty[acc], 0); else mbar_arrive(&tmem_empty[acc]);
+      }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
@@ -749,10 +816,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   tc_fence_before_sync();
   __syncthreads();
-  if (pair) cluster_sync();   // no arrival or commit may target a CTA that has already left
+  if constexpr (kPair) cluster_sync();   // no arrival or commit may target a CTA that has left
   if (warp == 1) {
     tc_fence_after_sync();
-    if (pair) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (kPair) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
