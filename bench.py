@@ -47,6 +47,9 @@ WORKLOADS = {
     # a slice of that share small enough for multi-pass ncu captures (16 experts, 1170 rows each)
     "kimi_k3_rank_share_slice_e16_t1170": dict(tokens=1170, hidden=7168, ffn=2048, experts=16,
                                                top_k=16, capacity=1.25, zipf=None),
+    # a slice of the single-GPU headline run: 32 experts with 146 rows each (weights 2.8 GB)
+    "kimi_k3_single_gpu_slice_e32_t292": dict(tokens=292, hidden=7168, ffn=2048, experts=32,
+                                              top_k=16, capacity=1.25, zipf=None),
     # smaller shapes for quick checks and ncu captures (not bench lines)
     "qwen3_30b_e128_k8_t4096": dict(tokens=4096, hidden=2048, ffn=768, experts=128, top_k=8,
                                     capacity=1.25, zipf=None),
@@ -64,6 +67,21 @@ def measured_peaks():
         return dict(hbm_gbs=float(d["hbm_gbs"]), tflops=float(d["bf16_tflops_sustained"]),
                     source="measured")
     return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
+
+
+def measured_traffic(hidden, ffn, top_k, rows, experts_per_rank):
+    """DRAM bytes per step of the grouped GEMM from the committed ncu captures
+    (profiles/grouped_gemm_dram_traffic.json), scaled by the number of local experts; None when
+    no capture matches this shape's rows per expert within 15 %."""
+    path = REPO / "profiles" / "grouped_gemm_dram_traffic.json"
+    if not path.exists() or (hidden, ffn, top_k) != (7168, 2048, 16) or experts_per_rank <= 0:
+        return None
+    rows_per_expert = rows / experts_per_rank
+    captures = json.loads(path.read_text())["captures"]
+    best = min(captures, key=lambda key: abs(float(key) - rows_per_expert))
+    if abs(float(best) - rows_per_expert) > 0.15 * rows_per_expert:
+        return None
+    return round(captures[best]["bytes_per_expert_per_step"] * experts_per_rank)
 
 
 class ClockSampler:
@@ -329,6 +347,9 @@ def run_ours(args, w, name):
         achieved = flops / (gemm_total_ms / 1e3) / 1e12
         roofline = dict(bound="tensor", achieved=round(achieved, 1), peak=peaks["tflops"],
                         unit="TFLOP/s", frac=round(achieved / peaks["tflops"], 4), traffic=None)
+    roofline["traffic"] = measured_traffic(H, F, k, m_rows, epr)
+    roofline["traffic_unit"] = "bytes per step (six launches), ncu capture of a slice scaled by local experts"
+    roofline["algorithmic_bytes"] = bytes_alg
     roofline["kernel"] = "grouped_gemm_kernel (6 launches per step)"
     roofline["kernel_ms_per_step"] = round(gemm_total_ms, 3)
     roofline["peak_source"] = peaks["source"]
