@@ -83,9 +83,17 @@ bool prepare_kernel() {
   return true;
 }
 
+#ifdef MM_PROFILE
+unsigned long long* g_prof_buffer = nullptr;   // [grid, 16] counters of the next launches
+#endif
+
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-           const GemmParams& p, int grid_limit, cudaStream_t stream) {
+           const GemmParams& p_in, int grid_limit, cudaStream_t stream) {
   if (!prepare_kernel()) return MM_ERR_CUDA;
+  GemmParams p = p_in;
+#ifdef MM_PROFILE
+  p.prof = g_prof_buffer;
+#endif
   int grid = g_num_sms;
   if (grid_limit > 0 && grid_limit < grid) grid = grid_limit;
   cudaLaunchConfig_t cfg = {};
@@ -341,7 +349,17 @@ int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void
   p.out_group_stride = out_group_stride;
   p.status = reinterpret_cast<StatusRecord*>(status);
   p.tma_store = 1;
+  {
+    const char* env = getenv("MM_WGRAD_STORE");   // "plain" / "wide": row stores instead of TMA
+    if (env && env[0] == 'p') p.tma_store = 0;
+    if (env && env[0] == 'w') { p.tma_store = 0; p.wide_store = 1; }
+  }
   return launch(tmA, tmB, tmC, p, grid_limit, stream);
 }
+
+#ifdef MM_PROFILE
+// Instrumented builds only: where the following GEMM launches write their wait counters.
+void mm_profile_buffer(void* buffer) { mm::g_prof_buffer = reinterpret_cast<unsigned long long*>(buffer); }
+#endif
 
 }  // extern "C"

@@ -98,7 +98,25 @@ struct GemmParams {
   float* const* disp_peer_weights;    // routing-weight buffer base per rank
   int32_t* const* disp_peer_flags;    // arrival flags base per rank: [world * epr] per rank
   const int32_t* disp_my_flags;       // this rank's arrival flags
+  // MM_PROFILE builds only: [grid, 16] clock counters of the roles' waits (see prof_now)
+  unsigned long long* prof;
 };
+
+// Wait-time accounting of an instrumented build (-DMM_PROFILE): each role sums the SM clocks it
+// spends in its waits and writes them out when it leaves.  Without the macro the helpers fold
+// to constants and the counters disappear.
+__device__ __forceinline__ long long prof_now() {
+#ifdef MM_PROFILE
+  return clock64();
+#else
+  return 0;
+#endif
+}
+__device__ __forceinline__ void prof_store(const GemmParams& p, int slot, long long v) {
+#ifdef MM_PROFILE
+  if (p.prof != nullptr) p.prof[(size_t)blockIdx.x * 16 + slot] = (unsigned long long)v;
+#endif
+}
 
 __device__ __forceinline__ int32_t total_tiles(const GemmParams& p) {
   if (p.kind == kGroupedRows) return (*p.num_mtiles) * p.n_tiles;
@@ -261,6 +279,49 @@ __device__ __forceinline__ void load3d(bool direct, void* dst, const CUtensorMap
   tma_load_3d(dst, map, bar, c0, c1, c2);
 }
 
+// Order in which one CTA (or CTA pair) walks the launch's tiles.  Ragged-row GEMMs and pair
+// mode take every step-th tile.  A single-CTA ragged reduction (weight gradient) walks whole
+// units instead: a unit is one (group, 256-column n-tile) and the CTA runs all its m-tiles
+// back to back, so the unit's B operand can stay in shared memory while only A streams.
+struct TileCursor {
+  int32_t t;       // tile index understood by decode_tile
+  int32_t unit;    // unit mode: current unit
+  int32_t m;       // unit mode: m-tile inside the unit
+  int32_t step;
+  int32_t limit;
+  bool unit_mode;
+};
+
+template <bool kPair>
+__device__ __forceinline__ TileCursor cursor_begin(const GemmParams& p, int32_t ntiles) {
+  TileCursor c;
+  c.unit_mode = !kPair && p.kind == kGroupedReduce;
+  c.limit = ntiles;
+  c.m = 0;
+  if (c.unit_mode) {
+    c.unit = (int32_t)blockIdx.x;
+    c.step = (int32_t)gridDim.x;
+    c.t = c.unit * p.m_tiles;
+  } else {
+    c.unit = 0;
+    c.step = kPair ? (int32_t)(gridDim.x >> 1) : (int32_t)gridDim.x;
+    c.t = kPair ? (int32_t)(blockIdx.x >> 1) : (int32_t)blockIdx.x;
+  }
+  return c;
+}
+
+__device__ __forceinline__ void cursor_next(TileCursor& c, const GemmParams& p) {
+  if (c.unit_mode) {
+    if (++c.m == p.m_tiles) {
+      c.m = 0;
+      c.unit += c.step;
+    }
+    c.t = c.unit * p.m_tiles + c.m;
+  } else {
+    c.t += c.step;
+  }
+}
+
 // kPair selects the tile mode at compile time: the single-CTA instance contains no cluster or
 // cta_group::2 instruction and is launched without clusters; the pair instance needs clusters
 // of two.
@@ -277,6 +338,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* full_bar = bars;                         // [kMaxStages] this CTA's loads landed
   uint64_t* empty_bar = bars + kMaxStages;           // [kMaxStages] stage consumed by the MMA
   uint64_t* ready_bar = bars + 2 * kMaxStages;       // [kMaxStages] pair mode: both CTAs' stage ready
+  uint64_t* bempty_bar = ready_bar;                  // single mode: B half of a stage consumed
   uint64_t* tmem_full = bars + 3 * kMaxStages;       // [2]
   uint64_t* tmem_empty = tmem_full + 2;              // [2]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
@@ -326,8 +388,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t tmem_base = *tmem_base_slot;
 
   const int32_t ntiles = total_tiles(p);
-  const int32_t tile0 = pair ? (int32_t)(blockIdx.x >> 1) : (int32_t)blockIdx.x;
-  const int32_t tile_step = pair ? (int32_t)(gridDim.x >> 1) : (int32_t)gridDim.x;
+  // Single mode tracks the A and B halves of the stage ring separately: a ragged reduction
+  // whose group fits the ring keeps B resident over the m-tiles of a unit (see TileCursor).
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -336,12 +398,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       bool alive = true;
       int32_t ready_group = -1;
-      for (int32_t t = tile0; t < ntiles && alive; t += tile_step) {
-        const TileInfo ti = decode_tile(p, t, cta_rank);
+      int bstage = 0;          // single mode: B half of the ring, advances only when B is loaded
+      uint32_t bphase = 0;
+      long long pw_empty = 0, pw_bempty = 0, pw_flag = 0, pw_issue = 0;
+      const long long p_begin = prof_now();
+      for (TileCursor cur = cursor_begin<kPair>(p, ntiles); cur.t < cur.limit && alive;
+           cursor_next(cur, p)) {
+        const TileInfo ti = decode_tile(p, cur.t, cta_rank);
+        // B stays in shared memory over the m-tiles of a unit when the group's rows fit the ring
+        const bool resident = cur.unit_mode && ti.num_kb <= nstages;
+        const bool load_b = !resident || cur.m == 0;
         if (p.disp_src != nullptr && ti.group != ready_group) {
           // Rows of this expert are pushed by every rank's dispatch warps: wait (bounded)
           // until each source has flagged its bucket complete for this launch's epoch.
           const uint64_t t0 = globaltimer_ns();
+          const long long c0 = prof_now();
           for (int32_t src = 0; src < p.disp_world && alive; ++src) {
             const int32_t* flag = p.disp_my_flags + src * p.disp_epr + ti.group;
             uint32_t spins = 0;
@@ -362,17 +433,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
           if (!alive) break;
+          pw_flag += prof_now() - c0;
           // order the tensor-map (async proxy) reads after the flags just acquired
           asm volatile("fence.proxy.async.global;" ::: "memory");
           ready_group = ti.group;
         }
         for (int kb = 0; kb < ti.num_kb; ++kb) {
+          const long long c1 = prof_now();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kSiteSmemEmpty, stage)) {
             alive = false;
             break;
           }
+          pw_empty += prof_now() - c1;
           uint8_t* sA = stages + stage * stage_bytes;
           uint8_t* sB = sA + kStageABytes;
+          if constexpr (!kPair) {
+            sB = stages + bstage * stage_bytes + kStageABytes;
+            const long long c2 = prof_now();
+            if (load_b && !mbar_wait(&bempty_bar[bstage], bphase ^ 1, abort_flag, p.status,
+                                     kSiteSmemEmpty, 8 + bstage)) {
+              alive = false;
+              break;
+            }
+            pw_bempty += prof_now() - c2;
+          }
           // Pair mode: both CTAs' loads count on the leader's barrier, except for the last
           // k-block of a ragged reduction whose tail rows each CTA must clear itself first;
           // that block lands on the CTA's own barrier and is handed over through ready_bar.
@@ -380,10 +464,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const bool direct = pair && !tail;
           if (direct) {
             if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * stage_bytes);
-          } else {
+          } else if (pair || load_b) {
             mbar_arrive_expect_tx(&full_bar[stage], stage_bytes);
+          } else {
+            mbar_arrive_expect_tx(&full_bar[stage], kStageABytes);
           }
           uint64_t* fb = &full_bar[stage];
+          const long long c8 = prof_now();
           if (p.kind == kGroupedRows) {
             const int32_t k0 = kb * kBlockK;
             load2d<kPair>(direct, sA, &tmA, fb, k0, ti.row0);
@@ -411,11 +498,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int i = 0; i < 2; ++i) {
               load2d<kPair>(direct, sA + i * kBoxBytes, &tmA, fb, ti.row0 + 64 * i, kr);
             }
+            if (load_b) {
 #pragma unroll
-            for (int i = 0; i < b_boxes; ++i) {
-              const int32_t col = ti.n0 + b_col_off + 64 * i;
-              load3d<kPair>(direct, sB + i * kBoxBytes, &tmB, fb, col, kr, 0);
+              for (int i = 0; i < b_boxes; ++i) {
+                const int32_t col = ti.n0 + b_col_off + 64 * i;
+                load3d<kPair>(direct, sB + i * kBoxBytes, &tmB, fb, col, kr, 0);
+              }
             }
+          }
+          pw_issue += prof_now() - c8;
+          if (load_b && ++bstage == nstages) {
+            bstage = 0;
+            bphase ^= 1;
           }
           if (++stage == nstages) {
             stage = 0;
@@ -423,6 +517,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
       }
+      prof_store(p, 0, pw_empty);
+      prof_store(p, 1, pw_bempty);
+      prof_store(p, 2, pw_flag);
+      prof_store(p, 11, pw_issue);
+      prof_store(p, 12, prof_now() - p_begin);
       if (!alive) {
         // Give loads already in flight time to land before the CTA retires.
         const uint64_t t0 = globaltimer_ns();
@@ -443,10 +542,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t b_lbo = p.b_mn ? (uint32_t)kBoxBytes : 16u;
     const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
     const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
-    for (int32_t t = tile0; t < ntiles && alive; t += tile_step) {
-      const TileInfo ti = decode_tile(p, t, cta_rank);
+    int bstage = 0;    // single mode: next B slot of the ring
+    int unit_b0 = 0;   // first B slot of the resident unit in progress
+    long long mw_acc = 0, mw_full = 0, mw_tail = 0;
+    const long long m_begin = prof_now();
+    for (TileCursor cur = cursor_begin<kPair>(p, ntiles); cur.t < cur.limit && alive;
+         cursor_next(cur, p)) {
+      const TileInfo ti = decode_tile(p, cur.t, cta_rank);
+      const bool resident = cur.unit_mode && ti.num_kb <= nstages;
+      const bool fresh_b = !resident || cur.m == 0;                 // B was loaded for this tile
+      const bool release_b = !resident || cur.m == p.m_tiles - 1;   // B is not needed afterwards
+      if (resident && cur.m == 0) unit_b0 = bstage;
       // In pair mode only the leader CTA owns the accumulator hand-shake and issues MMAs; the
       // peer's warp still walks the stages to prepare its half of every stage.
+      const long long c3 = prof_now();
       if (leader) {
         bool ok = true;
         if constexpr (kPair) {
@@ -464,11 +573,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         tc_fence_after_sync();
       }
+      mw_acc += prof_now() - c3;
       const uint32_t d_tmem = tmem_base + acc * kBlockN;
       for (int kb = 0; kb < ti.num_kb; ++kb) {
         const bool tail = p.kind == kGroupedReduce && ti.kcnt - kb * kBlockK < kBlockK;
         const bool handover = pair && tail;   // the peer prepares its half itself, then reports
         uint8_t* sA = stages + stage * stage_bytes;
+        uint8_t* sB = sA + kStageABytes;
+        int bslot = stage;
+        if constexpr (!kPair) {
+          bslot = resident ? (unit_b0 + kb) % nstages : bstage;
+          sB = stages + bslot * stage_bytes + kStageABytes;
+        }
+        const long long c4 = prof_now();
         if (leader || handover) {
           // The peer's own barrier only sees the hand-over blocks, so it keeps its phases per stage.
           uint32_t par = phase;
@@ -482,17 +599,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           tc_fence_after_sync();
         }
+        const long long c5 = prof_now();
+        mw_full += c5 - c4;
         if (tail) {
           // Rows past the end of the group belong to the next group: clear them in every
           // 64x64 box of the stage (K rows are 128 contiguous bytes in this layout).
           const int32_t first = (ti.kcnt - kb * kBlockK) * 128;
           for (int b = 0; b < 2 + b_boxes; ++b) {
-            uint8_t* box = sA + b * kBoxBytes;
+            if (b >= 2 && !fresh_b) break;   // a resident B was cleared when it was loaded
+            uint8_t* box = b < 2 ? sA + b * kBoxBytes : sB + (b - 2) * kBoxBytes;
             for (int32_t off = first + lane * 16; off < kBoxBytes; off += 32 * 16)
               *reinterpret_cast<uint4*>(box + off) = make_uint4(0, 0, 0, 0);
           }
           fence_proxy_async_smem();
           __syncwarp();
+          mw_tail += prof_now() - c5;
         }
         if constexpr (kPair) if (handover) {
           if (!leader) {
@@ -514,7 +635,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         if (lane == 0 && leader) {
           const uint32_t a_addr = smem_u32(sA);
-          const uint32_t b_addr = a_addr + kStageABytes;
+          const uint32_t b_addr = smem_u32(sB);
           const uint64_t a_desc = make_smem_desc(a_addr, a_lbo, 1024);
           const uint64_t b_desc = make_smem_desc(b_addr, b_lbo, 1024);
 #pragma unroll
@@ -527,21 +648,34 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                        p.idesc, (kb | k) != 0 ? 1u : 0u);
             }
           }
-          if constexpr (kPair) umma_commit_pair(&empty_bar[stage]); else umma_commit(&empty_bar[stage]);
+          if constexpr (kPair) {
+            umma_commit_pair(&empty_bar[stage]);
+          } else {
+            umma_commit(&empty_bar[stage]);
+            if (release_b) umma_commit(&bempty_bar[bslot]);
+          }
         }
         __syncwarp();
+        if (!resident && ++bstage == nstages) bstage = 0;
         if (++stage == nstages) {
           stage = 0;
           phase ^= 1;
         }
       }
       if (!alive) break;
+      if (resident && release_b) bstage = (unit_b0 + ti.num_kb) % nstages;
       if (lane == 0 && leader) {
         if constexpr (kPair) umma_commit_pair(&tmem_full[acc]); else umma_commit(&tmem_full[acc]);
       }
       __syncwarp();
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+    }
+    if (lane == 0) {
+      prof_store(p, 3, mw_acc);
+      prof_store(p, 4, mw_full);
+      prof_store(p, 5, mw_tail);
+      prof_store(p, 6, prof_now() - m_begin);
     }
   } else if (warp >= 2 + kEpiWarps) {
     // ----------------------------- dispatch warps -----------------------------
@@ -644,9 +778,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t buf = 0;  // staging buffer the next chunk uses
-    for (int32_t t = tile0; t < ntiles; t += tile_step) {
-      const TileInfo ti = decode_tile(p, t, cta_rank);
+    long long ew_full = 0, ew_store = 0, e_tiles = 0;
+    const long long e_begin = prof_now();
+    for (TileCursor cur = cursor_begin<kPair>(p, ntiles); cur.t < cur.limit; cursor_next(cur, p)) {
+      const TileInfo ti = decode_tile(p, cur.t, cta_rank);
+      const long long c6 = prof_now();
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, kSiteTmemFull, acc)) break;
+      ew_full += prof_now() - c6;
+      ++e_tiles;
       tc_fence_after_sync();
       const int32_t row = q * 32 + lane;
       const int valid = row < ti.rows_valid;
@@ -721,8 +860,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int c = 0; c < nch; ++c) {
           uint8_t* sb = stg + buf * 4096;
           // the store issued two blocks ago from this buffer must have read it
+          const long long c7 = prof_now();
           if (lane == 0) bulk_wait_group_read<1>();
           __syncwarp();
+          ew_store += prof_now() - c7;
           if (!zero_tile) {
             tmem_ld_wait_regs(ra);
             stage_row_f32(sb, lane, ra);
@@ -812,6 +953,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     // every tensor store of this warp must have completed before the CTA retires
     if (p.tma_store && lane == 0) bulk_wait_group_all();
+    if (ew == 0 && lane == 0) {
+      prof_store(p, 7, ew_full);
+      prof_store(p, 8, ew_store);
+      prof_store(p, 9, prof_now() - e_begin);
+      prof_store(p, 10, e_tiles);
+    }
   }
 
   tc_fence_before_sync();
