@@ -50,6 +50,11 @@ WORKLOADS = {
     # a slice of the single-GPU headline run: 32 experts with 146 rows each (weights 2.8 GB)
     "kimi_k3_single_gpu_slice_e32_t292": dict(tokens=292, hidden=7168, ffn=2048, experts=32,
                                               top_k=16, capacity=1.25, zipf=None),
+    # slices with the rows per expert of the 2- and 4-GPU runs (292 and 585)
+    "kimi_k3_two_gpu_slice_e32_t584": dict(tokens=584, hidden=7168, ffn=2048, experts=32,
+                                           top_k=16, capacity=1.25, zipf=None),
+    "kimi_k3_four_gpu_slice_e32_t1170": dict(tokens=1170, hidden=7168, ffn=2048, experts=32,
+                                             top_k=16, capacity=1.25, zipf=None),
     # smaller shapes for quick checks and ncu captures (not bench lines)
     "qwen3_30b_e128_k8_t4096": dict(tokens=4096, hidden=2048, ffn=768, experts=128, top_k=8,
                                     capacity=1.25, zipf=None),

@@ -153,6 +153,15 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Ask L2 to fetch a box of a 3-D tensor map from DRAM; nothing returns to the SM.
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int32_t c0, int32_t c1,
+                                                   int32_t c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               :
+               : "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+
 // Pair-mode loads: the data lands in this CTA's shared memory while the transaction bytes are
 // counted on the mbarrier at the same offset in the leader CTA (rank 0) of the pair, so the
 // leader's MMA warp waits on one barrier for both halves of a stage.  No multicast.

@@ -7,7 +7,7 @@
 
 #include <mutex>
 
-#include "gemm_sm100.cuh"
+#include "gemm_skinny_sm100.cuh"
 #include "internal.h"
 
 namespace mm {
@@ -69,6 +69,9 @@ bool prepare_kernel() {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(grouped_gemm_kernel<true>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kGemmSmemBytes);
     if (e != cudaSuccess) {
       set_error("cudaFuncSetAttribute(grouped_gemm_kernel): %s", cudaGetErrorString(e));
       return;
@@ -93,6 +96,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   GemmParams p = p_in;
 #ifdef MM_PROFILE
   p.prof = g_prof_buffer;
+  p.prof_skip_mma = getenv("MM_PROFILE_SKIP_MMA") != nullptr;
 #endif
   int grid = g_num_sms;
   if (grid_limit > 0 && grid_limit < grid) grid = grid_limit;
@@ -134,6 +138,31 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("grouped_gemm_kernel launch: %s", cudaGetErrorString(e));
+    return MM_ERR_CUDA;
+  }
+  return MM_OK;
+}
+
+// Transposed-product kernel for groups with few rows (tile mode 2).
+int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p_in,
+                  int grid_limit, cudaStream_t stream) {
+  if (!prepare_kernel()) return MM_ERR_CUDA;
+  GemmParams p = p_in;
+#ifdef MM_PROFILE
+  p.prof = nullptr;
+  p.prof_skip_mma = getenv("MM_PROFILE_SKIP_MMA") != nullptr;
+#endif
+  int grid = g_num_sms;
+  if (grid_limit > 0 && grid_limit < grid) grid = grid_limit;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.dynamicSmemBytes = kGemmSmemBytes;
+  cfg.stream = stream;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel, tmA, tmB, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("skinny_gemm_kernel launch: %s", cudaGetErrorString(e));
     return MM_ERR_CUDA;
   }
   return MM_OK;
@@ -187,18 +216,23 @@ int grouped_rows_gemm(int epi, const mm_gemm_desc& d, GemmParams p, cudaStream_t
     set_error("grouped GEMM needs K %% 8 == 0 and N %% 32 == 0 (K=%d N=%d)", d.K, d.N);
     return MM_ERR_ARG;
   }
+  if (d.pair < 0 || d.pair > 2) {
+    set_error("grouped GEMM: tile mode %d is not one of 0 (single), 1 (pair), 2 (skinny)", d.pair);
+    return MM_ERR_ARG;
+  }
+  const bool skinny = d.pair == 2;
   CUtensorMap tmA, tmB;
   {
     uint64_t dims[2] = {(uint64_t)d.K, (uint64_t)d.a_rows_cap};
     uint64_t str[1] = {(uint64_t)d.lda * 2};
-    uint32_t box[2] = {64, (uint32_t)kBlockM};
+    uint32_t box[2] = {64, (uint32_t)(skinny ? kSkinnyRowBoxRows : kBlockM)};
     if (!encode_map(&tmA, d.a, 2, dims, str, box)) return MM_ERR_CUDA;
   }
   const int b_cols = d.b_cols_total;  // full column extent of B (2F for the packed gate|up table)
   if (d.b_k_major) {
     uint64_t dims[3] = {(uint64_t)d.K, (uint64_t)b_cols, (uint64_t)d.num_groups};
     uint64_t str[2] = {(uint64_t)d.b_ld * 2, (uint64_t)d.b_group_stride * 2};
-    uint32_t box[3] = {64, (uint32_t)(d.pair ? kBlockN / 2 : kBlockN), 1};
+    uint32_t box[3] = {64, (uint32_t)(d.pair ? kBlockN / 2 : kBlockN), 1};  // 128 rows in modes 1, 2
     if (!encode_map(&tmB, d.b, 3, dims, str, box)) return MM_ERR_CUDA;
   } else {
     uint64_t dims[3] = {(uint64_t)b_cols, (uint64_t)d.K, (uint64_t)d.num_groups};
@@ -213,7 +247,7 @@ int grouped_rows_gemm(int epi, const mm_gemm_desc& d, GemmParams p, cudaStream_t
   p.K = d.K;
   p.a_mn = 0;
   p.b_mn = d.b_k_major ? 0 : 1;
-  p.pair = d.pair ? 1 : 0;
+  p.pair = d.pair == 1 ? 1 : 0;
   p.idesc = make_idesc_bf16(p.pair ? 2 * kBlockM : kBlockM, kBlockN, 0, p.b_mn);
   p.group_offs = d.group_offs;
   p.mtile_group = d.mtile_group;
@@ -232,6 +266,14 @@ int grouped_rows_gemm(int epi, const mm_gemm_desc& d, GemmParams p, cudaStream_t
     p.swiglu_F = 0;
   }
   p.tma_store = 0;
+  if (skinny) {
+    static const int prefetch_kb = [] {
+      const char* env = getenv("MM_SKINNY_PREFETCH");   // k-blocks of L2 prefetch distance
+      return env ? atoi(env) : 0;
+    }();
+    p.prefetch_kb = prefetch_kb < 0 ? 0 : (prefetch_kb > 64 ? 64 : prefetch_kb);
+    return launch_skinny(tmA, tmB, p, d.grid_limit, stream);
+  }
   return launch(tmA, tmB, tmA, p, d.grid_limit, stream);
 }
 

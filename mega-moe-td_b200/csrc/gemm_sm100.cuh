@@ -59,6 +59,7 @@ struct GemmParams {
   int32_t tma_store;     // kGroupedReduce: output tiles leave through TMA tensor stores
   int32_t wide_store;    // row stores in 256-byte pieces (scatter over NVLink)
   int32_t pair;          // 1: cta_group::2, clusters of two CTAs, 256-row tiles
+  int32_t prefetch_kb;   // skinny kernel: k-blocks of weights requested into L2 ahead of the loads
   int32_t act;
   float act_beta;
   float act_linear_beta; // <= 0: no transform on up
@@ -100,6 +101,7 @@ struct GemmParams {
   const int32_t* disp_my_flags;       // this rank's arrival flags
   // MM_PROFILE builds only: [grid, 16] clock counters of the roles' waits (see prof_now)
   unsigned long long* prof;
+  int32_t prof_skip_mma;   // MM_PROFILE builds only: stages are freed without issuing MMAs
 };
 
 // Wait-time accounting of an instrumented build (-DMM_PROFILE): each role sums the SM clocks it
@@ -279,6 +281,132 @@ __device__ __forceinline__ void load3d(bool direct, void* dst, const CUtensorMap
   tma_load_3d(dst, map, bar, c0, c1, c2);
 }
 
+// Body of one dispatch warp of a fused launch: push this rank's send rows into the owning
+// ranks' receive buffers in dispatch order, count delivered rows per (destination, expert)
+// bucket and flag a bucket's arrival at the destination once it is complete.  Never waits.
+__device__ __forceinline__ void dispatch_warp_run(const GemmParams& p, int32_t dispatch_warp,
+                                                  uint32_t lane) {
+  if (p.disp_src != nullptr) {
+    const int32_t gid = blockIdx.x * kDispatchWarps + dispatch_warp;
+    const int32_t nd = gridDim.x * kDispatchWarps;
+    const int32_t nb = p.disp_world * p.disp_epr;
+    // buckets without rows are complete from the start
+    for (int32_t q = gid * 32 + (int32_t)lane; q < nb; q += nd * 32) {
+      const int32_t b = dispatch_order_bucket(q, p.disp_rank, p.disp_world, p.disp_epr);
+      if (p.disp_counts[b] == 0) {
+        int32_t* flag = p.disp_peer_flags[b / p.disp_epr] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch) : "memory");
+      }
+    }
+    const int32_t n_send = *p.disp_num_send;
+    const int32_t chunks = p.disp_row_bytes >> 4;
+    constexpr int kRowsPerFence = 4;   // rows pushed between two system-scope fences
+    constexpr int kBatch = 14;         // 16-byte loads in flight per lane
+    for (int32_t j0 = gid * kRowsPerFence; j0 < n_send; j0 += nd * kRowsPerFence) {
+      // Lanes 0..3 resolve one row each (their dependent table lookups overlap), then the
+      // warp copies the rows one after the other.
+      int32_t my_b = -1, my_dst = 0, my_row = 0, my_tok = 0;
+      float my_w = 0.0f;
+      if ((int32_t)lane < kRowsPerFence && j0 + (int32_t)lane < n_send) {
+        const int32_t j = j0 + (int32_t)lane;
+        // largest q with order_prefix[q] <= j (empty buckets share their successor's prefix)
+        int32_t lo = 0, hi = nb;
+        while (hi - lo > 1) {
+          const int32_t mid = (lo + hi) >> 1;
+          if (p.disp_order_prefix[mid] <= j) lo = mid; else hi = mid;
+        }
+        my_b = dispatch_order_bucket(lo, p.disp_rank, p.disp_world, p.disp_epr);
+        const int32_t in_bucket = j - p.disp_order_prefix[lo];
+        const int32_t i = p.disp_bucket_starts[my_b] + in_bucket;
+        my_dst = my_b / p.disp_epr;
+        my_row = p.disp_dst_starts[my_b] + in_bucket;
+        my_tok = p.disp_send_token[i];
+        if (p.disp_weights != nullptr) my_w = p.disp_weights[p.disp_send_route[i]];
+      }
+      int32_t bucket_of[kRowsPerFence];
+      int32_t dst_of[kRowsPerFence];
+#pragma unroll
+      for (int r = 0; r < kRowsPerFence; ++r) {
+        const int32_t b = __shfl_sync(0xffffffffu, my_b, r);
+        const int32_t dst_rank = __shfl_sync(0xffffffffu, my_dst, r);
+        const int32_t dst_row = __shfl_sync(0xffffffffu, my_row, r);
+        const int32_t tok = __shfl_sync(0xffffffffu, my_tok, r);
+        const float wgt = __shfl_sync(0xffffffffu, my_w, r);
+        bucket_of[r] = b;
+        dst_of[r] = dst_rank;
+        if (b < 0 || dst_row >= p.disp_capacity) continue;  // overflow: metadata kernel reports
+        const uint8_t* src = p.disp_src + (size_t)tok * p.disp_row_bytes;
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.disp_peer_rows[dst_rank]) +
+                       (size_t)dst_row * p.disp_row_bytes;
+        for (int32_t c0 = 0; c0 < chunks; c0 += 32 * kBatch) {
+          uint4 v[kBatch];
+#pragma unroll
+          for (int k = 0; k < kBatch; ++k) {
+            const int32_t c = c0 + k * 32 + (int32_t)lane;
+            if (c < chunks) {
+              asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(v[k].x), "=r"(v[k].y), "=r"(v[k].z), "=r"(v[k].w)
+                           : "l"(src + (size_t)c * 16));
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < kBatch; ++k) {
+            const int32_t c = c0 + k * 32 + (int32_t)lane;
+            if (c < chunks) *reinterpret_cast<uint4*>(dst + (size_t)c * 16) = v[k];
+          }
+        }
+        if (p.disp_weights != nullptr && lane == 0) p.disp_peer_weights[dst_rank][dst_row] = wgt;
+      }
+      // every lane's stores must be visible system-wide before the rows are counted
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < kRowsPerFence; ++r) {
+          const int32_t b = bucket_of[r];
+          if (b < 0) continue;
+          const int32_t done = atomicAdd(&p.disp_bucket_done[b], 1) + 1;
+          if (done == p.disp_counts[b]) {
+            __threadfence_system();
+            int32_t* flag =
+                p.disp_peer_flags[dst_of[r]] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch)
+                         : "memory");
+          }
+        }
+      }
+    }
+  }
+}
+
+// Producer side of a fused launch: wait (bounded) until every source rank has flagged the
+// rows of local expert `group` complete for this launch's epoch, then order the tensor-map
+// (async proxy) reads after the flags just acquired.  False: gave up or the CTA is aborting.
+__device__ __forceinline__ bool wait_expert_arrival(const GemmParams& p, int32_t group,
+                                                    volatile int* abort_flag) {
+  const uint64_t t0 = globaltimer_ns();
+  for (int32_t src = 0; src < p.disp_world; ++src) {
+    const int32_t* flag = p.disp_my_flags + src * p.disp_epr + group;
+    uint32_t spins = 0;
+    while (true) {
+      int32_t seen;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+      if (seen >= p.disp_epoch) break;
+      if ((++spins & 0x3f) == 0) {
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+          report_status(p.status, kWaitTimeout, kSiteDispatchFlag, src * p.disp_epr + group,
+                        p.disp_epoch, seen);
+          *abort_flag = 1;
+          return false;
+        }
+      }
+    }
+  }
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+  return true;
+}
+
 // Order in which one CTA (or CTA pair) walks the launch's tiles.  Ragged-row GEMMs and pair
 // mode take every step-th tile.  A single-CTA ragged reduction (weight gradient) walks whole
 // units instead: a unit is one (group, 256-column n-tile) and the CTA runs all its m-tiles
@@ -409,33 +537,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool resident = cur.unit_mode && ti.num_kb <= nstages;
         const bool load_b = !resident || cur.m == 0;
         if (p.disp_src != nullptr && ti.group != ready_group) {
-          // Rows of this expert are pushed by every rank's dispatch warps: wait (bounded)
-          // until each source has flagged its bucket complete for this launch's epoch.
-          const uint64_t t0 = globaltimer_ns();
           const long long c0 = prof_now();
-          for (int32_t src = 0; src < p.disp_world && alive; ++src) {
-            const int32_t* flag = p.disp_my_flags + src * p.disp_epr + ti.group;
-            uint32_t spins = 0;
-            while (true) {
-              int32_t seen;
-              asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-              if (seen >= p.disp_epoch) break;
-              if ((++spins & 0x3f) == 0) {
-                if (*abort_flag) { alive = false; break; }
-                if (globaltimer_ns() - t0 > kWaitBudgetNs) {
-                  report_status(p.status, kWaitTimeout, kSiteDispatchFlag, src * p.disp_epr + ti.group,
-                                p.disp_epoch, seen);
-                  *abort_flag = 1;
-                  alive = false;
-                  break;
-                }
-              }
-            }
+          if (!wait_expert_arrival(p, ti.group, abort_flag)) {
+            alive = false;
+            break;
           }
-          if (!alive) break;
           pw_flag += prof_now() - c0;
-          // order the tensor-map (async proxy) reads after the flags just acquired
-          asm volatile("fence.proxy.async.global;" ::: "memory");
           ready_group = ti.group;
         }
         for (int kb = 0; kb < ti.num_kb; ++kb) {
@@ -544,11 +651,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
     int bstage = 0;    // single mode: next B slot of the ring
     int unit_b0 = 0;   // first B slot of the resident unit in progress
-    long long mw_acc = 0, mw_full = 0, mw_tail = 0;
+    long long mw_acc = 0, mw_full = 0, mw_tail = 0, mw_issue = 0, mw_decode = 0;
     const long long m_begin = prof_now();
     for (TileCursor cur = cursor_begin<kPair>(p, ntiles); cur.t < cur.limit && alive;
          cursor_next(cur, p)) {
+      const long long c9 = prof_now();
       const TileInfo ti = decode_tile(p, cur.t, cta_rank);
+      mw_decode += prof_now() - c9 + (ti.num_kb & 0);
       const bool resident = cur.unit_mode && ti.num_kb <= nstages;
       const bool fresh_b = !resident || cur.m == 0;                 // B was loaded for this tile
       const bool release_b = !resident || cur.m == p.m_tiles - 1;   // B is not needed afterwards
@@ -577,6 +686,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t d_tmem = tmem_base + acc * kBlockN;
       for (int kb = 0; kb < ti.num_kb; ++kb) {
         const bool tail = p.kind == kGroupedReduce && ti.kcnt - kb * kBlockK < kBlockK;
+        const int ksteps = tail ? (ti.kcnt - kb * kBlockK + kUmmaK - 1) / kUmmaK : kBlockK / kUmmaK;
         const bool handover = pair && tail;   // the peer prepares its half itself, then reports
         uint8_t* sA = stages + stage * stage_bytes;
         uint8_t* sB = sA + kStageABytes;
@@ -604,11 +714,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (tail) {
           // Rows past the end of the group belong to the next group: clear them in every
           // 64x64 box of the stage (K rows are 128 contiguous bytes in this layout).
+          // Only the 16-row MMA steps that hold valid rows are issued, so the rows to clear end
+          // at the next multiple of 16.
           const int32_t first = (ti.kcnt - kb * kBlockK) * 128;
+          const int32_t last = ksteps * kUmmaK * 128;
           for (int b = 0; b < 2 + b_boxes; ++b) {
             if (b >= 2 && !fresh_b) break;   // a resident B was cleared when it was loaded
             uint8_t* box = b < 2 ? sA + b * kBoxBytes : sB + (b - 2) * kBoxBytes;
-            for (int32_t off = first + lane * 16; off < kBoxBytes; off += 32 * 16)
+            for (int32_t off = first + lane * 16; off < last; off += 32 * 16)
               *reinterpret_cast<uint4*>(box + off) = make_uint4(0, 0, 0, 0);
           }
           fence_proxy_async_smem();
@@ -633,6 +746,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tc_fence_after_sync();
           }
         }
+        const long long c10 = prof_now();
+#ifdef MM_PROFILE
+        if (p.prof_skip_mma) {
+          if (lane == 0) {
+            mbar_arrive(&empty_bar[stage]);
+            if (release_b) mbar_arrive(&bempty_bar[bslot]);
+          }
+        } else
+#endif
         if (lane == 0 && leader) {
           const uint32_t a_addr = smem_u32(sA);
           const uint32_t b_addr = smem_u32(sB);
@@ -640,6 +762,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint64_t b_desc = make_smem_desc(b_addr, b_lbo, 1024);
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            if (k >= ksteps) break;
             if constexpr (kPair) {
               umma_f16_pair(d_tmem, a_desc + (uint64_t)(k * a_kstep),
                             b_desc + (uint64_t)(k * b_kstep), p.idesc, (kb | k) != 0 ? 1u : 0u);
@@ -656,6 +779,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         __syncwarp();
+        mw_issue += prof_now() - c10;
         if (!resident && ++bstage == nstages) bstage = 0;
         if (++stage == nstages) {
           stage = 0;
@@ -664,6 +788,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       if (!alive) break;
       if (resident && release_b) bstage = (unit_b0 + ti.num_kb) % nstages;
+#ifdef MM_PROFILE
+      if (p.prof_skip_mma) {
+        if (lane == 0) mbar_arrive(&tmem_full[acc]);
+      } else
+#endif
       if (lane == 0 && leader) {
         if constexpr (kPair) umma_commit_pair(&tmem_full[acc]); else umma_commit(&tmem_full[acc]);
       }
@@ -676,100 +805,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       prof_store(p, 4, mw_full);
       prof_store(p, 5, mw_tail);
       prof_store(p, 6, prof_now() - m_begin);
+      prof_store(p, 13, mw_issue);
+      prof_store(p, 14, mw_decode);
     }
   } else if (warp >= 2 + kEpiWarps) {
     // ----------------------------- dispatch warps -----------------------------
-    if (p.disp_src != nullptr) {
-      const int32_t gid = blockIdx.x * kDispatchWarps + (int32_t)(warp - 2 - kEpiWarps);
-      const int32_t nd = gridDim.x * kDispatchWarps;
-      const int32_t nb = p.disp_world * p.disp_epr;
-      // buckets without rows are complete from the start
-      for (int32_t q = gid * 32 + (int32_t)lane; q < nb; q += nd * 32) {
-        const int32_t b = dispatch_order_bucket(q, p.disp_rank, p.disp_world, p.disp_epr);
-        if (p.disp_counts[b] == 0) {
-          int32_t* flag = p.disp_peer_flags[b / p.disp_epr] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
-          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch) : "memory");
-        }
-      }
-      const int32_t n_send = *p.disp_num_send;
-      const int32_t chunks = p.disp_row_bytes >> 4;
-      constexpr int kRowsPerFence = 4;   // rows pushed between two system-scope fences
-      constexpr int kBatch = 14;         // 16-byte loads in flight per lane
-      for (int32_t j0 = gid * kRowsPerFence; j0 < n_send; j0 += nd * kRowsPerFence) {
-        // Lanes 0..3 resolve one row each (their dependent table lookups overlap), then the
-        // warp copies the rows one after the other.
-        int32_t my_b = -1, my_dst = 0, my_row = 0, my_tok = 0;
-        float my_w = 0.0f;
-        if ((int32_t)lane < kRowsPerFence && j0 + (int32_t)lane < n_send) {
-          const int32_t j = j0 + (int32_t)lane;
-          // largest q with order_prefix[q] <= j (empty buckets share their successor's prefix)
-          int32_t lo = 0, hi = nb;
-          while (hi - lo > 1) {
-            const int32_t mid = (lo + hi) >> 1;
-            if (p.disp_order_prefix[mid] <= j) lo = mid; else hi = mid;
-          }
-          my_b = dispatch_order_bucket(lo, p.disp_rank, p.disp_world, p.disp_epr);
-          const int32_t in_bucket = j - p.disp_order_prefix[lo];
-          const int32_t i = p.disp_bucket_starts[my_b] + in_bucket;
-          my_dst = my_b / p.disp_epr;
-          my_row = p.disp_dst_starts[my_b] + in_bucket;
-          my_tok = p.disp_send_token[i];
-          if (p.disp_weights != nullptr) my_w = p.disp_weights[p.disp_send_route[i]];
-        }
-        int32_t bucket_of[kRowsPerFence];
-        int32_t dst_of[kRowsPerFence];
-#pragma unroll
-        for (int r = 0; r < kRowsPerFence; ++r) {
-          const int32_t b = __shfl_sync(0xffffffffu, my_b, r);
-          const int32_t dst_rank = __shfl_sync(0xffffffffu, my_dst, r);
-          const int32_t dst_row = __shfl_sync(0xffffffffu, my_row, r);
-          const int32_t tok = __shfl_sync(0xffffffffu, my_tok, r);
-          const float wgt = __shfl_sync(0xffffffffu, my_w, r);
-          bucket_of[r] = b;
-          dst_of[r] = dst_rank;
-          if (b < 0 || dst_row >= p.disp_capacity) continue;  // overflow: metadata kernel reports
-          const uint8_t* src = p.disp_src + (size_t)tok * p.disp_row_bytes;
-          uint8_t* dst = reinterpret_cast<uint8_t*>(p.disp_peer_rows[dst_rank]) +
-                         (size_t)dst_row * p.disp_row_bytes;
-          for (int32_t c0 = 0; c0 < chunks; c0 += 32 * kBatch) {
-            uint4 v[kBatch];
-#pragma unroll
-            for (int k = 0; k < kBatch; ++k) {
-              const int32_t c = c0 + k * 32 + (int32_t)lane;
-              if (c < chunks) {
-                asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(v[k].x), "=r"(v[k].y), "=r"(v[k].z), "=r"(v[k].w)
-                             : "l"(src + (size_t)c * 16));
-              }
-            }
-#pragma unroll
-            for (int k = 0; k < kBatch; ++k) {
-              const int32_t c = c0 + k * 32 + (int32_t)lane;
-              if (c < chunks) *reinterpret_cast<uint4*>(dst + (size_t)c * 16) = v[k];
-            }
-          }
-          if (p.disp_weights != nullptr && lane == 0) p.disp_peer_weights[dst_rank][dst_row] = wgt;
-        }
-        // every lane's stores must be visible system-wide before the rows are counted
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-#pragma unroll
-          for (int r = 0; r < kRowsPerFence; ++r) {
-            const int32_t b = bucket_of[r];
-            if (b < 0) continue;
-            const int32_t done = atomicAdd(&p.disp_bucket_done[b], 1) + 1;
-            if (done == p.disp_counts[b]) {
-              __threadfence_system();
-              int32_t* flag =
-                  p.disp_peer_flags[dst_of[r]] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
-              asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch)
-                           : "memory");
-            }
-          }
-        }
-      }
-    }
+    dispatch_warp_run(p, (int32_t)(warp - 2 - kEpiWarps), lane);
   } else {
     // -------------------------------- epilogue --------------------------------
     const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read

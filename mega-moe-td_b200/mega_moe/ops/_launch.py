@@ -51,12 +51,40 @@ def weight_operand(weight: torch.Tensor, k_dim: int, n_dim: int):
     return b_k_major, ld, weight.stride(0), weight.shape[n_dim]
 
 
-def pair_mode_enabled() -> bool:
-    """MOE_GEMM_PAIR=1 selects clusters of two CTAs sharing 256-row tiles (tcgen05
-    cta_group::2) instead of one CTA per 128-row tile (cta_group::1, the default: measured
-    equal on the ragged-row GEMMs and faster on the weight gradients)."""
+TILE_SINGLE, TILE_PAIR, TILE_SKINNY = 0, 1, 2
+# Expected rows per local expert up to which the transposed ("skinny") tiles are chosen.
+SKINNY_MAX_ROWS_PER_EXPERT = 256
+
+
+def gemm_tile_mode(ctx=None) -> int:
+    """Tile mode of the ragged-row GEMMs (``mm_gemm_desc.pair``).
+
+    ``MOE_GEMM_MODE`` = ``single`` (one CTA per 128x256 tile, cta_group::1), ``pair`` (clusters
+    of two CTAs sharing 256-row tiles, cta_group::2; also ``MOE_GEMM_PAIR=1``), ``skinny``
+    (transposed product: 256 output columns x up to 256 rows, the rows as the MMA's N extent in
+    steps of 16) or ``auto`` (default): skinny when the expected rows per local expert
+    (tokens x top_k x world / experts) fit one skinny tile, else single.
+    """
     import os
-    return os.environ.get("MOE_GEMM_PAIR", "0") == "1"
+    mode = os.environ.get("MOE_GEMM_MODE", "auto").lower()
+    if os.environ.get("MOE_GEMM_PAIR", "0") == "1" or mode == "pair":
+        return TILE_PAIR
+    if mode == "single":
+        return TILE_SINGLE
+    if mode == "skinny":
+        return TILE_SKINNY
+    if mode != "auto":
+        raise ValueError(f"MOE_GEMM_MODE={mode!r} is not one of auto, single, pair, skinny")
+    if ctx is None:
+        return TILE_SINGLE
+    expected = ctx.max_tokens_per_rank * ctx.top_k * ctx.world_size / max(ctx.num_experts, 1)
+    return TILE_SKINNY if expected <= SKINNY_MAX_ROWS_PER_EXPERT else TILE_SINGLE
+
+
+def pair_mode_enabled() -> bool:
+    """Weight gradients: MOE_GEMM_PAIR=1 / MOE_GEMM_MODE=pair selects CTA pairs (default: single
+    CTAs, measured faster on the weight gradients)."""
+    return gemm_tile_mode(None) == TILE_PAIR
 
 
 def make_desc(ctx: MoEForwardContext, a: torch.Tensor, a_rows_cap: int, lda: int,
@@ -76,7 +104,7 @@ def make_desc(ctx: MoEForwardContext, a: torch.Tensor, a_rows_cap: int, lda: int
     d.N = n_out
     d.K = k_extent
     d.grid_limit = grid_limit
-    d.pair = 1 if pair_mode_enabled() else 0
+    d.pair = gemm_tile_mode(ctx)
     src = plan if plan is not None else ctx
     d.group_offs = src.metadata_recv_expert_offs.data_ptr()
     if d.pair:

@@ -159,9 +159,10 @@ def test_routing_capacity_overflow_sets_status():
     assert out["stats"][1] == meta[0]["stats"][1]
 
 
-@pytest.fixture(params=[1, 0], ids=["pair", "single"])
+@pytest.fixture(params=[1, 0, 2], ids=["pair", "single", "skinny"])
 def gemm_mode(request):
-    """Run a GEMM test in both tcgen05 modes: CTA pairs (cta_group::2) and single CTAs."""
+    """Run a GEMM test in every tile mode: CTA pairs (cta_group::2), single CTAs, and the
+    transposed product for groups with few rows."""
     import _gpu_util
     old = _gpu_util.PAIR
     _gpu_util.PAIR = request.param
