@@ -15,7 +15,8 @@ CSRC = ROOT / "csrc"
 LIB_DIR = ROOT / "lib"
 LIB_PATH = LIB_DIR / "libmegamoe_sm100.so"
 SOURCES = ["abi.cu", "routing.cu", "movement.cu", "gemm_host.cu"]
-HEADERS = ["common.cuh", "gemm_sm100.cuh", "internal.h", "../../include/mega_moe_b200.h"]
+HEADERS = (sorted(p.name for p in CSRC.glob("*.cuh")) + sorted(p.name for p in CSRC.glob("*.h"))
+           + ["../../include/mega_moe_b200.h"])
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

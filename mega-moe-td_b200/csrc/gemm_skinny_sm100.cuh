@@ -250,21 +250,21 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint32_t acc_phase = 0;
     for (int32_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
       const SkinnyTile ti = skinny_tile(p, t);
-      // Per-row lookups do not depend on the accumulator: resolve them while the main loop of
-      // this tile is still running.  Lane l owns row j * 32 + l of every 32-row chunk j.
+      // Destination lookups do not depend on the accumulator: resolve them while the main loop
+      // of this tile is still running.  Lane l owns row j * 32 + l of every 32-row chunk j.
+      // (The routing weights of a fused launch arrive with the dispatched rows, so they are
+      // read only after the accumulator is complete.)
       constexpr int kMaxChunks = kSkinnyRows / 32;
       const int32_t nchunks = (ti.rows_valid + 31) >> 5;
-      float my_w[kMaxChunks];
       __nv_bfloat16* my_ptr[kMaxChunks];
 #pragma unroll
       for (int j = 0; j < kMaxChunks; ++j) {
-        my_w[j] = 0.0f;
         my_ptr[j] = nullptr;
         const int32_t r = j * 32 + (int32_t)lane;
         if (r < ti.rows_valid) {
           const int32_t row = ti.row0 + r;
           if (p.epi == kEpiSwiglu) {
-            my_w[j] = p.row_weight[row];
+            // routing weights: see below
           } else if (p.epi == kEpiScatter) {
             my_ptr[j] = p.peer_bases[p.row_dst_rank[row]] + (int64_t)p.row_dst_pos[row] * p.ld_dst;
           } else {
@@ -279,9 +279,14 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
       if (p.epi == kEpiSwiglu) {
         const int32_t f = ti.n0 + lane_col;                 // column of act, gate column of raw
-#pragma unroll
-        for (int j = 0; j < kMaxChunks; ++j) {
-          if (j >= nchunks) break;
+        // the chunk loop stays rolled (its body is large); the next chunk's routing weights are
+        // fetched while this chunk is converted
+        float w_next = (int32_t)lane < ti.rows_valid ? p.row_weight[ti.row0 + (int32_t)lane] : 0.0f;
+#pragma unroll 1
+        for (int j = 0; j < nchunks; ++j) {
+          const float w_mine = w_next;
+          const int32_t rn = (j + 1) * 32 + (int32_t)lane;
+          w_next = rn < ti.rows_valid ? p.row_weight[ti.row0 + rn] : 0.0f;
           uint32_t rg[32], ru[32];
           tmem_ld_32x32(t_acc + j * 32, rg);
           tmem_ld_32x32(t_acc + 256 + j * 32, ru);
@@ -290,7 +295,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           const int32_t cnt = min(32, ti.rows_valid - j * 32);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float w = __shfl_sync(0xffffffffu, my_w[j], i);
+            const float w = __shfl_sync(0xffffffffu, w_mine, i);
             if (i < cnt) {
               const int64_t row = (int64_t)ti.row0 + j * 32 + i;
               const float g = bf16_round(__uint_as_float(rg[i]));

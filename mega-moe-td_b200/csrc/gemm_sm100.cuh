@@ -418,7 +418,33 @@ struct TileCursor {
   int32_t step;
   int32_t limit;
   bool unit_mode;
+  // unit mode: the unit's group, first column and reduction range, looked up once per unit
+  int32_t u_group, u_n0, u_krow0, u_kcnt;
 };
+
+__device__ __forceinline__ void cursor_load_unit(TileCursor& c, const GemmParams& p) {
+  if (c.unit * p.m_tiles >= c.limit) return;
+  c.u_group = c.unit / p.n_tiles;
+  c.u_n0 = (c.unit - c.u_group * p.n_tiles) * kBlockN;
+  c.u_krow0 = p.group_offs[c.u_group];
+  c.u_kcnt = p.group_offs[c.u_group + 1] - c.u_krow0;
+}
+
+// Tile under the cursor; in unit mode it comes from the cursor's cached unit, without
+// divisions or table lookups.
+__device__ __forceinline__ TileInfo cursor_tile(const TileCursor& c, const GemmParams& p,
+                                                int32_t cta_rank) {
+  if (!c.unit_mode) return decode_tile(p, c.t, cta_rank);
+  TileInfo ti;
+  ti.group = c.u_group;
+  ti.row0 = c.m * kBlockM;
+  ti.rows_valid = max(0, min(kBlockM, p.Mw - ti.row0));
+  ti.n0 = c.u_n0;
+  ti.krow0 = c.u_krow0;
+  ti.kcnt = c.u_kcnt;
+  ti.num_kb = (ti.kcnt + kBlockK - 1) / kBlockK;
+  return ti;
+}
 
 template <bool kPair>
 __device__ __forceinline__ TileCursor cursor_begin(const GemmParams& p, int32_t ntiles) {
@@ -430,6 +456,7 @@ __device__ __forceinline__ TileCursor cursor_begin(const GemmParams& p, int32_t 
     c.unit = (int32_t)blockIdx.x;
     c.step = (int32_t)gridDim.x;
     c.t = c.unit * p.m_tiles;
+    cursor_load_unit(c, p);
   } else {
     c.unit = 0;
     c.step = kPair ? (int32_t)(gridDim.x >> 1) : (int32_t)gridDim.x;
@@ -443,11 +470,30 @@ __device__ __forceinline__ void cursor_next(TileCursor& c, const GemmParams& p) 
     if (++c.m == p.m_tiles) {
       c.m = 0;
       c.unit += c.step;
+      cursor_load_unit(c, p);
     }
     c.t = c.unit * p.m_tiles + c.m;
   } else {
     c.t += c.step;
   }
+}
+
+// Ragged reduction, last k-block of a group: rows past the group's end belong to the next
+// group.  Clear them (K rows are 128 contiguous bytes in the MN-major boxes) up to the last
+// 16-row MMA step that is issued; one warp, followed by a proxy fence so the tensor core sees
+// the zeros.
+__device__ __forceinline__ void clear_tail_rows(uint8_t* sA, uint8_t* sB, int b_boxes, bool with_b,
+                                                int32_t rows_valid, int32_t ksteps, uint32_t lane) {
+  const int32_t first = rows_valid * 128;
+  const int32_t last = ksteps * kUmmaK * 128;
+  for (int b = 0; b < 2 + b_boxes; ++b) {
+    if (b >= 2 && !with_b) break;
+    uint8_t* box = b < 2 ? sA + b * kBoxBytes : sB + (b - 2) * kBoxBytes;
+    for (int32_t off = first + (int32_t)lane * 16; off < last; off += 32 * 16)
+      *reinterpret_cast<uint4*>(box + off) = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
 }
 
 // kPair selects the tile mode at compile time: the single-CTA instance contains no cluster or
@@ -469,7 +515,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* bempty_bar = ready_bar;                  // single mode: B half of a stage consumed
   uint64_t* tmem_full = bars + 3 * kMaxStages;       // [2]
   uint64_t* tmem_empty = tmem_full + 2;              // [2]
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* fixed_bar = tmem_empty + 2;              // [kMaxStages] single mode: tail rows cleared
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(fixed_bar + kMaxStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
   const uint32_t warp = threadIdx.x >> 5;
@@ -486,8 +533,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      // single-mode ragged reduction: a stage is free once the MMA has consumed it and the
+      // tail warp has passed it, so that warp is never more than one phase behind the ring
+      mbar_init(&empty_bar[s], (!kPair && p.kind == kGroupedReduce) ? 2 : 1);
       mbar_init(&ready_bar[s], 1);
+      mbar_init(&fixed_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
@@ -532,7 +582,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const long long p_begin = prof_now();
       for (TileCursor cur = cursor_begin<kPair>(p, ntiles); cur.t < cur.limit && alive;
            cursor_next(cur, p)) {
-        const TileInfo ti = decode_tile(p, cur.t, cta_rank);
+        const TileInfo ti = cursor_tile(cur, p, cta_rank);
         // B stays in shared memory over the m-tiles of a unit when the group's rows fit the ring
         const bool resident = cur.unit_mode && ti.num_kb <= nstages;
         const bool load_b = !resident || cur.m == 0;
@@ -645,6 +695,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool alive = true;
     uint32_t peer_full_phase = 0;   // per-stage parity of the peer CTA's own full barrier
     uint32_t ready_phase = 0;       // per-stage parity of the leader's hand-over barrier
+    uint32_t fixed_phase = 0;       // per-stage parity of the tail warp's barrier (single mode)
     const uint32_t a_lbo = p.a_mn ? (uint32_t)kBoxBytes : 16u;
     const uint32_t b_lbo = p.b_mn ? (uint32_t)kBoxBytes : 16u;
     const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
@@ -656,7 +707,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (TileCursor cur = cursor_begin<kPair>(p, ntiles); cur.t < cur.limit && alive;
          cursor_next(cur, p)) {
       const long long c9 = prof_now();
-      const TileInfo ti = decode_tile(p, cur.t, cta_rank);
+      const TileInfo ti = cursor_tile(cur, p, cta_rank);
       mw_decode += prof_now() - c9 + (ti.num_kb & 0);
       const bool resident = cur.unit_mode && ti.num_kb <= nstages;
       const bool fresh_b = !resident || cur.m == 0;                 // B was loaded for this tile
@@ -712,20 +763,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const long long c5 = prof_now();
         mw_full += c5 - c4;
         if (tail) {
-          // Rows past the end of the group belong to the next group: clear them in every
-          // 64x64 box of the stage (K rows are 128 contiguous bytes in this layout).
-          // Only the 16-row MMA steps that hold valid rows are issued, so the rows to clear end
-          // at the next multiple of 16.
-          const int32_t first = (ti.kcnt - kb * kBlockK) * 128;
-          const int32_t last = ksteps * kUmmaK * 128;
-          for (int b = 0; b < 2 + b_boxes; ++b) {
-            if (b >= 2 && !fresh_b) break;   // a resident B was cleared when it was loaded
-            uint8_t* box = b < 2 ? sA + b * kBoxBytes : sB + (b - 2) * kBoxBytes;
-            for (int32_t off = first + lane * 16; off < last; off += 32 * 16)
-              *reinterpret_cast<uint4*>(box + off) = make_uint4(0, 0, 0, 0);
+          if constexpr (kPair) {
+            clear_tail_rows(sA, sB, b_boxes, fresh_b, ti.kcnt - kb * kBlockK, ksteps, lane);
+          } else {
+            // the tail warp clears the rows as soon as the block lands and reports here
+            if (!mbar_wait(&fixed_bar[stage], (fixed_phase >> stage) & 1u, abort_flag, p.status,
+                           kSiteSmemFull, 16 + stage)) {
+              alive = false;
+              break;
+            }
+            fixed_phase ^= 1u << stage;
+            tc_fence_after_sync();
           }
-          fence_proxy_async_smem();
-          __syncwarp();
           mw_tail += prof_now() - c5;
         }
         if constexpr (kPair) if (handover) {
@@ -809,8 +858,54 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       prof_store(p, 14, mw_decode);
     }
   } else if (warp >= 2 + kEpiWarps) {
-    // ----------------------------- dispatch warps -----------------------------
-    dispatch_warp_run(p, (int32_t)(warp - 2 - kEpiWarps), lane);
+    if (!kPair && p.kind == kGroupedReduce) {
+      // --------------------------------- tail warp ---------------------------------
+      // Ragged reduction in single mode: the first of the two spare warps follows the stage
+      // ring and clears the rows past the group's end in each group's last k-block, off the
+      // MMA warp's critical path.
+      if (warp == 2 + kEpiWarps) {
+        int stage = 0;
+        uint32_t phase = 0;
+        int bstage = 0;
+        int unit_b0 = 0;
+        bool alive = true;
+        for (TileCursor cur = cursor_begin<kPair>(p, ntiles); cur.t < cur.limit && alive;
+             cursor_next(cur, p)) {
+          const TileInfo ti = cursor_tile(cur, p, cta_rank);
+          const bool resident = cur.unit_mode && ti.num_kb <= nstages;
+          const bool fresh_b = !resident || cur.m == 0;
+          if (resident && cur.m == 0) unit_b0 = bstage;
+          for (int kb = 0; kb < ti.num_kb; ++kb) {
+            // Wait for every block, not only the tails: the warp must never run ahead of the
+            // data (a parity wait cannot tell a phase from the one two phases later).
+            if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kSiteSmemFull,
+                           32 + stage)) {
+              alive = false;
+              break;
+            }
+            const int32_t rows_left = ti.kcnt - kb * kBlockK;
+            if (rows_left < kBlockK) {
+              const int bslot = resident ? (unit_b0 + kb) % nstages : bstage;
+              clear_tail_rows(stages + stage * stage_bytes,
+                              stages + bslot * stage_bytes + kStageABytes, b_boxes, fresh_b,
+                              rows_left, (rows_left + kUmmaK - 1) / kUmmaK, lane);
+              if (lane == 0) mbar_arrive(&fixed_bar[stage]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);
+            if (!resident && ++bstage == nstages) bstage = 0;
+            if (++stage == nstages) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          if (resident && cur.m == p.m_tiles - 1) bstage = (unit_b0 + ti.num_kb) % nstages;
+        }
+      }
+    } else {
+      // ----------------------------- dispatch warps -----------------------------
+      dispatch_warp_run(p, (int32_t)(warp - 2 - kEpiWarps), lane);
+    }
   } else {
     // -------------------------------- epilogue --------------------------------
     const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
@@ -822,7 +917,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     long long ew_full = 0, ew_store = 0, e_tiles = 0;
     const long long e_begin = prof_now();
     for (TileCursor cur = cursor_begin<kPair>(p, ntiles); cur.t < cur.limit; cursor_next(cur, p)) {
-      const TileInfo ti = decode_tile(p, cur.t, cta_rank);
+      const TileInfo ti = cursor_tile(cur, p, cta_rank);
       const long long c6 = prof_now();
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, kSiteTmemFull, acc)) break;
       ew_full += prof_now() - c6;

@@ -15,6 +15,14 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
+@pytest.fixture(autouse=True, params=["auto", "single"])
+def tile_mode(request, monkeypatch):
+    """Every operator test runs with the automatic tile choice (the transposed "skinny" tiles at
+    these rows per expert) and with the 128-row single-CTA tiles."""
+    monkeypatch.setenv("MOE_GEMM_MODE", request.param)
+    return request.param
+
+
 def _pow2_divisor(n, cap):
     d = 16
     while d * 2 <= cap and n % (d * 2) == 0:
