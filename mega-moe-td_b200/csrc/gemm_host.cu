@@ -302,6 +302,45 @@ int mm_fc1_swiglu(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void*
   p.act_linear_beta = linear_beta;
   p.act_clamp = clamp_limit;
   if (!fill_dispatch(dispatch, p)) return MM_ERR_ARG;
+  if (d->pair == 2 && raw_out != nullptr) {
+    // Skinny mode with a raw buffer: a plain GEMM over all 2F columns stores the raw gate|up
+    // rows, a row-wise pass applies the activation (see swiglu_rows_kernel).
+    if ((d->N % 128) || (ld_raw % 8) || (ld_act % 8) || !aligned16(raw_out) || !aligned16(act_out)) {
+      set_error("fused FC1 needs F %% 128 == 0 and 16-byte aligned outputs");
+      return MM_ERR_ARG;
+    }
+    mm_gemm_desc wide = *d;
+    wide.N = 2 * d->N;
+    GemmParams g = p;
+    g.out = reinterpret_cast<__nv_bfloat16*>(raw_out);
+    g.ld_out = ld_raw;
+    g.out2 = nullptr;
+    const int rc = grouped_rows_gemm(kEpiStore, wide, g, stream);
+    if (rc != MM_OK) return rc;
+    GemmParams a{};
+    a.out = p.out;
+    a.ld_out = p.ld_out;
+    a.row_weight = row_weight;
+    a.act = activation;
+    a.act_beta = beta;
+    a.act_linear_beta = linear_beta;
+    a.act_clamp = clamp_limit;
+    a.swiglu_F = d->N;
+    a.group_offs = d->group_offs;
+    a.num_groups = d->num_groups;
+    const int max_rows = (int)(d->a_rows_cap < (int64_t)INT32_MAX ? d->a_rows_cap : INT32_MAX);
+    int blocks = g_num_sms * 8;
+    if (blocks > max_rows) blocks = max_rows;
+    if (blocks < 1) blocks = 1;
+    swiglu_rows_kernel<<<blocks, kSwigluRowsThreads, 0, stream>>>(
+        a, reinterpret_cast<const __nv_bfloat16*>(raw_out), ld_raw, max_rows);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      set_error("swiglu_rows_kernel launch: %s", cudaGetErrorString(e));
+      return MM_ERR_CUDA;
+    }
+    return MM_OK;
+  }
   return grouped_rows_gemm(kEpiSwiglu, *d, p, stream);
 }
 

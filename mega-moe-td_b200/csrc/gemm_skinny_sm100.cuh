@@ -344,4 +344,39 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   }
 }
 
+// Activation pass of the two-step FC1 (skinny mode): act[row, f] = activation(gate, up) * w[row]
+// from the raw gate|up rows a plain GEMM stored as bf16 -- the same rounding points as the
+// fused epilogue.  With few rows per expert the raw rows are a small fraction of the weight
+// traffic, and the plain GEMM reads 256 contiguous weight columns per tile instead of two
+// separate 128-column runs.  One block per row, 16-byte accesses; the number of rows is
+// group_offs[num_groups].
+constexpr int kSwigluRowsThreads = 256;
+
+__global__ void __launch_bounds__(kSwigluRowsThreads)
+swiglu_rows_kernel(const GemmParams p, const __nv_bfloat16* __restrict__ raw, int64_t ld_raw,
+                   int32_t max_rows) {
+  const int32_t n = min(p.group_offs[p.num_groups], max_rows);
+  const int32_t chunks = p.swiglu_F >> 3;
+  for (int32_t row = blockIdx.x; row < n; row += gridDim.x) {
+    const uint4* gate = reinterpret_cast<const uint4*>(raw + (int64_t)row * ld_raw);
+    const uint4* up = reinterpret_cast<const uint4*>(raw + (int64_t)row * ld_raw + p.swiglu_F);
+    uint4* act = reinterpret_cast<uint4*>(p.out + (int64_t)row * p.ld_out);
+    const float w = p.row_weight[row];
+    for (int32_t i = threadIdx.x; i < chunks; i += kSwigluRowsThreads) {
+      const uint4 g4 = gate[i];
+      const uint4 u4 = up[i];
+      const uint32_t gs[4] = {g4.x, g4.y, g4.z, g4.w};
+      const uint32_t us[4] = {u4.x, u4.y, u4.z, u4.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gs[k]));
+        const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&us[k]));
+        o[k] = pack_bf16x2(gated_activation(g.x, u.x, p) * w, gated_activation(g.y, u.y, p) * w);
+      }
+      act[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
 }  // namespace mm

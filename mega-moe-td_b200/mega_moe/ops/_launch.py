@@ -119,11 +119,17 @@ def make_desc(ctx: MoEForwardContext, a: torch.Tensor, a_rows_cap: int, lda: int
     return d
 
 
-def fused_dispatch_enabled() -> bool:
-    """MOE_FUSED_DISPATCH=0 selects the separate row-push kernel followed by a rank barrier
-    instead of the dispatch warps inside the GEMM launch (default: fused)."""
+def fused_dispatch_enabled(ctx=None) -> bool:
+    """Whether the dispatch warps ride inside the GEMM launch (FC1, FC2 input gradient) or a
+    separate row-push kernel plus a rank barrier runs first.  ``MOE_FUSED_DISPATCH`` = 1 / 0
+    forces one; by default the dispatch is fused when there are peers (the pushes cross NVLink
+    while the GEMM works) and separate on a single rank, where there is no link latency to
+    hide and the copy warps only compete with the GEMM for memory bandwidth."""
     import os
-    return os.environ.get("MOE_FUSED_DISPATCH", "1") != "0"
+    env = os.environ.get("MOE_FUSED_DISPATCH")
+    if env is not None:
+        return env != "0"
+    return ctx is None or ctx.world_size > 1
 
 
 def make_dispatch_desc(ctx: MoEForwardContext, src: torch.Tensor, weights, plan=None,
@@ -185,7 +191,8 @@ def fc1_swiglu(ctx, desc, act_out, raw_out, row_weight, activation, beta, linear
             row_weight.data_ptr(), N.ACT_IDS[activation], float(beta),
             float(linear_beta) if linear_beta is not None else 0.0, float(clamp),
             N.stream_ptr()), "mm_fc1_swiglu")
-    N.count_launches(1)
+    # skinny tiles with a raw buffer: plain GEMM + activation pass (two kernels)
+    N.count_launches(2 if (desc.pair == TILE_SKINNY and raw_out is not None) else 1)
 
 
 def grouped_gemm(desc, out, name="grouped_gemm", dispatch=None):

@@ -88,7 +88,7 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     grad_swiglu = torch.empty(max(m, 1), ffn, dtype=dtype, device=device)[:m]
     desc = L.make_desc(ctx, recv_dy, cap, hidden, fc2, k_dim=1, n_dim=2, n_out=ffn,
                        k_extent=hidden, **tiles)
-    if L.fused_dispatch_enabled():
+    if L.fused_dispatch_enabled(ctx):
         disp = L.make_dispatch_desc(ctx, dy, None, plan=plan, reset_counters=True)
     else:
         disp = None

@@ -388,7 +388,7 @@ class FusedMoEForward(torch.nn.Module):
         recv = ctx.peer_mem.view(ctx.max_received_routes, self.hidden_size)
         desc = L.make_desc(ctx, recv, ctx.max_received_routes, self.hidden_size, fc1_weight,
                            k_dim=1, n_dim=2, n_out=n_out, k_extent=self.hidden_size)
-        if L.fused_dispatch_enabled():
+        if L.fused_dispatch_enabled(ctx):
             disp = L.make_dispatch_desc(ctx, hidden_states, routing_weights)
         else:
             disp = None
@@ -461,7 +461,10 @@ class FusedMoEForward(torch.nn.Module):
         num_routes = tokens * self.top_k
         hidden = self.hidden_size
         cap = ctx.max_received_routes
-        self._ensure_activation_buffers(ffn_size, need_fc1=return_saved)
+        # Skinny tiles run FC1 in two steps (plain GEMM into the raw gate|up buffer, then the
+        # activation pass), so they need the raw buffer even when nothing is saved.
+        two_step_fc1 = L.gemm_tile_mode(ctx) == L.TILE_SKINNY
+        self._ensure_activation_buffers(ffn_size, need_fc1=return_saved or two_step_fc1)
         out = torch.empty(tokens, hidden, dtype=self.activation_dtype, device=hidden_states.device)
 
         launch_routing_metadata(ctx, selected_experts)
@@ -472,13 +475,14 @@ class FusedMoEForward(torch.nn.Module):
         recv = ctx.peer_mem.view(cap, hidden)
         fc1_desc = L.make_desc(ctx, recv, cap, hidden, gate_up_weight, k_dim=1, n_dim=2,
                                n_out=ffn_size, k_extent=hidden)
-        if L.fused_dispatch_enabled():
+        if L.fused_dispatch_enabled(ctx):
             disp = L.make_dispatch_desc(ctx, hidden_states, routing_weights)
         else:
             disp = None
             L.dispatch_rows(ctx, hidden_states, routing_weights, num_routes)
             ctx.rank_barrier()
-        L.fc1_swiglu(ctx, fc1_desc, self._act_buf, self._fc1_buf if return_saved else None,
+        L.fc1_swiglu(ctx, fc1_desc, self._act_buf,
+                     self._fc1_buf if (return_saved or two_step_fc1) else None,
                      ctx.routing_weight_mem, self.activation, self.situ_beta,
                      self.situ_linear_beta, self.clamp_limit, dispatch=disp)
         saved = None
