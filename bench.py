@@ -355,7 +355,7 @@ def run_ours(args, w, name):
     roofline["traffic"] = measured_traffic(H, F, k, m_rows, epr)
     roofline["traffic_unit"] = "bytes per step (six launches), ncu capture of a slice scaled by local experts"
     roofline["algorithmic_bytes"] = bytes_alg
-    roofline["kernel"] = "grouped_gemm_kernel (6 launches per step)"
+    roofline["kernel"] = "grouped_gemm_kernel / skinny_gemm_kernel (6 GEMM launches per step)"
     roofline["kernel_ms_per_step"] = round(gemm_total_ms, 3)
     roofline["peak_source"] = peaks["source"]
     roofline["per_launch_ms"] = {k_: round(sum(v) / len(v), 3) for k_, v in gemm_ms.items()}

@@ -122,7 +122,7 @@ int mm_route_local_static(const int32_t* selected, int num_routes, int top_k, in
  *   stats [2 + world] = {M, max over destinations, per-destination totals}
  *   mtile_group / mtile_row0 [capacity_rows / 128 + epr]   num_mtiles [1]   (128-row tiles)
  *   mtile2_group / mtile2_row0 [capacity_rows / 256 + epr]  num_mtiles2 [1]  (256-row tiles of
- *     the CTA-pair GEMM, mm_gemm_desc.pair = 1)
+ *     the CTA-pair and skinny GEMMs, mm_gemm_desc.pair = 1 or 2)
  *   row_src_rank / row_src_pos [capacity_rows]
  *   order_prefix [world * epr + 1]: prefix of the local counts in dispatch order (local expert
  *     slot outermost, destination rank rotated by `rank`), bucket_done [world * epr]: zeroed
@@ -172,8 +172,12 @@ typedef struct mm_gemm_desc {
   int32_t N;                  /* output columns (fused FC1: F) */
   int32_t K;                  /* reduction extent */
   int32_t grid_limit;         /* 0: one CTA per SM */
-  int32_t pair;               /* 1: tcgen05 cta_group::2 - clusters of two CTAs share 256-row tiles
-                                 (pass the 256-row tile table); 0: one CTA per 128-row tile */
+  int32_t pair;               /* tile mode.  0: one CTA per 128-row x 256-column tile (pass the
+                                 128-row tile table).  1: tcgen05 cta_group::2 - clusters of two
+                                 CTAs share 256-row tiles.  2: "skinny", for groups with few rows:
+                                 the product is computed transposed, 256 output columns x up to
+                                 256 rows per tile with the rows as the MMA's N extent in steps
+                                 of 16.  Modes 1 and 2 take the 256-row tile table. */
   int32_t reserved;
   const int32_t* group_offs;  /* [num_groups + 1] */
   const int32_t* mtile_group; /* from mm_route_finalize */
@@ -211,7 +215,9 @@ typedef struct mm_dispatch_desc {
  * (reference: kernels/fused_forward.py:551-876).  b is the packed [E, H, 2F] table
  * (b_k_major = 0, b_cols_total = 2F, N = F).
  *   act_out [rows, F] = bf16(f(bf16(gate), bf16(up)) * row_weight)
- *   raw_out [rows, 2F] = bf16 gate | up (may be null)
+ *   raw_out [rows, 2F] = bf16 gate | up (may be null; in tile mode 2 a non-null raw_out
+ *     selects the two-step form: a plain GEMM stores the raw rows, a row-wise pass applies
+ *     the activation - same rounding points, two launches)
  *   dispatch: null for rows already resident in `a`, else the fused dispatch above */
 int mm_fc1_swiglu(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void* act_out, int64_t ld_act, void* raw_out,
                   int64_t ld_raw, const float* row_weight, int activation, float beta,
