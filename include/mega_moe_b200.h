@@ -44,6 +44,12 @@ enum {
 /* Activation selector shared by forward and backward (reference: config.py:28-32). */
 enum { MM_ACT_SWIGLU = 0, MM_ACT_SITUGLU = 1, MM_ACT_CLAMP_SWIGLU = 2 };
 
+/* Format of saved FC1 rows (reference: config.py:179-186 `save_fc1_dtype`,
+ * kernels/fused_forward.py:877-949): raw bf16, a plain fp16 copy, or fp8 E4M3 with one fp32
+ * scale per row and per `scale_group` columns, table [rows, 2F / scale_group], gate groups
+ * first; scale = group amax / 448, an all-zero group keeps q = 0 and the scale 1 / 448. */
+enum { MM_FC1_BF16 = 0, MM_FC1_FP16 = 1, MM_FC1_FP8 = 2 };
+
 /* Device status record (32 bytes).  code: 0 ok, 1 wait timed out, 2 receive-capacity
  * overflow, 3 bad index.  Mirrors the reference's bounded-spin diagnostic record
  * (kernels/dispatch_fc2_bwd.py:23-42). */
@@ -248,12 +254,32 @@ int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void
 /* Gated-activation backward per received row (reference: kernels/swiglu_bwd.py:15-83):
  *   grad_fc1 [rows, 2F] = dGate | dUp (bf16), grad_scale [rows] = bf16(sum f(g) v(u) dC).
  * `num_rows` is read from device memory (stats[0]).  When peer_gate is not null the row's
- * grad_scale is also stored to rank row_dst_rank[row] at peer_gate[rank][row_dst_pos[row]]. */
+ * grad_scale is also stored to rank row_dst_rank[row] at peer_gate[rank][row_dst_pos[row]].
+ * fc1_out is in `fc1_format` (ld_fc1 in elements); fp8 rows are dequantised at the load with
+ * fc1_scale (reference: kernels/mega_bwd.py:3187-3205). */
 int mm_swiglu_bwd(const void* grad_act, int64_t ld_ga, const void* fc1_out, int64_t ld_fc1,
                   const void* row_scale_bf16, int ffn, const int32_t* num_rows, int max_rows,
                   void* grad_fc1, int64_t ld_gf, void* grad_scale, int activation, float beta,
                   float linear_beta, float clamp_limit, const int32_t* row_dst_rank,
-                  const int32_t* row_dst_pos, void* const* peer_gate, cudaStream_t stream);
+                  const int32_t* row_dst_pos, void* const* peer_gate, int fc1_format,
+                  const float* fc1_scale, int fc1_scale_group, cudaStream_t stream);
+
+/* ---- saved-activation formats and the recompute backward ---------------------------- */
+/* Convert the raw bf16 FC1 rows [rows, cols = 2F] to the saved format: MM_FC1_FP16 or
+ * MM_FC1_FP8 (+ scale table [rows, cols / scale_group])
+ * (reference: kernels/fused_forward.py:877-949, quantise leg of the FC1 epilogue). */
+int mm_fc1_save_convert(const void* raw_bf16, int64_t ld_raw, int cols, const int32_t* num_rows,
+                        int max_rows, int fc1_format, int scale_group, void* out, int64_t ld_out,
+                        float* scale, cudaStream_t stream);
+
+/* Recompute the weighted activation rows act [rows, F] = bf16(f(gate, up) * bf16 row scale)
+ * from saved FC1 rows of any format (reference: kernels/mega_bwd.py:1408-1465,
+ * MOE_SAVED_RECOMPUTE=1). */
+int mm_swiglu_recompute(const void* fc1_out, int64_t ld_fc1, int fc1_format, const float* fc1_scale,
+                        int fc1_scale_group, const void* row_scale_bf16, int ffn,
+                        const int32_t* num_rows, int max_rows, void* act_out, int64_t ld_act,
+                        int activation, float beta, float linear_beta, float clamp_limit,
+                        cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,9 @@
 // HBM / NVLink bound kernels around the grouped GEMMs: dispatch (row push into the
 // owning rank's receive buffer), top-k reduce (gather-sum of returned rows), the gated
 // activation backward, and the cross-rank flag barrier.
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -147,9 +150,30 @@ __device__ __forceinline__ void act_pair(float g, float u, int act, float beta, 
   }
 }
 
+// Saved FC1 rows come as bf16, fp16 (plain copy) or fp8 E4M3 with one fp32 scale per row and
+// per `group_n` columns (MM_FC1_* in the header).  Elements 2i, 2i+1 of the row part that
+// starts at column `col0`, as fp32.
+template <int kFmt>
+__device__ __forceinline__ float2 load_fc1_pair(const void* row, int col0, int i,
+                                                const float* scale_row, int group_n) {
+  const int col = col0 + 2 * i;
+  if constexpr (kFmt == MM_FC1_BF16) {
+    return __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(row)[col >> 1]);
+  } else if constexpr (kFmt == MM_FC1_FP16) {
+    return __half22float2(reinterpret_cast<const __half2*>(row)[col >> 1]);
+  } else {
+    const __nv_fp8x2_storage_t q = reinterpret_cast<const __nv_fp8x2_storage_t*>(row)[col >> 1];
+    const float2 v = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(q, __NV_E4M3)));
+    const float sc = scale_row[col / group_n];
+    return make_float2(v.x * sc, v.y * sc);
+  }
+}
+
+template <int kFmt>
 __global__ void __launch_bounds__(kSwigluBwdThreads)
 swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ grad_act, int64_t ld_ga,
-                  const __nv_bfloat16* __restrict__ fc1_out, int64_t ld_fc1,
+                  const uint8_t* __restrict__ fc1_out, int64_t fc1_row_bytes,
+                  const float* __restrict__ fc1_scale, int group_n,
                   const __nv_bfloat16* __restrict__ row_scale, int ffn,
                   const int32_t* __restrict__ num_rows, int max_rows,
                   __nv_bfloat16* __restrict__ grad_fc1, int64_t ld_gf,
@@ -159,18 +183,19 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ grad_act, int64_t ld_ga,
   __shared__ float red[kSwigluBwdThreads / 32];
   const int n = min(*num_rows, max_rows);
   const int pairs = ffn >> 1;
+  const int groups = kFmt == MM_FC1_FP8 ? (2 * ffn) / group_n : 0;
   for (int row = blockIdx.x; row < n; row += gridDim.x) {
     const __nv_bfloat162* dc = reinterpret_cast<const __nv_bfloat162*>(grad_act + (size_t)row * ld_ga);
-    const __nv_bfloat162* ga = reinterpret_cast<const __nv_bfloat162*>(fc1_out + (size_t)row * ld_fc1);
-    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(fc1_out + (size_t)row * ld_fc1 + ffn);
+    const uint8_t* raw = fc1_out + (size_t)row * fc1_row_bytes;
+    const float* srow = kFmt == MM_FC1_FP8 ? fc1_scale + (size_t)row * groups : nullptr;
     __nv_bfloat162* dg = reinterpret_cast<__nv_bfloat162*>(grad_fc1 + (size_t)row * ld_gf);
     __nv_bfloat162* du = reinterpret_cast<__nv_bfloat162*>(grad_fc1 + (size_t)row * ld_gf + ffn);
     const float sc = __bfloat162float(row_scale[row]);
     float part = 0.0f;
     for (int i = threadIdx.x; i < pairs; i += kSwigluBwdThreads) {
       const float2 c = __bfloat1622float2(dc[i]);
-      const float2 g = __bfloat1622float2(ga[i]);
-      const float2 u = __bfloat1622float2(up[i]);
+      const float2 g = load_fc1_pair<kFmt>(raw, 0, i, srow, group_n);
+      const float2 u = load_fc1_pair<kFmt>(raw, ffn, i, srow, group_n);
       float a0, d0, v0, dv0, a1, d1, v1, dv1;
       act_pair(g.x, u.x, act, beta, lbeta, clamp, a0, d0, v0, dv0);
       act_pair(g.y, u.y, act, beta, lbeta, clamp, a1, d1, v1, dv1);
@@ -192,6 +217,81 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ grad_act, int64_t ld_ga,
         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(peer_gate[row_dst_rank[row]]);
         dst[row_dst_pos[row]] = v;
       }
+    }
+  }
+}
+
+// Activation recompute of the backward (saved-recompute mode): the weighted activation rows
+// from the saved FC1 rows and the saved bf16 routing weights; fp32 intermediates, bf16 store.
+template <int kFmt>
+__global__ void __launch_bounds__(kSwigluBwdThreads)
+swiglu_recompute_kernel(const uint8_t* __restrict__ fc1_out, int64_t fc1_row_bytes,
+                        const float* __restrict__ fc1_scale, int group_n,
+                        const __nv_bfloat16* __restrict__ row_scale, int ffn,
+                        const int32_t* __restrict__ num_rows, int max_rows,
+                        __nv_bfloat16* __restrict__ act_out, int64_t ld_act, int act, float beta,
+                        float lbeta, float clamp) {
+  const int n = min(*num_rows, max_rows);
+  const int pairs = ffn >> 1;
+  const int groups = kFmt == MM_FC1_FP8 ? (2 * ffn) / group_n : 0;
+  for (int row = blockIdx.x; row < n; row += gridDim.x) {
+    const uint8_t* raw = fc1_out + (size_t)row * fc1_row_bytes;
+    const float* srow = kFmt == MM_FC1_FP8 ? fc1_scale + (size_t)row * groups : nullptr;
+    __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(act_out + (size_t)row * ld_act);
+    const float sc = __bfloat162float(row_scale[row]);
+    for (int i = threadIdx.x; i < pairs; i += kSwigluBwdThreads) {
+      const float2 g = load_fc1_pair<kFmt>(raw, 0, i, srow, group_n);
+      const float2 u = load_fc1_pair<kFmt>(raw, ffn, i, srow, group_n);
+      float a0, d0, v0, dv0, a1, d1, v1, dv1;
+      act_pair(g.x, u.x, act, beta, lbeta, clamp, a0, d0, v0, dv0);
+      act_pair(g.y, u.y, act, beta, lbeta, clamp, a1, d1, v1, dv1);
+      out[i] = __floats2bfloat162_rn(a0 * v0 * sc, a1 * v1 * sc);
+    }
+  }
+}
+
+// Saved-format conversion of the raw bf16 FC1 rows: fp16 copy, or fp8 E4M3 with one fp32
+// scale per row and per `group_n` columns (scale = amax / 448; an all-zero group keeps
+// q = 0 and the scale 1 / 448).  One warp per (row, group) for fp8, 8 warps per block.
+constexpr int kFp8Max = 448;
+
+__global__ void __launch_bounds__(256)
+fc1_to_fp16_kernel(const __nv_bfloat16* __restrict__ raw, int64_t ld_raw, int cols,
+                   const int32_t* __restrict__ num_rows, int max_rows, __half* __restrict__ out,
+                   int64_t ld_out) {
+  const int n = min(*num_rows, max_rows);
+  const int pairs = cols >> 1;
+  for (int row = blockIdx.x; row < n; row += gridDim.x) {
+    const __nv_bfloat162* src = reinterpret_cast<const __nv_bfloat162*>(raw + (size_t)row * ld_raw);
+    __half2* dst = reinterpret_cast<__half2*>(out + (size_t)row * ld_out);
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x)
+      dst[i] = __float22half2_rn(__bfloat1622float2(src[i]));
+  }
+}
+
+__global__ void __launch_bounds__(256)
+fc1_to_fp8_kernel(const __nv_bfloat16* __restrict__ raw, int64_t ld_raw, int cols, int group_n,
+                  const int32_t* __restrict__ num_rows, int max_rows, uint8_t* __restrict__ out,
+                  int64_t ld_out, float* __restrict__ scale) {
+  const int n = min(*num_rows, max_rows);
+  const int groups = cols / group_n;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int row = blockIdx.x; row < n; row += gridDim.x) {
+    const __nv_bfloat16* src = raw + (size_t)row * ld_raw;
+    uint8_t* dst = out + (size_t)row * ld_out;
+    for (int g = warp; g < groups; g += warps) {
+      const int c0 = g * group_n;
+      float amax = 0.0f;
+      for (int c = lane; c < group_n; c += 32) amax = fmaxf(amax, fabsf(__bfloat162float(src[c0 + c])));
+#pragma unroll
+      for (int k = 16; k > 0; k >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, k));
+      const float safe = amax > 0.0f ? amax : 1.0f;
+      const float inv = (float)kFp8Max / safe;
+      for (int c = lane; c < group_n; c += 32) {
+        const float x = __bfloat162float(src[c0 + c]) * inv;
+        dst[c0 + c] = (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+      }
+      if (lane == 0) scale[(size_t)row * groups + g] = safe / (float)kFp8Max;
     }
   }
 }
@@ -281,11 +381,34 @@ int mm_topk_reduce(const void* rows, int64_t ld_rows, const int32_t* route_to_se
   return check_launch("topk_reduce_kernel");
 }
 
+namespace {
+int row_blocks(int max_rows) {
+  int sms = 148;
+  mm_num_sms(&sms);
+  return max_rows < sms * 8 ? max_rows : sms * 8;
+}
+
+bool fc1_format_ok(int fmt, const void* scale, int group_n, int ffn, const char* who) {
+  if (fmt != MM_FC1_BF16 && fmt != MM_FC1_FP16 && fmt != MM_FC1_FP8) {
+    set_error("%s: unknown saved FC1 format %d", who, fmt);
+    return false;
+  }
+  if (fmt == MM_FC1_FP8 && (!scale || group_n <= 0 || (group_n % 2) || ((2 * ffn) % group_n))) {
+    set_error("%s: fp8 rows need a scale table and a group size that divides 2F", who);
+    return false;
+  }
+  return true;
+}
+
+int64_t fc1_elem_bytes(int fmt) { return fmt == MM_FC1_FP8 ? 1 : 2; }
+}  // namespace
+
 int mm_swiglu_bwd(const void* grad_act, int64_t ld_ga, const void* fc1_out, int64_t ld_fc1,
                   const void* row_scale_bf16, int ffn, const int32_t* num_rows, int max_rows,
                   void* grad_fc1, int64_t ld_gf, void* grad_scale, int activation, float beta,
                   float linear_beta, float clamp_limit, const int32_t* row_dst_rank,
-                  const int32_t* row_dst_pos, void* const* peer_gate, cudaStream_t stream) {
+                  const int32_t* row_dst_pos, void* const* peer_gate, int fc1_format,
+                  const float* fc1_scale, int fc1_scale_group, cudaStream_t stream) {
   if (!grad_act || !fc1_out || !row_scale_bf16 || !num_rows || !grad_fc1 || !grad_scale ||
       (peer_gate && (!row_dst_rank || !row_dst_pos))) {
     set_error("mm_swiglu_bwd: null argument");
@@ -295,17 +418,85 @@ int mm_swiglu_bwd(const void* grad_act, int64_t ld_ga, const void* fc1_out, int6
     set_error("mm_swiglu_bwd: ffn and leading dimensions must be even");
     return MM_ERR_ARG;
   }
+  if (!fc1_format_ok(fc1_format, fc1_scale, fc1_scale_group, ffn, "mm_swiglu_bwd")) return MM_ERR_ARG;
   if (max_rows <= 0) return MM_OK;
-  int sms = 148;
-  mm_num_sms(&sms);
-  int blocks = max_rows < sms * 8 ? max_rows : sms * 8;
-  swiglu_bwd_kernel<<<blocks, kSwigluBwdThreads, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(grad_act), ld_ga,
-      reinterpret_cast<const __nv_bfloat16*>(fc1_out), ld_fc1,
-      reinterpret_cast<const __nv_bfloat16*>(row_scale_bf16), ffn, num_rows, max_rows,
-      reinterpret_cast<__nv_bfloat16*>(grad_fc1), ld_gf, reinterpret_cast<__nv_bfloat16*>(grad_scale),
-      activation, beta, linear_beta, clamp_limit, row_dst_rank, row_dst_pos, peer_gate);
+  const int blocks = row_blocks(max_rows);
+  const int64_t row_bytes = ld_fc1 * fc1_elem_bytes(fc1_format);
+#define MM_LAUNCH_SWIGLU_BWD(FMT)                                                                  \
+  swiglu_bwd_kernel<FMT><<<blocks, kSwigluBwdThreads, 0, stream>>>(                                \
+      reinterpret_cast<const __nv_bfloat16*>(grad_act), ld_ga,                                     \
+      reinterpret_cast<const uint8_t*>(fc1_out), row_bytes, fc1_scale, fc1_scale_group,            \
+      reinterpret_cast<const __nv_bfloat16*>(row_scale_bf16), ffn, num_rows, max_rows,             \
+      reinterpret_cast<__nv_bfloat16*>(grad_fc1), ld_gf, reinterpret_cast<__nv_bfloat16*>(grad_scale), \
+      activation, beta, linear_beta, clamp_limit, row_dst_rank, row_dst_pos, peer_gate)
+  if (fc1_format == MM_FC1_BF16) MM_LAUNCH_SWIGLU_BWD(MM_FC1_BF16);
+  else if (fc1_format == MM_FC1_FP16) MM_LAUNCH_SWIGLU_BWD(MM_FC1_FP16);
+  else MM_LAUNCH_SWIGLU_BWD(MM_FC1_FP8);
+#undef MM_LAUNCH_SWIGLU_BWD
   return check_launch("swiglu_bwd_kernel");
+}
+
+int mm_swiglu_recompute(const void* fc1_out, int64_t ld_fc1, int fc1_format, const float* fc1_scale,
+                        int fc1_scale_group, const void* row_scale_bf16, int ffn,
+                        const int32_t* num_rows, int max_rows, void* act_out, int64_t ld_act,
+                        int activation, float beta, float linear_beta, float clamp_limit,
+                        cudaStream_t stream) {
+  if (!fc1_out || !row_scale_bf16 || !num_rows || !act_out) {
+    set_error("mm_swiglu_recompute: null argument");
+    return MM_ERR_ARG;
+  }
+  if (ffn <= 0 || (ffn % 2) || (ld_fc1 % 2) || (ld_act % 2)) {
+    set_error("mm_swiglu_recompute: ffn and leading dimensions must be even");
+    return MM_ERR_ARG;
+  }
+  if (!fc1_format_ok(fc1_format, fc1_scale, fc1_scale_group, ffn, "mm_swiglu_recompute"))
+    return MM_ERR_ARG;
+  if (max_rows <= 0) return MM_OK;
+  const int blocks = row_blocks(max_rows);
+  const int64_t row_bytes = ld_fc1 * fc1_elem_bytes(fc1_format);
+#define MM_LAUNCH_RECOMPUTE(FMT)                                                                   \
+  swiglu_recompute_kernel<FMT><<<blocks, kSwigluBwdThreads, 0, stream>>>(                          \
+      reinterpret_cast<const uint8_t*>(fc1_out), row_bytes, fc1_scale, fc1_scale_group,            \
+      reinterpret_cast<const __nv_bfloat16*>(row_scale_bf16), ffn, num_rows, max_rows,             \
+      reinterpret_cast<__nv_bfloat16*>(act_out), ld_act, activation, beta, linear_beta, clamp_limit)
+  if (fc1_format == MM_FC1_BF16) MM_LAUNCH_RECOMPUTE(MM_FC1_BF16);
+  else if (fc1_format == MM_FC1_FP16) MM_LAUNCH_RECOMPUTE(MM_FC1_FP16);
+  else MM_LAUNCH_RECOMPUTE(MM_FC1_FP8);
+#undef MM_LAUNCH_RECOMPUTE
+  return check_launch("swiglu_recompute_kernel");
+}
+
+int mm_fc1_save_convert(const void* raw_bf16, int64_t ld_raw, int cols, const int32_t* num_rows,
+                        int max_rows, int fc1_format, int scale_group, void* out, int64_t ld_out,
+                        float* scale, cudaStream_t stream) {
+  if (!raw_bf16 || !num_rows || !out) {
+    set_error("mm_fc1_save_convert: null argument");
+    return MM_ERR_ARG;
+  }
+  if (cols <= 0 || (cols % 2) || (ld_raw % 2) || (ld_out % 2)) {
+    set_error("mm_fc1_save_convert: column count and leading dimensions must be even");
+    return MM_ERR_ARG;
+  }
+  if (fc1_format == MM_FC1_FP8 && (!scale || scale_group <= 0 || (cols % scale_group))) {
+    set_error("mm_fc1_save_convert: fp8 needs a scale table and a group size that divides the columns");
+    return MM_ERR_ARG;
+  }
+  if (fc1_format != MM_FC1_FP8 && fc1_format != MM_FC1_FP16) {
+    set_error("mm_fc1_save_convert: the target format must be fp16 or fp8");
+    return MM_ERR_ARG;
+  }
+  if (max_rows <= 0) return MM_OK;
+  const int blocks = row_blocks(max_rows);
+  if (fc1_format == MM_FC1_FP16) {
+    fc1_to_fp16_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(raw_bf16),
+                                                   ld_raw, cols, num_rows, max_rows,
+                                                   reinterpret_cast<__half*>(out), ld_out);
+  } else {
+    fc1_to_fp8_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(raw_bf16),
+                                                  ld_raw, cols, scale_group, num_rows, max_rows,
+                                                  reinterpret_cast<uint8_t*>(out), ld_out, scale);
+  }
+  return check_launch("fc1_save_convert");
 }
 
 int mm_rank_barrier(int32_t* const* peer_flags, int rank, int world, int epoch, int phase,

@@ -81,8 +81,17 @@ SIGNATURES = {
                                    _c_ptr, C.c_int32, C.c_int32, _c_ptr]),
     "mm_swiglu_bwd": (C.c_int, [_c_ptr, C.c_int64, _c_ptr, C.c_int64, _c_ptr, C.c_int, _c_i32p,
                                 C.c_int, _c_ptr, C.c_int64, _c_ptr, C.c_int, C.c_float, C.c_float,
-                                C.c_float, _c_i32p, _c_i32p, _c_ptr, _c_ptr]),
+                                C.c_float, _c_i32p, _c_i32p, _c_ptr, C.c_int, _c_ptr, C.c_int,
+                                _c_ptr]),
+    "mm_fc1_save_convert": (C.c_int, [_c_ptr, C.c_int64, C.c_int, _c_i32p, C.c_int, C.c_int,
+                                      C.c_int, _c_ptr, C.c_int64, _c_ptr, _c_ptr]),
+    "mm_swiglu_recompute": (C.c_int, [_c_ptr, C.c_int64, C.c_int, _c_ptr, C.c_int, _c_ptr, C.c_int,
+                                      _c_i32p, C.c_int, _c_ptr, C.c_int64, C.c_int, C.c_float,
+                                      C.c_float, C.c_float, _c_ptr]),
 }
+
+# saved FC1 formats (MM_FC1_* of the header) by the reference's config string / torch dtype
+FC1_FORMAT_IDS = {"bf16": 0, "fp16": 1, "fp8": 2}
 
 _lib: Optional[C.CDLL] = None
 

@@ -163,8 +163,10 @@ def make_dispatch_desc(ctx: MoEForwardContext, src: torch.Tensor, weights, plan=
     return d
 
 
-def dispatch_rows(ctx: MoEForwardContext, src: torch.Tensor, weights, num_routes: int, plan=None):
-    """Push the send rows of ``src`` (and their routing weights) to the owning ranks."""
+def dispatch_rows(ctx: MoEForwardContext, src: torch.Tensor, weights, num_routes: int, plan=None,
+                  region: str = "peer_mem"):
+    """Push the send rows of ``src`` (and their routing weights) to the owning ranks' ``region``
+    (the receive buffer, or the re-dispatch slab of the recompute backward)."""
     p = plan if plan is not None else ctx
     _t = _timed("dispatch_rows")
     _t.__enter__()
@@ -174,7 +176,7 @@ def dispatch_rows(ctx: MoEForwardContext, src: torch.Tensor, weights, num_routes
         p.send_bucket.data_ptr(), p.metadata_send_bucket_starts.data_ptr(),
         p.metadata_send_bucket_dst_starts.data_ptr(), p.metadata_local_stats.data_ptr(),
         num_routes, ctx.experts_per_rank, ctx.max_received_routes,
-        ctx.symm.peer_table("peer_mem").data_ptr(),
+        ctx.symm.peer_table(region).data_ptr(),
         ctx.symm.peer_table("routing_weight_mem").data_ptr() if weights is not None else None,
         N.stream_ptr()), "mm_dispatch_rows")
     _t.__exit__()
@@ -235,9 +237,36 @@ def topk_reduce(rows, route_to_send, tokens, top_k, hidden, out, gate_in=None, g
     N.count_launches(1)
 
 
+def fc1_format_of(fc1_out: torch.Tensor) -> int:
+    """MM_FC1_* id of a saved FC1 tensor, from its dtype (reference: ``save_fc1_dtype``)."""
+    if fc1_out.dtype == torch.bfloat16:
+        return N.FC1_FORMAT_IDS["bf16"]
+    if fc1_out.dtype == torch.float16:
+        return N.FC1_FORMAT_IDS["fp16"]
+    if fc1_out.dtype == torch.float8_e4m3fn:
+        return N.FC1_FORMAT_IDS["fp8"]
+    raise TypeError(f"saved fc1_output must be bf16, fp16 or float8_e4m3fn, got {fc1_out.dtype}")
+
+
+def _fc1_scale_args(fc1_out, fc1_scale, scale_group, ffn):
+    fmt = fc1_format_of(fc1_out)
+    if fmt == N.FC1_FORMAT_IDS["fp8"]:
+        if fc1_scale is None or not scale_group:
+            raise ValueError("fp8 fc1_output needs fc1_output_scale and fc1_scale_group_size")
+        scale_group = int(scale_group)
+        if (fc1_scale.dtype != torch.float32 or not fc1_scale.is_contiguous()
+                or fc1_scale.shape != (fc1_out.shape[0], 2 * ffn // scale_group)):
+            raise ValueError("fc1_output_scale must be FP32 [rows, 2F // fc1_scale_group_size] "
+                             "matching the FP8 fc1_output")
+        return fmt, fc1_scale.data_ptr(), scale_group
+    return fmt, None, 0
+
+
 def swiglu_bwd(ctx, grad_act, fc1_out, row_scale, ffn, num_rows_dev, max_rows, grad_fc1,
-               grad_scale, activation, beta, linear_beta, clamp, plan=None, push_gate=True):
+               grad_scale, activation, beta, linear_beta, clamp, plan=None, push_gate=True,
+               fc1_scale=None, scale_group=0):
     p = plan if plan is not None else ctx
+    fmt, scale_ptr, scale_group = _fc1_scale_args(fc1_out, fc1_scale, scale_group, ffn)
     _t = _timed("swiglu_bwd")
     _t.__enter__()
     N.check(N.lib().mm_swiglu_bwd(
@@ -250,6 +279,31 @@ def swiglu_bwd(ctx, grad_act, fc1_out, row_scale, ffn, num_rows_dev, max_rows, g
         p.row_src_rank.data_ptr() if push_gate else None,
         p.row_src_pos.data_ptr() if push_gate else None,
         ctx.symm.peer_table("combine_gate_mem").data_ptr() if push_gate else None,
-        N.stream_ptr()), "mm_swiglu_bwd")
+        fmt, scale_ptr, scale_group, N.stream_ptr()), "mm_swiglu_bwd")
     _t.__exit__()
+    N.count_launches(1)
+
+
+def swiglu_recompute(fc1_out, row_scale, ffn, num_rows_dev, max_rows, act_out, activation, beta,
+                     linear_beta, clamp, fc1_scale=None, scale_group=0):
+    """Weighted activation rows from saved FC1 rows (backward-side recompute)."""
+    fmt, scale_ptr, scale_group = _fc1_scale_args(fc1_out, fc1_scale, scale_group, ffn)
+    with _timed("swiglu_recompute"):
+        N.check(N.lib().mm_swiglu_recompute(
+            fc1_out.data_ptr(), fc1_out.stride(0), fmt, scale_ptr, scale_group,
+            row_scale.data_ptr(), ffn, num_rows_dev.data_ptr(), max_rows,
+            act_out.data_ptr(), act_out.stride(0), N.ACT_IDS[activation],
+            float(beta if beta is not None else 1.0),
+            float(linear_beta) if linear_beta is not None else 0.0,
+            float(clamp if clamp is not None else 7.0), N.stream_ptr()), "mm_swiglu_recompute")
+    N.count_launches(1)
+
+
+def fc1_save_convert(raw, num_rows_dev, max_rows, fmt_name, scale_group, out, scale=None):
+    """Raw bf16 FC1 rows -> the saved format (fp16 copy, or fp8 E4M3 + scale table)."""
+    with _timed("fc1_save_convert"):
+        N.check(N.lib().mm_fc1_save_convert(
+            raw.data_ptr(), raw.stride(0), raw.shape[1], num_rows_dev.data_ptr(), max_rows,
+            N.FC1_FORMAT_IDS[fmt_name], int(scale_group), out.data_ptr(), out.stride(0),
+            N.ptr(scale), N.stream_ptr()), "mm_fc1_save_convert")
     N.count_launches(1)

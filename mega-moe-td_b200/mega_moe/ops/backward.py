@@ -20,7 +20,7 @@ from __future__ import annotations
 import torch
 
 from ..runtime.routing import launch_routing_metadata
-from ..runtime.workspace import context_of
+from ..runtime.workspace import context_of, saved_recompute_enabled
 from . import _launch as L
 from .forward import snapshot_plan
 
@@ -54,16 +54,28 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     """
     if grad_transport is not None:
         raise ValueError("grad_transport requires a MoonEP saved_phys, which is not implemented")
+    recompute = saved_recompute_enabled()
     recv_hidden_sorted = saved.get("recv_hidden_sorted")
-    if recv_hidden_sorted is None:
-        raise ValueError(
-            "saved is missing recv_hidden_sorted; the fused backward requires "
-            "the activation section (replay saved or return_saved=True)")
-    if recv_hidden_sorted.data_ptr() == peer_mem.data_ptr():
-        raise ValueError(
-            "saved['recv_hidden_sorted'] aliases peer_mem; the receive buffer "
-            "is single-in-flight and was overwritten after dispatch")
+    if recompute:
+        # reference: ops/backward.py:135-145, kernels/mega_bwd.py:3211-3230
+        if hidden_states is None:
+            hidden_states = saved.get("hidden_states")
+        if hidden_states is None:
+            raise ValueError("MOE_SAVED_RECOMPUTE=1 needs the forward input hidden_states "
+                             "(saved['hidden_states'] or the hidden_states argument)")
+    else:
+        if recv_hidden_sorted is None:
+            raise ValueError(
+                "saved is missing recv_hidden_sorted; the fused backward requires "
+                "the activation section (replay saved or return_saved=True)")
+        if recv_hidden_sorted.data_ptr() == peer_mem.data_ptr():
+            raise ValueError(
+                "saved['recv_hidden_sorted'] aliases peer_mem; the receive buffer "
+                "is single-in-flight and was overwritten after dispatch")
     ctx = context_of(peer_mem)
+    if recompute and ctx.redispatch_mem is None:
+        raise RuntimeError("MOE_SAVED_RECOMPUTE=1 must be set before the operator is constructed: "
+                           "its symmetric allocation holds the re-dispatch slab")
     dtype = saved["fc1_1"].dtype
     dy = dy.to(dtype).contiguous()
     tokens, hidden = dy.shape
@@ -81,6 +93,20 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     group_offs = plan.metadata_recv_expert_offs
     tiles = dict(plan=plan)
 
+    fc1_scale = saved.get("fc1_output_scale")
+    scale_group = saved.get("fc1_scale_group_size") or 0
+    activation = saved.get("activation", "swiglu") or "swiglu"
+    act_args = (activation, saved.get("situ_beta"), saved.get("situ_linear_beta"),
+                saved.get("clamp_limit"))
+
+    if recompute:
+        # Re-dispatch the forward's input rows into the slab (same maps as the forward
+        # dispatch, so the rows land in the receive layout the FC1 weight gradient expects);
+        # the barrier of stage 1 publishes them together with the dy rows.
+        L.dispatch_rows(ctx, hidden_states.to(dtype).contiguous(), None, num_routes, plan=plan,
+                        region="redispatch_mem")
+        recv_hidden_sorted = ctx.redispatch_mem.view(cap, hidden)[:m]
+
     # ---- stage 1: dispatch dy + FC2 input gradient ------------------------------------
     # The dy dispatch is fused into the GEMM launch (it runs even when this rank received
     # nothing, because its rows are other ranks' input).
@@ -88,7 +114,7 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     grad_swiglu = torch.empty(max(m, 1), ffn, dtype=dtype, device=device)[:m]
     desc = L.make_desc(ctx, recv_dy, cap, hidden, fc2, k_dim=1, n_dim=2, n_out=ffn,
                        k_extent=hidden, **tiles)
-    if L.fused_dispatch_enabled(ctx):
+    if L.fused_dispatch_enabled(ctx) and not recompute:
         disp = L.make_dispatch_desc(ctx, dy, None, plan=plan, reset_counters=True)
     else:
         disp = None
@@ -100,7 +126,14 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
 
     # ---- stage 3: FC2 weight gradient (reads the receive buffer, so it runs before the
     #      barrier of stage 4 lets peers dispatch into it again) ---------------------------
-    act = saved["swiglu_out_weighted"]
+    if recompute:
+        # weighted activation rows from the saved FC1 rows and the saved bf16 routing weights
+        act = torch.empty(max(m, 1), ffn, dtype=dtype, device=device)[:m]
+        if m > 0:
+            L.swiglu_recompute(fc1_output, saved["recv_weights_sorted"], ffn, plan.metadata_stats,
+                               m, act, *act_args, fc1_scale=fc1_scale, scale_group=scale_group)
+    else:
+        act = saved["swiglu_out_weighted"]
     grad_ws = saved.get("_grad_workspace")
     if m > 0:
         grad_fc2 = (grad_ws["grad_fc2"] if grad_ws is not None
@@ -114,9 +147,8 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     grad_gate = torch.empty(m, dtype=dtype, device=device)
     if m > 0:
         L.swiglu_bwd(ctx, grad_swiglu, fc1_output, saved["recv_weights_sorted"], ffn,
-                     plan.metadata_stats, m, grad_fc1_output, grad_gate,
-                     saved.get("activation", "swiglu") or "swiglu", saved.get("situ_beta"),
-                     saved.get("situ_linear_beta"), saved.get("clamp_limit"), plan=plan)
+                     plan.metadata_stats, m, grad_fc1_output, grad_gate, *act_args, plan=plan,
+                     fc1_scale=fc1_scale, scale_group=scale_group)
 
     # ---- stage 4: FC1 input gradient -> source ranks, then gather-sum -------------------
     if m > 0:

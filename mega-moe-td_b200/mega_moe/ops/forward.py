@@ -178,6 +178,15 @@ class FusedMoEForward(torch.nn.Module):
         if self.world_size > 1:
             torch.distributed.barrier(group=self.ep_group)
 
+    def _fc1_scale_group(self, ffn: int) -> int:
+        """Columns per fp8 scale of a saved FC1 row: half the FC1 tile width of the
+        configuration, as in the reference (ops/forward.py:612-613)."""
+        group = self.config.fc1_gemm_block_size_n // 2
+        if group <= 0 or (2 * ffn) % group or group % 2:
+            raise ValueError(f"save_fc1_dtype='fp8' needs fc1_gemm_block_size_n // 2 (= {group}) "
+                             f"to divide 2 * ffn (= {2 * ffn})")
+        return group
+
     # ===================== buffer management =====================
     def _ensure_activation_buffers(self, ffn: int, need_fc1: bool):
         cap = max(self.context.max_received_routes, 1)
@@ -514,7 +523,22 @@ class FusedMoEForward(torch.nn.Module):
             num_sent_routes = int(ctx.metadata_local_stats[0].item())
             m = num_received_routes
             sent = num_sent_routes
-        fc1_output = self._fc1_buf[:m] if self.saved_views else self._fc1_buf[:m].clone()
+        save_fmt = self.config.save_fc1_dtype
+        fc1_scale = None
+        if save_fmt == "bf16":
+            fc1_output = self._fc1_buf[:m] if self.saved_views else self._fc1_buf[:m].clone()
+        else:
+            # Saved-format pass (reference: quantise leg of the FC1 epilogue,
+            # kernels/fused_forward.py:877-949): the raw bf16 rows stay in the operator's
+            # workspace, the saved tensor is the fp16 copy or fp8 E4M3 + per-group scales.
+            dt = torch.float16 if save_fmt == "fp16" else torch.float8_e4m3fn
+            fc1_output = torch.empty(m, 2 * ffn_size, dtype=dt, device=out.device)
+            if save_fmt == "fp8":
+                fc1_scale = torch.empty(m, 2 * ffn_size // self._fc1_scale_group(ffn_size),
+                                        dtype=torch.float32, device=out.device)
+            if m > 0:
+                L.fc1_save_convert(self._fc1_buf, ctx.metadata_stats, m, save_fmt,
+                                   self._fc1_scale_group(ffn_size), fc1_output, fc1_scale)
         saved = {
             # minimal contract of the reference's single-launch forward
             # (ops/forward.py:1813-1873)
@@ -556,6 +580,9 @@ class FusedMoEForward(torch.nn.Module):
             "output": out, "dy": None,
             "_plan": plan,
         }
+        if fc1_scale is not None:
+            saved["fc1_output_scale"] = fc1_scale
+            saved["fc1_scale_group_size"] = self._fc1_scale_group(ffn_size)
         if self.persistent_weight_grads:
             saved["_grad_workspace"] = self._get_grad_workspace(ffn_size)
         return out, saved

@@ -145,6 +145,7 @@ class MoEForwardContext:
     row_src_pos: Optional[torch.Tensor] = None
     status: Optional[torch.Tensor] = None
     dispatch_flags: Optional[torch.Tensor] = None
+    redispatch_mem: Optional[torch.Tensor] = None
     disp_order_prefix: Optional[torch.Tensor] = None
     disp_bucket_done: Optional[torch.Tensor] = None
     dispatch_epoch: int = 0
@@ -235,6 +236,15 @@ def context_of(peer_mem: torch.Tensor) -> MoEForwardContext:
     return ctx
 
 
+def saved_recompute_enabled() -> bool:
+    """``MOE_SAVED_RECOMPUTE=1`` (reference: ops/backward.py:135): the backward re-dispatches the
+    forward's input rows and recomputes the weighted activation instead of reading the saved
+    ``recv_hidden_sorted`` / ``swiglu_out_weighted``.  Read when the operator is constructed
+    (the symmetric re-dispatch slab is part of its allocation) and by every backward call."""
+    import os
+    return os.environ.get("MOE_SAVED_RECOMPUTE", "0") == "1"
+
+
 def create_moe_forward_context(
     *,
     max_tokens_per_rank: int,
@@ -296,6 +306,10 @@ def create_moe_forward_context(
         "combine_gate_mem": num_routes * 2,
         "dispatch_flags": world_size * experts_per_rank * 4,
     }
+    if saved_recompute_enabled():
+        # re-dispatch slab of the recompute backward (reference: kernels/mega_bwd.py:2962-3030):
+        # the forward's input rows are pushed again into it instead of being saved
+        regions["redispatch_mem"] = max_received_routes * hidden_size * 2
     ctx.symm = SymmetricBlock(regions, rank, world_size, ep_group, device)
     ctx.peer_mem = ctx.symm.local("peer_mem", torch.bfloat16)
     ctx.routing_weight_mem = ctx.symm.local("routing_weight_mem", torch.float32)
@@ -303,6 +317,8 @@ def create_moe_forward_context(
     ctx.combine_mem = ctx.symm.local("combine_mem", torch.bfloat16).view(num_routes, hidden_size)
     ctx.combine_gate_mem = ctx.symm.local("combine_gate_mem", torch.bfloat16)
     ctx.dispatch_flags = ctx.symm.local("dispatch_flags", torch.int32)
+    ctx.redispatch_mem = (ctx.symm.local("redispatch_mem", torch.bfloat16)
+                          if "redispatch_mem" in regions else None)
 
     num_buckets = world_size * experts_per_rank
     bins = next_power_of_2(num_buckets)

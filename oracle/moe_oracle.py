@@ -439,6 +439,56 @@ def swiglu_bwd(grad_swiglu, s):
     return grad_fc1_output, grad_gate
 
 
+# ---------------------------------------------------------------------------------------
+# saved-activation formats and the recompute backward.  The reference implements these only
+# in its Triton-Ascend kernels, which cannot run here, so this part restates the kernel source
+# and is NOT pinned by reference outputs ("parity unpinned" for these four functions); the
+# bounds the reference's own tests place on them are checked in tests/test_oracle_formats.py.
+# ---------------------------------------------------------------------------------------
+FP8_E4M3_MAX = 448.0
+
+
+@torch.no_grad()
+def quantize_fc1_fp8(raw: torch.Tensor, group_n: int):
+    """fp8 E4M3 save of raw FC1 rows [rows, 2F] (kernels/fused_forward.py:905-949): one fp32
+    scale per row and per ``group_n`` columns; q = e4m3(x * (448 / amax)), scale = amax / 448;
+    an all-zero group keeps q = 0 and the scale 1 / 448."""
+    rows, cols = raw.shape
+    x = raw.float().view(rows, cols // group_n, group_n)
+    amax = x.abs().amax(dim=-1)
+    safe = torch.where(amax > 0, amax, torch.ones_like(amax))
+    inv = torch.tensor(FP8_E4M3_MAX, dtype=torch.float32) / safe
+    q = (x * inv[:, :, None]).to(torch.float8_e4m3fn).view(rows, cols)
+    return q, safe / torch.tensor(FP8_E4M3_MAX, dtype=torch.float32)
+
+
+@torch.no_grad()
+def dequantize_fc1(fc1: torch.Tensor, scale=None, group_n: int = 0) -> torch.Tensor:
+    """fp32 values of saved FC1 rows in any format, as the backward loads them
+    (kernels/mega_bwd.py:1436-1443, 3187-3205)."""
+    if fc1.dtype != torch.float8_e4m3fn:
+        return fc1.float()
+    rows, cols = fc1.shape
+    return (fc1.float().view(rows, cols // group_n, group_n) * scale[:, :, None]).view(rows, cols)
+
+
+@torch.no_grad()
+def convert_fc1_fp16(raw: torch.Tensor) -> torch.Tensor:
+    """fp16 save: a plain copy of the raw values (kernels/fused_forward.py:893-904)."""
+    return raw.to(torch.float16)
+
+
+@torch.no_grad()
+def recompute_act(gate, up, recv_weights_bf16, activation="swiglu", situ_beta=1.0,
+                  situ_linear_beta=None, clamp_limit=7.0, dtype=torch.bfloat16):
+    """Backward-side recompute of the weighted activation rows from saved FC1 values and the
+    saved bf16 routing weights (kernels/mega_bwd.py:1408-1465): fp32 intermediates, one
+    rounding at the store."""
+    act = gated_activation(gate, up, activation, situ_beta or 1.0, situ_linear_beta,
+                           clamp_limit or 7.0)
+    return (act * recv_weights_bf16.float().unsqueeze(-1)).to(dtype)
+
+
 @torch.no_grad()
 def backward(saved: list[dict], dys: list[torch.Tensor]):
     """Five-stage backward (tests/_moe_baselines.py:96-226) for all ranks."""

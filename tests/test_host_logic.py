@@ -42,10 +42,11 @@ def test_config_defaults_and_validation():
         (dict(moonep_udma_chunk_bytes=3), ValueError),
         (dict(moonep_fused_balanced_count=False), ValueError),
         (dict(enable_moonep=True), NotImplementedError),
-        (dict(save_fc1_dtype="fp8"), NotImplementedError),
     ]:
         with pytest.raises(exc):
             MoEForwardConfig(**kw)
+    for fmt in ("bf16", "fp16", "fp8"):
+        assert MoEForwardConfig(save_fc1_dtype=fmt).save_fc1_dtype == fmt
     with pytest.raises(Exception):
         c.activation = "situglu"  # frozen
 
