@@ -113,6 +113,33 @@ def main():
                 check("oracle-saved " + name, ok, f"case {case_id} rank {rank} max_abs={max_d:.3e}")
         check("status", op.context.read_status().code == 0)
         op.finalize()
+        if drop == 0.0 and case_id == 2:
+            # recompute backward across ranks: the input rows are dispatched again into the
+            # symmetric slab and the activation is rebuilt from the saved FC1 rows
+            os.environ["MOE_SAVED_RECOMPUTE"] = "1"
+            try:
+                op2 = mega_moe.FusedMoEForward(group, max_tokens_per_rank=tokens,
+                                               hidden_size=hidden, top_k=top_k,
+                                               num_experts=experts, config=cfg)
+                gold = []
+                for s_r in saved:
+                    act = O.recompute_act(s_r["gate"], s_r["up"], s_r["recv_weights_sorted"])
+                    gold.append(dict(s_r, swiglu_out_weighted=act))
+                want2 = O.backward(gold, inp["dy"])[rank]
+                sd = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v)
+                      for k, v in saved[rank].items()
+                      if k not in ("recv_hidden_sorted", "swiglu_out_weighted")}
+                got = mega_moe.moe_backward_triton(sd, inp["dy"][rank].to(dev),
+                                                   op2.context.peer_mem, hidden_states=x)
+                for name in ("grad_hidden", "grad_routing_weights", "grad_fc1_1", "grad_fc1_2",
+                             "grad_fc2"):
+                    ok, max_d, rel, n_bad = O.cmp_grad(got[name].cpu(), want2[name])
+                    check("recompute " + name, ok,
+                          f"case {case_id} rank {rank} max_abs={max_d:.3e}")
+                check("recompute status", op2.context.read_status().code == 0)
+                op2.finalize()
+            finally:
+                del os.environ["MOE_SAVED_RECOMPUTE"]
     # receive-capacity overflow: every rank must raise ValueError, and the device stays usable
     tokens, hidden, ffn, experts, top_k = 256, 128, 128, 2 * world, 2
     inp = O.make_inputs(world, tokens, hidden, ffn, experts, top_k, seed=99)
