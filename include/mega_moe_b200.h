@@ -264,6 +264,15 @@ int mm_swiglu_bwd(const void* grad_act, int64_t ld_ga, const void* fc1_out, int6
                   const int32_t* row_dst_pos, void* const* peer_gate, int fc1_format,
                   const float* fc1_scale, int fc1_scale_group, cudaStream_t stream);
 
+/* ---- router in front of the layer ---------------------------------------------------- */
+/* selected [tokens, top_k] int32 = the top_k experts of every logits row in descending order
+ * of their logits (ties: lower expert id first); weights [tokens, top_k] fp32 = softmax over
+ * the selected logits (reference: the post-router inputs of its own benchmark and tests,
+ * benchmark/layer/bench_moe_suite.py:487-497).  top_k <= 32, num_experts <= 1024
+ * (MM_ERR_LIMIT above). */
+int mm_router_topk(const float* logits, int64_t ld_logits, int tokens, int num_experts, int top_k,
+                   int32_t* selected, float* weights, cudaStream_t stream);
+
 /* ---- saved-activation formats and the recompute backward ---------------------------- */
 /* Convert the raw bf16 FC1 rows [rows, cols = 2F] to the saved format: MM_FC1_FP16 or
  * MM_FC1_FP8 (+ scale table [rows, cols / scale_group])

@@ -383,6 +383,73 @@ route_row_tables_kernel(const int32_t* __restrict__ recv_expert_offs,
   }
 }
 
+// ---------------------------------------------------------------------------------
+// Router in front of the layer: top-k of the router logits and the softmax over the selected
+// logits.  One warp per token; every lane keeps its share of the row in registers and the
+// warp extracts the maximum k times (ties go to the lower expert id), so the selected experts
+// come out in descending order of their logits like torch.topk.
+// ---------------------------------------------------------------------------------
+constexpr int kRouterPerLane = 32;               // up to 1024 experts
+constexpr int kRouterWarps = 4;
+
+__global__ void __launch_bounds__(32 * kRouterWarps)
+router_topk_kernel(const float* __restrict__ logits, int64_t ld, int tokens, int experts, int top_k,
+                   int32_t* __restrict__ selected, float* __restrict__ weights) {
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * kRouterWarps + (threadIdx.x >> 5);
+  if (token >= tokens) return;
+  const float* row = logits + (int64_t)token * ld;
+  float v[kRouterPerLane];
+#pragma unroll
+  for (int i = 0; i < kRouterPerLane; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = e < experts ? row[e] : -INFINITY;
+  }
+  float my_logit = 0.0f;   // lane j keeps the j-th selected logit
+  int my_expert = 0;
+  float top = 0.0f;
+  for (int j = 0; j < top_k; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kRouterPerLane; ++i) {
+      // strict > keeps the lowest expert id of this lane among equal values
+      if (v[i] > best) {
+        best = v[i];
+        best_e = i * 32 + lane;
+      }
+    }
+#pragma unroll
+    for (int k = 16; k > 0; k >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, k);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, k);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    if (j == 0) top = best;
+    if (lane == j) {
+      my_logit = best;
+      my_expert = best_e;
+    }
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kRouterPerLane; ++i)
+        if (i == (best_e >> 5)) v[i] = -INFINITY;
+    }
+  }
+  // softmax over the selected logits (fp32, max-subtracted)
+  const float ex = lane < top_k ? expf(my_logit - top) : 0.0f;
+  float sum = ex;
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, k);
+  if (lane < top_k) {
+    selected[(int64_t)token * top_k + lane] = my_expert;
+    weights[(int64_t)token * top_k + lane] = ex / sum;
+  }
+}
+
 }  // namespace mm
 
 using namespace mm;
@@ -568,6 +635,29 @@ int mm_route_local_static(const int32_t* selected, int num_routes, int top_k, in
   return mm_route_local(selected, num_routes, top_k, num_experts, bins, send_route, send_token,
                         send_bucket, route_to_send, count_row, local_stats, scratch,
                         kRouteStaticScratchBytes, stream);
+}
+
+int mm_router_topk(const float* logits, int64_t ld_logits, int tokens, int num_experts, int top_k,
+                   int32_t* selected, float* weights, cudaStream_t stream) {
+  if (!logits || !selected || !weights) {
+    set_error("mm_router_topk: null argument");
+    return MM_ERR_ARG;
+  }
+  if (tokens < 0 || num_experts <= 0 || top_k <= 0 || top_k > 32 || top_k > num_experts ||
+      ld_logits < num_experts) {
+    set_error("mm_router_topk: need 1 <= top_k <= min(32, experts) and ld >= experts "
+              "(tokens=%d experts=%d top_k=%d)", tokens, num_experts, top_k);
+    return MM_ERR_ARG;
+  }
+  if (num_experts > 32 * kRouterPerLane) {
+    set_error("mm_router_topk: %d experts exceed the limit of %d", num_experts, 32 * kRouterPerLane);
+    return MM_ERR_LIMIT;
+  }
+  if (tokens == 0) return MM_OK;
+  const int blocks = (tokens + kRouterWarps - 1) / kRouterWarps;
+  router_topk_kernel<<<blocks, 32 * kRouterWarps, 0, stream>>>(logits, ld_logits, tokens, num_experts,
+                                                               top_k, selected, weights);
+  return check_launch("router_topk_kernel");
 }
 
 }  // extern "C"

@@ -8,9 +8,11 @@ from .config import MoEForwardConfig
 from .ops.backward import MegaMoEBackwardFunction, moe_backward_triton
 from .ops.forward import DispatchFC1Result, FusedMoEForward, pack_gate_up_weights
 from .ops.function import MegaMoEFunction
+from .ops.router import router_topk
 from .runtime.routing import MoERoutingPlan
 
 __all__ = [
+    "router_topk",
     "FusedMoEForward",
     "DispatchFC1Result",
     "pack_gate_up_weights",

@@ -83,6 +83,8 @@ SIGNATURES = {
                                 C.c_int, _c_ptr, C.c_int64, _c_ptr, C.c_int, C.c_float, C.c_float,
                                 C.c_float, _c_i32p, _c_i32p, _c_ptr, C.c_int, _c_ptr, C.c_int,
                                 _c_ptr]),
+    "mm_router_topk": (C.c_int, [_c_ptr, C.c_int64, C.c_int, C.c_int, C.c_int, _c_i32p, _c_ptr,
+                                 _c_ptr]),
     "mm_fc1_save_convert": (C.c_int, [_c_ptr, C.c_int64, C.c_int, _c_i32p, C.c_int, C.c_int,
                                       C.c_int, _c_ptr, C.c_int64, _c_ptr, _c_ptr]),
     "mm_swiglu_recompute": (C.c_int, [_c_ptr, C.c_int64, C.c_int, _c_ptr, C.c_int, _c_ptr, C.c_int,

@@ -440,6 +440,19 @@ def swiglu_bwd(grad_swiglu, s):
 
 
 # ---------------------------------------------------------------------------------------
+# router in front of the layer
+# ---------------------------------------------------------------------------------------
+@torch.no_grad()
+def router_topk(logits: torch.Tensor, top_k: int):
+    """Post-router inputs as the reference's benchmark builds them
+    (benchmark/layer/bench_moe_suite.py:487-497): top-k of the logits (descending; a stable
+    sort makes ties go to the lower expert id) and the fp32 softmax over the selected logits."""
+    order = torch.sort(logits.float(), dim=-1, descending=True, stable=True).indices[:, :top_k]
+    picked = torch.gather(logits.float(), 1, order)
+    return order.to(torch.int32), F.softmax(picked, dim=-1)
+
+
+# ---------------------------------------------------------------------------------------
 # saved-activation formats and the recompute backward.  The reference implements these only
 # in its Triton-Ascend kernels, which cannot run here, so this part restates the kernel source
 # and is NOT pinned by reference outputs ("parity unpinned" for these four functions); the
