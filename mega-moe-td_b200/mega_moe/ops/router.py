@@ -28,6 +28,8 @@ def router_topk(router_logits: torch.Tensor, top_k: int):
         raise ValueError("top_k must be an int in [1, min(experts, 32)]")
     selected = torch.empty(tokens, top_k, dtype=torch.int32, device=router_logits.device)
     weights = torch.empty(tokens, top_k, dtype=torch.float32, device=router_logits.device)
+    if tokens == 0:
+        return selected, weights
     N.check(N.lib().mm_router_topk(router_logits.data_ptr(), router_logits.stride(0), tokens,
                                    experts, top_k, selected.data_ptr(), weights.data_ptr(),
                                    N.stream_ptr()), "mm_router_topk")
