@@ -362,7 +362,9 @@ def run_ours(args, w, name):
 
     line = None
     if rank == 0:
-        cpu = cpu_baseline_sample(w, seconds_hint=20.0) if world == 1 else None
+        # MOE_BENCH_NO_CPU=1 skips the CPU leg (profiler runs, where only the launches matter)
+        cpu = (cpu_baseline_sample(w, seconds_hint=20.0)
+               if world == 1 and not os.environ.get("MOE_BENCH_NO_CPU") else None)
         line = {
             "metric": METRIC if name == DEFAULT_WORKLOAD else f"MoE fwd+bwd tokens/s ({name})",
             "value": round(tokens_per_s, 1), "unit": "tokens/s", "n_gpus": world,
