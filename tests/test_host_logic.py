@@ -176,3 +176,66 @@ def test_symmetric_exchange_and_count_cube_world2():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert results == {0: True, 1: True}
+
+
+def test_tile_mode_and_dispatch_defaults(monkeypatch):
+    """Host-side choices that need no GPU: the GEMM tile mode follows the expected rows per
+    local expert, the dispatch is fused only when there are peers, and the environment
+    switches override both."""
+    import types
+    from mega_moe.ops import _launch as L
+    for var in ("MOE_GEMM_MODE", "MOE_GEMM_PAIR", "MOE_FUSED_DISPATCH"):
+        monkeypatch.delenv(var, raising=False)
+
+    def ctx(tokens, top_k, world, experts):
+        return types.SimpleNamespace(max_tokens_per_rank=tokens, top_k=top_k, world_size=world,
+                                     num_experts=experts)
+
+    # the headline layer: 146 rows per expert on one GPU, 292 / 585 / 1170 on 2 / 4 / 8
+    assert L.gemm_tile_mode(ctx(8192, 16, 1, 896)) == L.TILE_SKINNY
+    for world in (2, 4, 8):
+        assert L.gemm_tile_mode(ctx(8192, 16, world, 896)) == L.TILE_SINGLE
+    assert L.gemm_tile_mode(None) == L.TILE_SINGLE and not L.pair_mode_enabled()
+    assert L.fused_dispatch_enabled(ctx(8192, 16, 8, 896))
+    assert not L.fused_dispatch_enabled(ctx(8192, 16, 1, 896))
+
+    monkeypatch.setenv("MOE_GEMM_MODE", "single")
+    assert L.gemm_tile_mode(ctx(8192, 16, 1, 896)) == L.TILE_SINGLE
+    monkeypatch.setenv("MOE_GEMM_MODE", "skinny")
+    assert L.gemm_tile_mode(ctx(8192, 16, 8, 896)) == L.TILE_SKINNY
+    monkeypatch.setenv("MOE_GEMM_MODE", "pair")
+    assert L.gemm_tile_mode(None) == L.TILE_PAIR and L.pair_mode_enabled()
+    monkeypatch.setenv("MOE_GEMM_MODE", "wide")
+    with pytest.raises(ValueError):
+        L.gemm_tile_mode(None)
+    monkeypatch.setenv("MOE_GEMM_MODE", "auto")
+    monkeypatch.setenv("MOE_GEMM_PAIR", "1")
+    assert L.gemm_tile_mode(ctx(8192, 16, 1, 896)) == L.TILE_PAIR
+    monkeypatch.setenv("MOE_FUSED_DISPATCH", "1")
+    assert L.fused_dispatch_enabled(ctx(8192, 16, 1, 896))
+    monkeypatch.setenv("MOE_FUSED_DISPATCH", "0")
+    assert not L.fused_dispatch_enabled(ctx(8192, 16, 8, 896))
+
+
+def test_saved_format_helpers(monkeypatch):
+    from mega_moe import _native as N
+    from mega_moe.ops import _launch as L
+    from mega_moe.runtime.workspace import saved_recompute_enabled
+    assert N.FC1_FORMAT_IDS == {"bf16": 0, "fp16": 1, "fp8": 2}
+    assert L.fc1_format_of(torch.empty(1, 2, dtype=torch.bfloat16)) == 0
+    assert L.fc1_format_of(torch.empty(1, 2, dtype=torch.float16)) == 1
+    assert L.fc1_format_of(torch.empty(1, 2, dtype=torch.float8_e4m3fn)) == 2
+    with pytest.raises(TypeError):
+        L.fc1_format_of(torch.empty(1, 2))
+    q = torch.empty(4, 256, dtype=torch.float8_e4m3fn)
+    with pytest.raises(ValueError):
+        L._fc1_scale_args(q, None, 0, 128)
+    with pytest.raises(ValueError):
+        L._fc1_scale_args(q, torch.empty(4, 3), 128, 128)          # wrong table shape
+    fmt, ptr, group = L._fc1_scale_args(q, torch.empty(4, 2), 128, 128)
+    assert fmt == 2 and group == 128 and ptr
+    assert L._fc1_scale_args(torch.empty(4, 256, dtype=torch.bfloat16), None, 0, 128) == (0, None, 0)
+    monkeypatch.delenv("MOE_SAVED_RECOMPUTE", raising=False)
+    assert not saved_recompute_enabled()
+    monkeypatch.setenv("MOE_SAVED_RECOMPUTE", "1")
+    assert saved_recompute_enabled()
