@@ -244,7 +244,9 @@ int mm_grouped_gemm_scatter(const mm_gemm_desc* d, const int32_t* row_dst_rank,
 
 /* Weight gradient: out[g][m', n'] = bf16(sum over rows of g: grad_out[row, m'] * orig_in[row, n'])
  * (reference: kernels/transposed_grouped_gemm.py:24-66; kernels/mega_bwd.py:394-493).
- * Groups without rows produce zeros. */
+ * Groups without rows produce zeros.  `pair`: 0 one CTA per 128x256 tile, every step-th tile;
+ * 1 CTA pairs (cta_group::2); 2 one CTA per tile walking whole (group, n-tile) units so that one
+ * operand stays in shared memory - for groups of up to 256 rows. */
 int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void* orig_in,
                      int64_t ld_in, int32_t Nw, int64_t rows_cap, const int32_t* group_offs,
                      int32_t num_groups, void* out, int64_t ld_out, int64_t out_group_stride,

@@ -420,7 +420,13 @@ int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void
   p.Mw = Mw;
   p.a_mn = 1;
   p.b_mn = 1;
-  p.pair = pair ? 1 : 0;
+  if (pair < 0 || pair > 2) {
+    set_error("mm_grouped_wgrad: tile mode %d is not one of 0 (single), 1 (pair), 2 (single, unit walk)",
+              pair);
+    return MM_ERR_ARG;
+  }
+  p.pair = pair == 1 ? 1 : 0;
+  p.unit_walk = pair == 2 ? 1 : 0;
   p.idesc = make_idesc_bf16(p.pair ? 2 * kBlockM : kBlockM, kBlockN, 1, 1);
   p.m_tiles = p.pair ? (Mw + 2 * kBlockM - 1) / (2 * kBlockM) : (Mw + kBlockM - 1) / kBlockM;
   p.n_tiles = (Nw + kBlockN - 1) / kBlockN;

@@ -60,6 +60,7 @@ struct GemmParams {
   int32_t wide_store;    // row stores in 256-byte pieces (scatter over NVLink)
   int32_t pair;          // 1: cta_group::2, clusters of two CTAs, 256-row tiles
   int32_t prefetch_kb;   // skinny kernel: k-blocks of weights requested into L2 ahead of the loads
+  int32_t unit_walk;     // single-CTA ragged reduction: walk whole units (see TileCursor)
   int32_t act;
   float act_beta;
   float act_linear_beta; // <= 0: no transform on up
@@ -407,10 +408,12 @@ __device__ __forceinline__ bool wait_expert_arrival(const GemmParams& p, int32_t
   return true;
 }
 
-// Order in which one CTA (or CTA pair) walks the launch's tiles.  Ragged-row GEMMs and pair
-// mode take every step-th tile.  A single-CTA ragged reduction (weight gradient) walks whole
-// units instead: a unit is one (group, 256-column n-tile) and the CTA runs all its m-tiles
-// back to back, so the unit's B operand can stay in shared memory while only A streams.
+// Order in which one CTA (or CTA pair) walks the launch's tiles.  By default every step-th
+// tile.  A single-CTA ragged reduction (weight gradient) over groups with few rows can walk
+// whole units instead (GemmParams::unit_walk): a unit is one (group, 256-column n-tile) and the
+// CTA runs all its m-tiles back to back, so the unit's B operand stays in shared memory while
+// only A streams.  Units are coarse (all m-tiles of one n-tile), so with many rows per group
+// the default walk balances the SMs better and keeps the working set in L2.
 struct TileCursor {
   int32_t t;       // tile index understood by decode_tile
   int32_t unit;    // unit mode: current unit
@@ -449,7 +452,7 @@ __device__ __forceinline__ TileInfo cursor_tile(const TileCursor& c, const GemmP
 template <bool kPair>
 __device__ __forceinline__ TileCursor cursor_begin(const GemmParams& p, int32_t ntiles) {
   TileCursor c;
-  c.unit_mode = !kPair && p.kind == kGroupedReduce;
+  c.unit_mode = !kPair && p.kind == kGroupedReduce && p.unit_walk != 0;
   c.limit = ntiles;
   c.m = 0;
   if (c.unit_mode) {

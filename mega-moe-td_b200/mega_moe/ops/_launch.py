@@ -82,9 +82,34 @@ def gemm_tile_mode(ctx=None) -> int:
 
 
 def pair_mode_enabled() -> bool:
-    """Weight gradients: MOE_GEMM_PAIR=1 / MOE_GEMM_MODE=pair selects CTA pairs (default: single
-    CTAs, measured faster on the weight gradients)."""
+    """MOE_GEMM_PAIR=1 / MOE_GEMM_MODE=pair: CTA pairs for every GEMM."""
     return gemm_tile_mode(None) == TILE_PAIR
+
+
+WGRAD_SINGLE, WGRAD_PAIR, WGRAD_UNIT = 0, 1, 2
+
+
+def wgrad_tile_mode(ctx=None) -> int:
+    """Tile mode of the weight gradients (``pair`` argument of ``mm_grouped_wgrad``):
+    ``MOE_WGRAD_MODE`` = ``single`` / ``pair`` / ``unit`` / ``auto`` (default).  Auto follows
+    ``MOE_GEMM_MODE=pair`` when that is set, takes the unit walk (one operand resident in shared
+    memory) when the expected rows per local expert fit it, and single CTAs otherwise."""
+    import os
+    mode = os.environ.get("MOE_WGRAD_MODE", "auto").lower()
+    if mode == "single":
+        return WGRAD_SINGLE
+    if mode == "pair":
+        return WGRAD_PAIR
+    if mode == "unit":
+        return WGRAD_UNIT
+    if mode != "auto":
+        raise ValueError(f"MOE_WGRAD_MODE={mode!r} is not one of auto, single, pair, unit")
+    if pair_mode_enabled():
+        return WGRAD_PAIR
+    if ctx is None:
+        return WGRAD_SINGLE
+    expected = ctx.max_tokens_per_rank * ctx.top_k * ctx.world_size / max(ctx.num_experts, 1)
+    return WGRAD_UNIT if expected <= SKINNY_MAX_ROWS_PER_EXPERT else WGRAD_SINGLE
 
 
 def make_desc(ctx: MoEForwardContext, a: torch.Tensor, a_rows_cap: int, lda: int,
@@ -222,7 +247,7 @@ def grouped_wgrad(ctx, grad_out, orig_in, rows_cap, group_offs, num_groups, out,
             grad_out.data_ptr(), grad_out.stride(0), grad_out.shape[1],
             orig_in.data_ptr(), orig_in.stride(0), orig_in.shape[1], rows_cap,
             group_offs.data_ptr(), num_groups, out.data_ptr(), out.stride(1), out.stride(0),
-            ctx.status.data_ptr(), 0, 1 if pair_mode_enabled() else 0, N.stream_ptr()),
+            ctx.status.data_ptr(), 0, wgrad_tile_mode(ctx), N.stream_ptr()),
             "mm_grouped_wgrad")
     N.count_launches(1)
 

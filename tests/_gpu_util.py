@@ -10,7 +10,8 @@ from mega_moe import _native as N
 from mega_moe.ops import _launch as L
 
 
-PAIR = 1   # tile mode under test: 0 = one CTA per tile, 1 = CTA pairs (cta_group::2), 2 = skinny
+PAIR = 1   # tile mode under test: 0 = one CTA per tile, 1 = CTA pairs (cta_group::2),
+           # 2 = skinny ragged-row GEMMs / unit walk of the weight gradient
 
 
 def tile_tables(counts, device, tile_rows=128):
@@ -100,7 +101,7 @@ def run_wgrad(grad_out, orig_in, counts):
     N.check(N.lib().mm_grouped_wgrad(
         grad_out.data_ptr(), grad_out.stride(0), grad_out.shape[1], orig_in.data_ptr(),
         orig_in.stride(0), orig_in.shape[1], rows, offs.data_ptr(), groups, out.data_ptr(),
-        out.stride(1), out.stride(0), status.data_ptr(), 0, 1 if PAIR == 1 else 0, N.stream_ptr()),
+        out.stride(1), out.stride(0), status.data_ptr(), 0, PAIR, N.stream_ptr()),
         "mm_grouped_wgrad")
     torch.cuda.synchronize()
     assert int(status[0]) == 0, status.tolist()
