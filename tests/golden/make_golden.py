@@ -1,7 +1,7 @@
 """Generate the golden fixtures of ``tests/golden/*.npz`` from the reference itself.
 
-Run where the reference checkout is mounted (``python tests/golden/make_golden.py
-[/path/to/reference]``, default ``/root/reference``).  The reference's Torch functional
+Run where a checkout of the reference is available: ``python tests/golden/make_golden.py
+/path/to/reference`` (or set ``MEGA_MOE_REFERENCE``).  The reference's Torch functional
 oracle is imported by file path with a stub ``torch_npu`` module (its production package
 cannot be imported without the Ascend toolchain), then executed under a gloo process group
 with one CPU process per rank:
@@ -130,7 +130,9 @@ def worker(rank, world, port, ref_root, name, c, out_dir):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MEGA_MOE_REFERENCE")
+    if not ref_root:
+        raise SystemExit("usage: make_golden.py /path/to/reference (or MEGA_MOE_REFERENCE)")
     port = 29610
     for name, c in CASES.items():
         port += 1
