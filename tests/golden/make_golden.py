@@ -45,6 +45,23 @@ CASES = {
 }
 
 
+# Activation variants: the reference's Torch functional forward with another gated activation
+# (ops/_torch_forward.py:177-205) and, where its hand-written backward covers it (situglu,
+# tests/_moe_baselines.py:122-160), the backward.  Forward-saved tensors and gradients only.
+ACT_CASES = {
+    "act_situglu_w2": dict(world=2, tokens=40, hidden=64, ffn=128, experts=8, top_k=2, seed=5,
+                           zipf=None, drop=0.0, bwd=True,
+                           act=dict(activation="situglu", situ_beta=1.5, situ_linear_beta=2.0)),
+    "act_situglu_plain_up_w1": dict(world=1, tokens=48, hidden=64, ffn=128, experts=4, top_k=2,
+                                    seed=6, zipf=None, drop=0.0, bwd=True,
+                                    act=dict(activation="situglu", situ_beta=0.75,
+                                             situ_linear_beta=None)),
+    "act_clamp_swiglu_w1": dict(world=1, tokens=48, hidden=64, ffn=128, experts=4, top_k=2,
+                                seed=7, zipf=None, drop=0.0, bwd=False,
+                                act=dict(activation="clamp_swiglu", clamp_limit=0.5)),
+}
+
+
 def load_reference(ref_root: Path):
     sys.modules.setdefault("torch_npu", types.ModuleType("torch_npu"))
     for pkg in ("mega_moe", "mega_moe.ops", "tests"):
@@ -129,14 +146,49 @@ def worker(rank, world, port, ref_root, name, c, out_dir):
     dist.destroy_process_group()
 
 
+def act_worker(rank, world, port, ref_root, name, c, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    tf, bl = load_reference(Path(ref_root))
+    inp = case_inputs(c)
+    x, rw, sel = inp["hidden"][rank], inp["routing_weights"][rank], inp["selected"][rank]
+    wg, wu, wd = inp["w_gate"][rank], inp["w_up"][rank], inp["w_down"][rank]
+    dy = inp["dy"][rank]
+    res = {}
+    with torch.no_grad():
+        out, saved = tf.moe_forward(x, rw, sel, wg, wu, wd, dist.group.WORLD, c["top_k"],
+                                    return_saved=True, **c["act"])
+        res["mf_output"] = bits(out)
+        for k in ("fc1_output", "swiglu_out_weighted", "recv_weights_sorted", "fc2_out"):
+            res["saved_" + k] = bits(saved[k])
+        if c["bwd"]:
+            grads = bl.moe_backward_torch(saved, dy)
+            for k in ("grad_hidden", "grad_routing_weights", "grad_fc1_1", "grad_fc1_2",
+                      "grad_fc2", "grad_fc1_output", "grad_gate"):
+                res["bwd_" + k] = bits(grads[k])
+    for k, v in (("in_hidden", x), ("in_routing_weights", rw), ("in_selected", sel),
+                 ("in_w_gate", wg), ("in_w_up", wu), ("in_w_down", wd), ("in_dy", dy)):
+        res[k] = bits(v)
+    np.savez_compressed(Path(out_dir) / f"_{name}_rank{rank}.npz", **res)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MEGA_MOE_REFERENCE")
     if not ref_root:
         raise SystemExit("usage: make_golden.py /path/to/reference (or MEGA_MOE_REFERENCE)")
     port = 29610
-    for name, c in CASES.items():
+    only = set(sys.argv[2].split(",")) if len(sys.argv) > 2 else None   # optional case filter
+    todo = [(n, c, worker) for n, c in CASES.items()] + \
+           [(n, c, act_worker) for n, c in ACT_CASES.items()]
+    for name, c, fn in todo:
+        if only is not None and name not in only:
+            continue
         port += 1
-        mp.spawn(worker, args=(c["world"], port, ref_root, name, c, str(HERE)),
+        mp.spawn(fn, args=(c["world"], port, ref_root, name, c, str(HERE)),
                  nprocs=c["world"], join=True)
         merged = {"meta": np.array([c["world"], c["tokens"], c["hidden"], c["ffn"], c["experts"],
                                     c["top_k"]], dtype=np.int64)}

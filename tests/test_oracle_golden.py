@@ -148,3 +148,34 @@ def test_topk_reduce_masks_dropped_routes():
             if r >= 0:
                 expect[t] += rows[r]
     assert torch.equal(out, expect)
+
+
+# Activation variants (fixtures written by act_worker of tests/golden/make_golden.py).
+ACT_FIXTURES = {
+    "act_situglu_w2": (dict(activation="situglu", situ_beta=1.5, situ_linear_beta=2.0), True),
+    "act_situglu_plain_up_w1": (dict(activation="situglu", situ_beta=0.75,
+                                     situ_linear_beta=None), True),
+    "act_clamp_swiglu_w1": (dict(activation="clamp_swiglu", clamp_limit=0.5), False),
+}
+
+
+def test_activation_variants_match_reference():
+    """Forward (saved tensors, output) with situglu / clamp_swiglu and the situglu backward are
+    bit-identical to what the reference's Torch functional path produced."""
+    from conftest import Golden
+    for name, (kw, has_bwd) in ACT_FIXTURES.items():
+        g = Golden(name)
+        outs, saved = O.forward_saved(g.per_rank("in_hidden"), g.per_rank("in_routing_weights"),
+                                      g.per_rank("in_selected"), g.per_rank("in_w_gate"),
+                                      g.per_rank("in_w_up"), g.per_rank("in_w_down"), g.top_k,
+                                      **kw)
+        for r in range(g.world):
+            _eq(outs[r], g.get(r, "mf_output"))
+            for k in ("fc1_output", "swiglu_out_weighted", "recv_weights_sorted", "fc2_out"):
+                _eq(saved[r][k], g.get(r, "saved_" + k))
+        if has_bwd:
+            grads = O.backward(saved, g.per_rank("in_dy"))
+            for r in range(g.world):
+                for k in ("grad_hidden", "grad_routing_weights", "grad_fc1_1", "grad_fc1_2",
+                          "grad_fc2", "grad_fc1_output", "grad_gate"):
+                    _eq(grads[r][k], g.get(r, "bwd_" + k))
