@@ -39,27 +39,27 @@ import torch.distributed as dist  # noqa: E402
 WORKLOADS = {
     # the configuration the headline metric is quoted on
     "kimi_k3_e896_k16_t8192": dict(tokens=8192, hidden=7168, ffn=2048, experts=896, top_k=16,
-                                   capacity=1.25, zipf=None),
+                                   capacity=1.25),
     # one rank's share of the headline layer at 8 GPUs (112 local experts, same rows per rank):
     # the per-GPU GEMM shapes of the 8-GPU run on a single GPU, for kernel tuning and ncu
     "kimi_k3_rank_share_e112_k16_t8192": dict(tokens=8192, hidden=7168, ffn=2048, experts=112,
-                                              top_k=16, capacity=1.25, zipf=None),
+                                              top_k=16, capacity=1.25),
     # a slice of that share small enough for multi-pass ncu captures (16 experts, 1170 rows each)
     "kimi_k3_rank_share_slice_e16_t1170": dict(tokens=1170, hidden=7168, ffn=2048, experts=16,
-                                               top_k=16, capacity=1.25, zipf=None),
+                                               top_k=16, capacity=1.25),
     # a slice of the single-GPU headline run: 32 experts with 146 rows each (weights 2.8 GB)
     "kimi_k3_single_gpu_slice_e32_t292": dict(tokens=292, hidden=7168, ffn=2048, experts=32,
-                                              top_k=16, capacity=1.25, zipf=None),
+                                              top_k=16, capacity=1.25),
     # slices with the rows per expert of the 2- and 4-GPU runs (292 and 585)
     "kimi_k3_two_gpu_slice_e32_t584": dict(tokens=584, hidden=7168, ffn=2048, experts=32,
-                                           top_k=16, capacity=1.25, zipf=None),
+                                           top_k=16, capacity=1.25),
     "kimi_k3_four_gpu_slice_e32_t1170": dict(tokens=1170, hidden=7168, ffn=2048, experts=32,
-                                             top_k=16, capacity=1.25, zipf=None),
+                                             top_k=16, capacity=1.25),
     # smaller shapes for quick checks and ncu captures (not bench lines)
     "qwen3_30b_e128_k8_t4096": dict(tokens=4096, hidden=2048, ffn=768, experts=128, top_k=8,
-                                    capacity=1.25, zipf=None),
+                                    capacity=1.25),
     "small_e32_k4_t1024": dict(tokens=1024, hidden=1024, ffn=512, experts=32, top_k=4,
-                               capacity=2.0, zipf=None),
+                               capacity=2.0),
 }
 DEFAULT_WORKLOAD = "kimi_k3_e896_k16_t8192"
 METRIC = "MoE fwd+bwd tokens/s (E896 top-16 H7168 F2048, 8K tok/rank), whole job"
@@ -161,9 +161,6 @@ def make_device_inputs(w, rank, world, device):
     x = torch.randn(T, H, generator=g, device=device).to(torch.bfloat16)
     dy = torch.randn(T, H, generator=g, device=device).to(torch.bfloat16)
     logits = torch.randn(T, E, generator=g, device=device)
-    if w.get("zipf"):
-        from oracle import moe_oracle as O  # only to build the seeded bias vector
-        logits = logits + O.zipf_expert_bias(E, w["zipf"]).to(device)[None, :]
     top_v, top_i = torch.topk(logits, k, dim=-1)
     rw = torch.softmax(top_v, dim=-1).float().contiguous()
     sel = top_i.to(torch.int32).contiguous()

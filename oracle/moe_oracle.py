@@ -612,6 +612,48 @@ def make_inputs(world, tokens, hidden, ffn, num_experts, top_k, seed=0, dtype=to
     return out
 
 
+KIMI_OWNER_LOADS = (19, 27, 11, 11, 15, 15, 15, 15)   # routes per owner rank out of every 128
+
+
+def kimi_skewed_routes(tokens: int, num_experts: int, top_k: int, rank: int) -> torch.Tensor:
+    """Deterministic skewed routes of the reference's benchmark
+    (benchmark/layer/_kimi_routes.py:7-40): out of every 128 consecutive routes of a rank,
+    owner rank o receives KIMI_OWNER_LOADS[o]; a token never repeats an expert.
+
+    The 128 routes span ``period = 128 // top_k`` tokens.  Token phase p sends
+    ``load // period`` routes to each owner, and the remainders are handed out one at a time,
+    owner after owner, to phases 0, 1, 2, ... cyclically.  Within an owner the experts are taken
+    round-robin from a cursor that starts at ``rank % experts_per_owner``.
+    """
+    world = len(KIMI_OWNER_LOADS)
+    if top_k not in (8, 16) or num_experts % world:
+        raise ValueError("Kimi skewed routes require W8 and top-k 8 or 16")
+    period = sum(KIMI_OWNER_LOADS) // top_k
+    if tokens % period:
+        raise ValueError("tokens must contain whole Kimi owner periods")
+    per_owner = num_experts // world
+    loads = np.asarray(KIMI_OWNER_LOADS)
+    quota = np.tile(loads // period, (period, 1))                  # [phase, owner]
+    handed = 0
+    for owner, rest in enumerate(loads % period):
+        for _ in range(int(rest)):
+            quota[handed % period, owner] += 1
+            handed += 1
+    if quota.max() > per_owner:
+        raise ValueError("too few local experts for distinct per-token choices")
+    per_token = quota[np.arange(tokens) % period]                  # [token, owner]
+    start = rank % per_owner + np.cumsum(per_token, axis=0) - per_token   # cursor before the token
+    routes = np.empty((tokens, top_k), dtype=np.int32)
+    col = np.zeros(tokens, dtype=np.int64)
+    rows = np.arange(tokens)
+    for owner in range(world):
+        for j in range(int(quota[:, owner].max())):
+            take = per_token[:, owner] > j
+            routes[rows[take], col[take]] = owner * per_owner + (start[take, owner] + j) % per_owner
+            col[take] += 1
+    return torch.from_numpy(routes)
+
+
 def zipf_expert_bias(num_experts: int, s: float, seed: int = 7) -> torch.Tensor:
     """Per-expert router bias 2*log(1/rank^s) over a seeded expert permutation."""
     g = torch.Generator().manual_seed(seed)

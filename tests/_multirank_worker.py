@@ -140,6 +140,25 @@ def main():
                 op2.finalize()
             finally:
                 del os.environ["MOE_SAVED_RECOMPUTE"]
+    # the reference benchmark's deterministic skewed routes (owner loads 19/27/11/11/15/15/15/15
+    # of every 128): forward parity with a capacity sized for the hottest owner
+    tokens, hidden, ffn, experts, top_k = 256, 256, 128, 32, 8
+    if experts % world == 0:
+        inp = O.make_inputs(world, tokens, hidden, ffn, experts, top_k, seed=77, weight_std=0.05)
+        routes = [O.kimi_skewed_routes(tokens, experts, top_k, r) for r in range(world)]
+        want_out = O.forward_golden(inp["hidden"], inp["routing_weights"], routes,
+                                    inp["w_gate"], inp["w_up"], inp["w_down"], experts)[rank]
+        cfg = mega_moe.MoEForwardConfig(receive_capacity_factor=min(float(world), 2.0))
+        op = mega_moe.FusedMoEForward(group, max_tokens_per_rank=tokens, hidden_size=hidden,
+                                      top_k=top_k, num_experts=experts, config=cfg)
+        gate_up = mega_moe.pack_gate_up_weights(inp["w_gate"][rank].to(dev),
+                                                inp["w_up"][rank].to(dev))
+        out = op(inp["hidden"][rank].to(dev), routes[rank].to(dev), gate_up,
+                 inp["w_down"][rank].to(dev), inp["routing_weights"][rank].to(dev))
+        torch.testing.assert_close(out.cpu().float(), want_out.float(), rtol=O.OUTPUT_RTOL,
+                                   atol=O.OUTPUT_ATOL)
+        check("skewed routes status", op.context.read_status().code == 0)
+        op.finalize()
     # receive-capacity overflow: every rank must raise ValueError, and the device stays usable
     tokens, hidden, ffn, experts, top_k = 256, 128, 128, 2 * world, 2
     inp = O.make_inputs(world, tokens, hidden, ffn, experts, top_k, seed=99)

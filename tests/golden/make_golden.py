@@ -176,6 +176,28 @@ def act_worker(rank, world, port, ref_root, name, c, out_dir):
     dist.destroy_process_group()
 
 
+ROUTE_CASES = [(64, 896, 16), (8192, 896, 16), (128, 32, 8), (256, 64, 16), (4096, 128, 8)]
+
+
+def route_digests(ref_root: Path):
+    """SHA-256 of the reference's deterministic skewed routes
+    (benchmark/layer/_kimi_routes.py) for a few shapes and ranks -> kimi_routes_digests.json."""
+    import hashlib
+    import json
+    spec = importlib.util.spec_from_file_location(
+        "_kimi_routes", ref_root / "benchmark/layer/_kimi_routes.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = {}
+    for tokens, experts, top_k in ROUTE_CASES:
+        for rank in (0, 3, 7):
+            routes = mod.kimi_skewed_routes(tokens, experts, top_k, rank)
+            key = f"t{tokens}_e{experts}_k{top_k}_r{rank}"
+            out[key] = hashlib.sha256(routes.contiguous().numpy().tobytes()).hexdigest()
+    (HERE / "kimi_routes_digests.json").write_text(json.dumps(out, indent=1, sort_keys=True))
+    print("kimi_routes_digests.json", len(out), "entries")
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MEGA_MOE_REFERENCE")
     if not ref_root:
@@ -184,6 +206,8 @@ def main():
     only = set(sys.argv[2].split(",")) if len(sys.argv) > 2 else None   # optional case filter
     todo = [(n, c, worker) for n, c in CASES.items()] + \
            [(n, c, act_worker) for n, c in ACT_CASES.items()]
+    if only is None or "routes" in only:
+        route_digests(Path(ref_root))
     for name, c, fn in todo:
         if only is not None and name not in only:
             continue

@@ -314,3 +314,29 @@ def test_host_sync_free_mode_matches_and_defers_capacity_error():
         assert op.context.read_status().code == 0
     finally:
         op.finalize()
+
+
+def test_forward_with_the_reference_benchmarks_skewed_routes():
+    """Deterministic skewed routes of the reference's benchmark (restated in the oracle and
+    pinned by digests): forward and backward parity on one rank."""
+    import mega_moe
+    tokens, hidden, ffn, experts, top_k = 256, 256, 128, 32, 8
+    inp = O.make_inputs(1, tokens, hidden, ffn, experts, top_k, seed=78, weight_std=0.05)
+    routes = [O.kimi_skewed_routes(tokens, experts, top_k, 0)]
+    want_out = O.forward_golden(inp["hidden"], inp["routing_weights"], routes, inp["w_gate"],
+                                inp["w_up"], inp["w_down"], experts)[0]
+    _, saved = O.forward_saved(inp["hidden"], inp["routing_weights"], routes, inp["w_gate"],
+                               inp["w_up"], inp["w_down"], top_k)
+    want = O.backward(saved, inp["dy"])[0]
+    op = _make_op(tokens, hidden, top_k, experts)
+    try:
+        gate_up = mega_moe.pack_gate_up_weights(inp["w_gate"][0].to(DEV), inp["w_up"][0].to(DEV))
+        out, dev_saved = op(inp["hidden"][0].to(DEV), routes[0].to(DEV), gate_up,
+                            inp["w_down"][0].to(DEV), inp["routing_weights"][0].to(DEV),
+                            return_saved=True)
+        _check_out(out, want_out)
+        got = mega_moe.moe_backward_triton(dev_saved, inp["dy"][0].to(DEV), op.context.peer_mem)
+        for k in ("grad_hidden", "grad_routing_weights", "grad_fc1_1", "grad_fc1_2", "grad_fc2"):
+            _check_grad(k, got[k], want[k])
+    finally:
+        op.finalize()

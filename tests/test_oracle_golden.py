@@ -179,3 +179,28 @@ def test_activation_variants_match_reference():
                 for k in ("grad_hidden", "grad_routing_weights", "grad_fc1_1", "grad_fc1_2",
                           "grad_fc2", "grad_fc1_output", "grad_gate"):
                     _eq(grads[r][k], g.get(r, "bwd_" + k))
+
+
+def test_kimi_skewed_routes_match_reference_digests():
+    """The restated skew generator reproduces the reference's routes (SHA-256 known answers
+    written by tests/golden/make_golden.py) and keeps its invariants."""
+    import hashlib
+    import json
+    from conftest import GOLDEN_DIR
+    digests = json.loads((GOLDEN_DIR / "kimi_routes_digests.json").read_text())
+    assert len(digests) == 15
+    for key, want in digests.items():
+        tokens, experts, top_k, rank = (int(p[1:]) for p in key.split("_"))
+        routes = O.kimi_skewed_routes(tokens, experts, top_k, rank)
+        assert routes.dtype == torch.int32 and routes.shape == (tokens, top_k)
+        assert hashlib.sha256(routes.numpy().tobytes()).hexdigest() == want, key
+        # no token repeats an expert; owner loads follow the profile
+        assert all(len(set(row.tolist())) == top_k for row in routes[:64])
+        owners = torch.bincount((routes // (experts // 8)).flatten(), minlength=8)
+        assert owners.tolist() == [c * tokens * top_k // 128 for c in O.KIMI_OWNER_LOADS]
+    for bad in ((64, 896, 4, 0), (60, 896, 16, 0), (64, 900, 16, 0)):
+        try:
+            O.kimi_skewed_routes(*bad)
+        except ValueError:
+            continue
+        raise AssertionError(bad)
