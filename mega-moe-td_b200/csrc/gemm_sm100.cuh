@@ -530,16 +530,34 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const bool leader = cta_rank == 0;
   constexpr int nstages = kPair ? kPairStages : kStages;
   constexpr int stage_bytes = kPair ? kPairStageBytes : kStageBytes;
+  // Ring geometry.  Normally a stage is [A | B] and both halves have `nstages` slots.  The
+  // unit walk of a single-CTA ragged reduction keeps B resident, so only A streams and the
+  // number of A bytes in flight bounds the kernel: there the memory is carved as three B slots
+  // (96 KB, groups of up to 192 rows stay resident) followed by six A slots (96 KB).
+  const bool compact = !kPair && p.kind == kGroupedReduce && p.unit_walk != 0;
+  const int na = compact ? 6 : nstages;   // slots of the A ring (full / empty / fixed barriers)
+  const int nb = compact ? 3 : nstages;   // slots of the B ring (B-consumed barriers)
+  auto a_slot = [&](int i) -> uint8_t* {
+    return compact ? stages + 3 * kStageBBytes + i * kStageABytes : stages + i * stage_bytes;
+  };
+  auto b_slot = [&](int i) -> uint8_t* {
+    return compact ? stages + i * kStageBBytes : stages + i * stage_bytes + kStageABytes;
+  };
+  static_assert(3 * kStageBBytes + 6 * kStageABytes <= kStages * kStageBytes, "compact ring fits");
+  static_assert(kMaxStages >= 6, "barrier arrays cover the compact A ring");
   constexpr int b_boxes = kPair ? 2 : 4;             // 64-column boxes of an MN-major B stage
   const int32_t b_col_off = kPair ? (int32_t)cta_rank * (kBlockN / 2) : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&full_bar[s], 1);
-      // single-mode ragged reduction: a stage is free once the MMA has consumed it and the
-      // tail warp has passed it, so that warp is never more than one phase behind the ring
-      mbar_init(&empty_bar[s], (!kPair && p.kind == kGroupedReduce) ? 2 : 1);
-      mbar_init(&ready_bar[s], 1);
+      // single-mode ragged reduction: a stage is free once the issuing warp's MMAs have
+      // consumed it and the other issuing warp and the tail warp have passed it, so none of
+      // them is ever more than one phase behind the ring
+      mbar_init(&empty_bar[s], (!kPair && p.kind == kGroupedReduce) ? 3 : 1);
+      // ready_bar doubles as the single-mode "B half consumed" barrier; a ragged reduction has
+      // two MMA-issuing warps and both report on it
+      mbar_init(&ready_bar[s], (!kPair && p.kind == kGroupedReduce) ? 2 : 1);
       mbar_init(&fixed_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -571,6 +589,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int32_t ntiles = total_tiles(p);
   // Single mode tracks the A and B halves of the stage ring separately: a ragged reduction
   // whose group fits the ring keeps B resident over the m-tiles of a unit (see TileCursor).
+  const bool dual_issue = !kPair && p.kind == kGroupedReduce;   // two MMA-issuing warps
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -587,7 +606,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
            cursor_next(cur, p)) {
         const TileInfo ti = cursor_tile(cur, p, cta_rank);
         // B stays in shared memory over the m-tiles of a unit when the group's rows fit the ring
-        const bool resident = cur.unit_mode && ti.num_kb <= nstages;
+        const bool resident = cur.unit_mode && ti.num_kb <= nb;
         const bool load_b = !resident || cur.m == 0;
         if (p.disp_src != nullptr && ti.group != ready_group) {
           const long long c0 = prof_now();
@@ -605,10 +624,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             break;
           }
           pw_empty += prof_now() - c1;
-          uint8_t* sA = stages + stage * stage_bytes;
+          uint8_t* sA = a_slot(stage);
           uint8_t* sB = sA + kStageABytes;
           if constexpr (!kPair) {
-            sB = stages + bstage * stage_bytes + kStageABytes;
+            sB = b_slot(bstage);
             const long long c2 = prof_now();
             if (load_b && !mbar_wait(&bempty_bar[bstage], bphase ^ 1, abort_flag, p.status,
                                      kSiteSmemEmpty, 8 + bstage)) {
@@ -667,11 +686,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
           pw_issue += prof_now() - c8;
-          if (load_b && ++bstage == nstages) {
+          if (load_b && ++bstage == nb) {
             bstage = 0;
             bphase ^= 1;
           }
-          if (++stage == nstages) {
+          if (++stage == na) {
             stage = 0;
             phase ^= 1;
           }
@@ -689,11 +708,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || (dual_issue && warp == 3 + kEpiWarps)) {
     // ------------------------------- MMA issuer -------------------------------
+    // A single-CTA ragged reduction has two issuing warps (warp 1 and the last warp): tile i of
+    // this CTA's walk belongs to issuer i & 1 and accumulates in TMEM buffer i & 1, so while one
+    // warp sits in its (blocking) MMA issue the other already waits for the next tile's loads,
+    // tail rows and accumulator.  Both warps walk every tile and observe every stage barrier
+    // in order (a parity wait cannot tell a phase from the one two phases later); each issues
+    // only its own tiles.
+    const int issuer = warp == 1 ? 0 : 1;
+    int seq = 0;                 // tiles walked so far
     int stage = 0;
     uint32_t phase = 0;
-    int acc = 0;
+    int acc = dual_issue ? issuer : 0;
     uint32_t acc_phase = 0;
     bool alive = true;
     uint32_t peer_full_phase = 0;   // per-stage parity of the peer CTA's own full barrier
@@ -712,14 +739,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const long long c9 = prof_now();
       const TileInfo ti = cursor_tile(cur, p, cta_rank);
       mw_decode += prof_now() - c9 + (ti.num_kb & 0);
-      const bool resident = cur.unit_mode && ti.num_kb <= nstages;
+      const bool resident = cur.unit_mode && ti.num_kb <= nb;
       const bool fresh_b = !resident || cur.m == 0;                 // B was loaded for this tile
-      const bool release_b = !resident || cur.m == p.m_tiles - 1;   // B is not needed afterwards
+      const bool mine = !dual_issue || (seq & 1) == issuer;
+      // When B leaves shared memory.  One issuer: after the unit's last tile (or after every
+      // tile when B streams).  Two issuers share a resident B, so each reports after its own
+      // last tile of the unit, and the one without a tile in the unit just passes by.
+      bool release_b = !resident || cur.m == p.m_tiles - 1;
+      bool pass_b = false;        // not my tile, but my report on the B slots is due here
+      if (dual_issue) {
+        if (mine) {
+          release_b = !resident || cur.m + 2 > p.m_tiles - 1;
+        } else {
+          release_b = false;
+          pass_b = !resident || p.m_tiles == 1;
+        }
+      }
       if (resident && cur.m == 0) unit_b0 = bstage;
       // In pair mode only the leader CTA owns the accumulator hand-shake and issues MMAs; the
       // peer's warp still walks the stages to prepare its half of every stage.
       const long long c3 = prof_now();
-      if (leader) {
+      if (leader && mine) {
         bool ok = true;
         if constexpr (kPair) {
           // cluster-scope acquire: one lane polls, the warp follows
@@ -742,12 +782,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool tail = p.kind == kGroupedReduce && ti.kcnt - kb * kBlockK < kBlockK;
         const int ksteps = tail ? (ti.kcnt - kb * kBlockK + kUmmaK - 1) / kUmmaK : kBlockK / kUmmaK;
         const bool handover = pair && tail;   // the peer prepares its half itself, then reports
-        uint8_t* sA = stages + stage * stage_bytes;
+        uint8_t* sA = a_slot(stage);
         uint8_t* sB = sA + kStageABytes;
         int bslot = stage;
         if constexpr (!kPair) {
-          bslot = resident ? (unit_b0 + kb) % nstages : bstage;
-          sB = stages + bslot * stage_bytes + kStageABytes;
+          bslot = resident ? (unit_b0 + kb) % nb : bstage;
+          sB = b_slot(bslot);
         }
         const long long c4 = prof_now();
         if (leader || handover) {
@@ -799,6 +839,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         const long long c10 = prof_now();
+        if (!mine) {
+          // passing by: this warp has observed the block, the stage may be refilled once the
+          // other issuer's MMAs are done
+          if (lane == 0) {
+            mbar_arrive(&empty_bar[stage]);
+            if (pass_b) mbar_arrive(&bempty_bar[bslot]);
+          }
+        } else
 #ifdef MM_PROFILE
         if (p.prof_skip_mma) {
           if (lane == 0) {
@@ -832,27 +880,34 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         __syncwarp();
         mw_issue += prof_now() - c10;
-        if (!resident && ++bstage == nstages) bstage = 0;
-        if (++stage == nstages) {
+        if (!resident && ++bstage == nb) bstage = 0;
+        if (++stage == na) {
           stage = 0;
           phase ^= 1;
         }
       }
       if (!alive) break;
-      if (resident && release_b) bstage = (unit_b0 + ti.num_kb) % nstages;
+      if (resident && cur.m == p.m_tiles - 1) bstage = (unit_b0 + ti.num_kb) % nb;
+      if (mine) {
 #ifdef MM_PROFILE
-      if (p.prof_skip_mma) {
-        if (lane == 0) mbar_arrive(&tmem_full[acc]);
-      } else
+        if (p.prof_skip_mma) {
+          if (lane == 0) mbar_arrive(&tmem_full[acc]);
+        } else
 #endif
-      if (lane == 0 && leader) {
-        if constexpr (kPair) umma_commit_pair(&tmem_full[acc]); else umma_commit(&tmem_full[acc]);
+        if (lane == 0 && leader) {
+          if constexpr (kPair) umma_commit_pair(&tmem_full[acc]); else umma_commit(&tmem_full[acc]);
+        }
       }
       __syncwarp();
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1;
+      ++seq;
+      if (dual_issue) {
+        if (mine) acc_phase ^= 1;        // this issuer's buffer is used once per own tile
+      } else {
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
     }
-    if (lane == 0) {
+    if (lane == 0 && issuer == 0) {
       prof_store(p, 3, mw_acc);
       prof_store(p, 4, mw_full);
       prof_store(p, 5, mw_tail);
@@ -875,7 +930,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (TileCursor cur = cursor_begin<kPair>(p, ntiles); cur.t < cur.limit && alive;
              cursor_next(cur, p)) {
           const TileInfo ti = cursor_tile(cur, p, cta_rank);
-          const bool resident = cur.unit_mode && ti.num_kb <= nstages;
+          const bool resident = cur.unit_mode && ti.num_kb <= nb;
           const bool fresh_b = !resident || cur.m == 0;
           if (resident && cur.m == 0) unit_b0 = bstage;
           for (int kb = 0; kb < ti.num_kb; ++kb) {
@@ -888,21 +943,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
             const int32_t rows_left = ti.kcnt - kb * kBlockK;
             if (rows_left < kBlockK) {
-              const int bslot = resident ? (unit_b0 + kb) % nstages : bstage;
-              clear_tail_rows(stages + stage * stage_bytes,
-                              stages + bslot * stage_bytes + kStageABytes, b_boxes, fresh_b,
+              const int bslot = resident ? (unit_b0 + kb) % nb : bstage;
+              clear_tail_rows(a_slot(stage),
+                              b_slot(bslot), b_boxes, fresh_b,
                               rows_left, (rows_left + kUmmaK - 1) / kUmmaK, lane);
               if (lane == 0) mbar_arrive(&fixed_bar[stage]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[stage]);
-            if (!resident && ++bstage == nstages) bstage = 0;
-            if (++stage == nstages) {
+            if (!resident && ++bstage == nb) bstage = 0;
+            if (++stage == na) {
               stage = 0;
               phase ^= 1;
             }
           }
-          if (resident && cur.m == p.m_tiles - 1) bstage = (unit_b0 + ti.num_kb) % nstages;
+          if (resident && cur.m == p.m_tiles - 1) bstage = (unit_b0 + ti.num_kb) % nb;
         }
       }
     } else {
