@@ -373,6 +373,9 @@ def run_ours(args, w, name):
                        "receive_capacity_factor": cfg.receive_capacity_factor
                        if cfg.receive_capacity_factor is not None else world,
                        "received_rows_rank0": m_rows, "parallelism": f"ep{world}",
+                       "gemm_tile_mode": ("single", "pair", "skinny")[L.gemm_tile_mode(op.context)],
+                       "wgrad_tile_mode": ("single", "pair", "unit")[L.wgrad_tile_mode(op.context)],
+                       "fused_dispatch": bool(L.fused_dispatch_enabled(op.context)),
                        "l2": "inputs larger than L2 (expert weights and their gradients "
                              f"are {3 * weight_bytes / 1e9:.1f} GB per rank and step)"},
             "tokens_per_s_per_gpu": round(tokens_per_s / world, 1),
