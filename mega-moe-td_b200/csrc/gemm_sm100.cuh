@@ -1,11 +1,15 @@
 // Grouped GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM -> epilogue.
 //
-// One persistent CTA per SM, six warps:
+// One persistent CTA per SM (or a cluster of two CTAs per 256-row tile in pair mode), eight warps:
 //   warp 0      TMA producer (one lane issues cp.async.bulk.tensor loads)
 //   warp 1      TMEM allocator and MMA issuer (one lane issues tcgen05.mma)
 //   warps 2..5  epilogue: tcgen05.ld the accumulator, convert, stage, store
-// A four-stage shared-memory ring feeds the tensor core; two 128x256 fp32
-// accumulators in TMEM let the epilogue of tile i overlap the main loop of i+1.
+//   warps 6..7  ragged rows: dispatch warps of a fused launch (push this rank's rows to their
+//               owners while the GEMM consumes the experts whose rows have arrived);
+//               ragged reduction, single CTA: warp 6 clears the rows past a group's end in the
+//               group's last k-block, warp 7 is a second MMA issuer (tiles alternate)
+// A ring of shared-memory stages feeds the tensor core; two 128x256 fp32 accumulators in TMEM
+// let the epilogue of tile i overlap the main loop of tile i+1.
 //
 // Two problem kinds share the kernel:
 //   kGroupedRows  out[rows of group g, :] = A[rows of g, 0:K] * B_g      (ragged M)
