@@ -239,3 +239,82 @@ def test_saved_format_helpers(monkeypatch):
     assert not saved_recompute_enabled()
     monkeypatch.setenv("MOE_SAVED_RECOMPUTE", "1")
     assert saved_recompute_enabled()
+
+
+class _FakeSymmetricBlock:
+    """CPU stand-in for the CUDA-IPC block: same region bookkeeping, plain host tensors."""
+
+    def __init__(self, regions, rank, world_size, group, device):
+        self.regions = dict(regions)
+        self.rank, self.world_size = rank, world_size
+        self._mem = {name: torch.zeros(max(size, 16), dtype=torch.uint8)
+                     for name, size in regions.items()}
+
+    def local(self, name, dtype):
+        return self._mem[name][:self.regions[name]].view(dtype)
+
+    def peer_table(self, name):
+        return torch.tensor([self._mem[name].data_ptr()] * self.world_size, dtype=torch.int64)
+
+    def free(self):
+        self._mem = {}
+
+
+@pytest.mark.parametrize("grouped_tile,fused_tile", [(128, None), (128, 256), (256, 128), (128, 16)])
+@pytest.mark.parametrize("recompute", [False, True])
+def test_workspace_sizing_on_cpu(monkeypatch, grouped_tile, fused_tile, recompute):
+    """Workspace sizing with host tensors in place of the symmetric block (the reference checks
+    its own sizing the same way, tests/function/test_forward_workspace.py:13-44): the receive
+    buffer holds int(T * k * factor) rows, the source-tile bound covers the worst case of every
+    route going to one expert for both dispatch tile sizes, the count cube has
+    next_pow2(world * experts_per_rank) bins per rank, and the tile tables cover every row tile
+    a rank can receive."""
+    from mega_moe.runtime import workspace as W
+    monkeypatch.setattr(W, "SymmetricBlock", _FakeSymmetricBlock)
+    if recompute:
+        monkeypatch.setenv("MOE_SAVED_RECOMPUTE", "1")
+    else:
+        monkeypatch.delenv("MOE_SAVED_RECOMPUTE", raising=False)
+    tokens, hidden, top_k, experts, world, factor = 257, 16, 3, 14, 2, 2
+    ctx = W.create_moe_forward_context(
+        max_tokens_per_rank=tokens, hidden_size=hidden, top_k=top_k, num_experts=experts,
+        rank=0, world_size=world, receive_capacity_factor=factor,
+        dispatch_fc1_block_size_m=grouped_tile, single_kernel_dispatch_block_size_m=fused_tile,
+        device=torch.device("cpu"))
+    try:
+        routes = tokens * top_k
+        cap = int(routes * factor)
+        epr = experts // world
+        assert ctx.experts_per_rank == ctx.physical_experts_per_rank == epr
+        assert ctx.max_received_routes == cap
+        for tile in (grouped_tile, fused_tile or grouped_tile):
+            assert (routes + tile - 1) // tile <= ctx.max_source_tiles
+        assert ctx.peer_mem.numel() == cap * hidden and ctx.peer_mem.dtype == torch.bfloat16
+        assert ctx.routing_weight_mem.numel() == cap and ctx.routing_weight_mem.dtype == torch.float32
+        assert tuple(ctx.combine_mem.shape) == (routes, hidden)
+        assert ctx.combine_gate_mem.numel() == routes
+        assert ctx.dispatch_flags.numel() == world * epr
+        assert (ctx.redispatch_mem is not None) == recompute
+        if recompute:
+            assert ctx.redispatch_mem.numel() == cap * hidden
+        bins = W.next_power_of_2(world * epr)
+        assert ctx.metadata_num_bins == bins == 16
+        assert ctx.metadata_counts_mem.numel() == world * bins
+        assert ctx.metadata_recv_counts_re.shape == (world, epr)
+        assert ctx.metadata_recv_seg_starts.shape == (epr, world + 1)
+        assert ctx.metadata_recv_expert_offs.numel() == epr + 1
+        assert ctx.metadata_stats.numel() == 2 + world
+        # every expert can end on a partial tile: tiles <= cap // rows + experts
+        assert ctx.mtile_group.numel() >= cap // 128 + epr
+        assert ctx.mtile2_group.numel() >= cap // 256 + epr
+        assert ctx.row_src_rank.numel() >= cap and ctx.route_to_send.numel() == routes
+        assert bool((ctx.route_to_send == -1).all())
+        assert ctx.disp_order_prefix.numel() == world * epr + 1
+        assert W.context_of(ctx.peer_mem) is ctx
+    finally:
+        W.unregister_context(ctx)
+    with pytest.raises(NotImplementedError):
+        W.create_moe_forward_context(
+            max_tokens_per_rank=8, hidden_size=16, top_k=2, num_experts=4, rank=0, world_size=1,
+            receive_capacity_factor=1.0, dispatch_fc1_block_size_m=128, enable_moonep=True,
+            device=torch.device("cpu"))
