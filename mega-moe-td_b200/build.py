@@ -1,7 +1,10 @@
 """Build libmegamoe_sm100.so in-tree with nvcc for sm_100a.
 
-Usage: ``python mega-moe-td_b200/build.py [--force] [--verbose]``.  The shared library lands
-in ``mega-moe-td_b200/lib/`` next to the sources, so a copy of the repository carries it.
+Usage: ``python mega-moe-td_b200/build.py [--force] [--verbose] [--profile]``.  The shared
+library lands in ``mega-moe-td_b200/lib/`` next to the sources, so a copy of the repository
+carries it.  ``--profile`` builds a second, instrumented library
+(``libmegamoe_sm100_prof.so``, ``-DMM_PROFILE``) whose GEMM kernels count the clocks each warp
+role spends in its waits; ``profile_roles.py`` reads them.  The product never loads it.
 """
 from __future__ import annotations
 
@@ -14,6 +17,7 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 LIB_DIR = ROOT / "lib"
 LIB_PATH = LIB_DIR / "libmegamoe_sm100.so"
+PROFILE_LIB_PATH = LIB_DIR / "libmegamoe_sm100_prof.so"
 SOURCES = ["abi.cu", "routing.cu", "movement.cu", "gemm_host.cu"]
 HEADERS = (sorted(p.name for p in CSRC.glob("*.cuh")) + sorted(p.name for p in CSRC.glob("*.h"))
            + ["../../include/mega_moe_b200.h"])
@@ -39,10 +43,12 @@ def _stale(out: Path, deps: list[Path]) -> bool:
     return any(d.exists() and d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, profile: bool = False) -> Path:
     LIB_DIR.mkdir(exist_ok=True)
-    obj_dir = ROOT / "build"
+    obj_dir = ROOT / ("build_prof" if profile else "build")
     obj_dir.mkdir(exist_ok=True)
+    lib_path = PROFILE_LIB_PATH if profile else LIB_PATH
+    flags = NVCC_FLAGS + (["-DMM_PROFILE"] if profile else [])
     headers = [CSRC / h for h in HEADERS]
     sources = [s for s in SOURCES if (CSRC / s).exists()]
     objs = []
@@ -52,7 +58,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         obj = obj_dir / (src.stem + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + headers):
-            cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+            cmd = [_nvcc(), *flags, "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas")
                 cmd.insert(2, "-v")
@@ -66,14 +72,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed; see the compiler output above")
-    if force or procs or _stale(LIB_PATH, objs):
-        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lcudart"]
+    if force or procs or _stale(lib_path, objs):
+        cmd = [_nvcc(), "-shared", "-o", str(lib_path), *map(str, objs), "-lcudart"]
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
+                 profile="--profile" in sys.argv)
     print(path)
