@@ -318,3 +318,35 @@ def test_workspace_sizing_on_cpu(monkeypatch, grouped_tile, fused_tile, recomput
             max_tokens_per_rank=8, hidden_size=16, top_k=2, num_experts=4, rank=0, world_size=1,
             receive_capacity_factor=1.0, dispatch_fc1_block_size_m=128, enable_moonep=True,
             device=torch.device("cpu"))
+
+
+def test_bench_binds_host_threads_to_the_gpus_cpus(monkeypatch):
+    """bench.py's NUMA binding for multi-GPU runs, against a fake NVML: the NVML core mask is
+    intersected with the cores the process may use; nothing changes when NVML is missing, the
+    intersection is too small, or the switch is set."""
+    import types
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+    calls = []
+    monkeypatch.setattr(os, "sched_getaffinity", lambda pid: set(range(0, 48)), raising=False)
+    monkeypatch.setattr(os, "sched_setaffinity", lambda pid, cpus: calls.append(set(cpus)),
+                        raising=False)
+    monkeypatch.setattr(os, "cpu_count", lambda: 96)
+    monkeypatch.delenv("MOE_BENCH_NO_AFFINITY", raising=False)
+    fake = types.SimpleNamespace(
+        nvmlDeviceGetHandleByUUID=lambda u: u,
+        nvmlDeviceGetCpuAffinity=lambda h, words: [0xFFFF0000, 0xFF][:words])   # cores 16-31, 64-71
+    assert bench.bind_host_threads_near_gpu(0, nvml=fake, uuid="abc") == 16
+    assert calls == [set(range(16, 32))]
+    narrow = types.SimpleNamespace(nvmlDeviceGetHandleByUUID=lambda u: u,
+                                   nvmlDeviceGetCpuAffinity=lambda h, words: [0, 0x1][:words])
+    assert bench.bind_host_threads_near_gpu(0, nvml=narrow, uuid="abc") is None
+
+    def broken(h, words):
+        raise RuntimeError("not supported")
+    bad = types.SimpleNamespace(nvmlDeviceGetHandleByUUID=lambda u: u,
+                                nvmlDeviceGetCpuAffinity=broken)
+    assert bench.bind_host_threads_near_gpu(0, nvml=bad, uuid="abc") is None
+    monkeypatch.setenv("MOE_BENCH_NO_AFFINITY", "1")
+    assert bench.bind_host_threads_near_gpu(0, nvml=fake, uuid="abc") is None
+    assert len(calls) == 1
