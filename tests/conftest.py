@@ -12,7 +12,7 @@ for p in (REPO, REPO / "mega-moe-td_b200"):
         sys.path.insert(0, str(p))
 
 GOLDEN_DIR = Path(__file__).resolve().parent / "golden"
-GOLDEN_CASES = ["w1_e8_k2", "w2_e8_k3_drop", "w4_e16_k4_zipf"]
+GOLDEN_CASES = ["w1_e8_k2", "w2_e8_k3_drop", "w4_e16_k4_zipf", "w8_e16_k4"]
 
 
 def pytest_configure(config):

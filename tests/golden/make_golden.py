@@ -42,6 +42,8 @@ CASES = {
                           zipf=None, drop=0.25),
     "w4_e16_k4_zipf": dict(world=4, tokens=32, hidden=64, ffn=128, experts=16, top_k=4, seed=2,
                            zipf=1.2, drop=0.0),
+    "w8_e16_k4": dict(world=8, tokens=24, hidden=64, ffn=64, experts=16, top_k=4, seed=3,
+                      zipf=None, drop=0.1),
 }
 
 
