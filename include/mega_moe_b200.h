@@ -7,7 +7,7 @@
  * its own: its Python operator launches Triton-Ascend kernels directly.  Each entry
  * point below therefore names the reference *launch site* it stands in for
  * (path:line inside the reference project).  `mega_moe/_native.py` binds all of them
- * with ctypes; INTEGRATION.md shows the binding.
+ * with ctypes.
  *
  * Conventions
  *   - every function returns 0 (MM_OK) or a negative MM_ERR_* code and never throws;
@@ -133,7 +133,12 @@ int mm_route_local_static(const int32_t* selected, int num_routes, int top_k, in
  *   order_prefix [world * epr + 1]: prefix of the local counts in dispatch order (local expert
  *     slot outermost, destination rank rotated by `rank`), bucket_done [world * epr]: zeroed
  *     delivery counters; both feed mm_dispatch_desc
- * If M exceeds capacity_rows the status record gets code 2 and num_mtiles is 0. */
+ *   row_arrival / arrival_row [capacity_rows], both or neither (may be null): the permutation
+ *     between this receive order (expert-major, then source) and the source-major arrival
+ *     order of an all-to-all, and its inverse: the saved contract's local_sort_idxs / inv_local
+ *     (ops/_single_saved_adapter.py:335-338)
+ * If a destination's total exceeds capacity_rows the status record gets code 2, num_mtiles and
+ * num_mtiles2 are 0 and no entry of the row-tile tables is written. */
 int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, int bins,
                       int capacity_rows, int32_t* send_bucket_starts,
                       int32_t* send_bucket_dst_starts, int32_t* recv_counts_re,
@@ -142,7 +147,8 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
                       int32_t* mtile_group, int32_t* mtile_row0, int32_t* num_mtiles,
                       int32_t* mtile2_group, int32_t* mtile2_row0, int32_t* num_mtiles2,
                       int32_t* row_src_rank, int32_t* row_src_pos, int32_t* order_prefix,
-                      int32_t* bucket_done, void* status, cudaStream_t stream);
+                      int32_t* bucket_done, int32_t* row_arrival, int32_t* arrival_row,
+                      void* status, cudaStream_t stream);
 
 /* ---- dispatch / combine data movement ---------------------------------------------- */
 /* Push send row i (= src[send_token[i]]) to rank send_bucket[i] / epr at row
@@ -209,7 +215,7 @@ typedef struct mm_dispatch_desc {
   const int32_t* count_row;           /* rows per bucket (local count row) */
   const int32_t* order_prefix;        /* from mm_route_finalize */
   const int32_t* local_stats;         /* [0] = number of send rows */
-  int32_t* bucket_done;               /* zeroed [world * epr] */
+  int32_t* bucket_done;               /* [world * epr], zero at launch; left zero again */
   void* const* peer_rows;             /* device array of `world` receive-buffer bases */
   float* const* peer_weights;         /* device array of `world` weight-buffer bases */
   int32_t* const* peer_flags;         /* device array of `world` flag-array bases */
@@ -224,10 +230,13 @@ typedef struct mm_dispatch_desc {
  *   raw_out [rows, 2F] = bf16 gate | up (may be null; in tile mode 2 a non-null raw_out
  *     selects the two-step form: a plain GEMM stores the raw rows, a row-wise pass applies
  *     the activation - same rounding points, two launches)
+ *   row_weight_bf16_out [rows] = bf16(row_weight), the received routing weights as the
+ *     backward reads them (ops/_torch_forward.py:254); may be null
  *   dispatch: null for rows already resident in `a`, else the fused dispatch above */
-int mm_fc1_swiglu(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void* act_out, int64_t ld_act, void* raw_out,
-                  int64_t ld_raw, const float* row_weight, int activation, float beta,
-                  float linear_beta, float clamp_limit, cudaStream_t stream);
+int mm_fc1_swiglu(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void* act_out,
+                  int64_t ld_act, void* raw_out, int64_t ld_raw, const float* row_weight,
+                  void* row_weight_bf16_out, int activation, float beta, float linear_beta,
+                  float clamp_limit, cudaStream_t stream);
 
 /* out[rows of g, 0:N] = bf16(A[rows of g] * B_g)
  * (reference: kernels/dispatch_fc1.py:580-751 for FC1 without activation,

@@ -24,7 +24,7 @@ using namespace mm;
 
 extern "C" {
 
-int mm_abi_version(void) { return 1; }
+int mm_abi_version(void) { return 2; }
 
 const char* mm_last_error(void) { return g_error; }
 

@@ -58,12 +58,11 @@ bool encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* di
   return true;
 }
 
-std::once_flag g_attr_once;
-int g_num_sms = 0;
+PerDeviceOnce g_gemm_attr;
 
-bool prepare_kernel() {
-  static bool ok = false;
-  std::call_once(g_attr_once, [] {
+// Opt-in shared-memory size of the three GEMM kernels on the current device, and its SM count.
+bool prepare_kernel(int* num_sms) {
+  const int rc = g_gemm_attr([] {
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
     if (e == cudaSuccess)
@@ -74,16 +73,12 @@ bool prepare_kernel() {
                                kGemmSmemBytes);
     if (e != cudaSuccess) {
       set_error("cudaFuncSetAttribute(grouped_gemm_kernel): %s", cudaGetErrorString(e));
-      return;
+      return (int)MM_ERR_CUDA;
     }
-    ok = true;
+    return (int)MM_OK;
   });
-  if (!ok) return false;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return false;
-  if (cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-    return false;
-  return true;
+  if (rc != MM_OK) return false;
+  return mm_num_sms(num_sms) == MM_OK;
 }
 
 #ifdef MM_PROFILE
@@ -92,13 +87,14 @@ unsigned long long* g_prof_buffer = nullptr;   // [grid, 16] counters of the nex
 
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
            const GemmParams& p_in, int grid_limit, cudaStream_t stream) {
-  if (!prepare_kernel()) return MM_ERR_CUDA;
+  int num_sms = 0;
+  if (!prepare_kernel(&num_sms)) return MM_ERR_CUDA;
   GemmParams p = p_in;
 #ifdef MM_PROFILE
   p.prof = g_prof_buffer;
   p.prof_skip_mma = getenv("MM_PROFILE_SKIP_MMA") != nullptr;
 #endif
-  int grid = g_num_sms;
+  int grid = num_sms;
   if (grid_limit > 0 && grid_limit < grid) grid = grid_limit;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
@@ -117,7 +113,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
     static int max_pairs = -1;
     if (max_pairs < 0) {
       cudaLaunchConfig_t probe = cfg;
-      probe.gridDim = dim3(g_num_sms & ~1, 1, 1);
+      probe.gridDim = dim3(num_sms & ~1, 1, 1);
       int n = 0;
       cudaError_t pe = cudaOccupancyMaxActiveClusters(&n, grouped_gemm_kernel<true>, &probe);
       if (pe != cudaSuccess || n <= 0) {
@@ -146,13 +142,14 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
 // Transposed-product kernel for groups with few rows (tile mode 2).
 int launch_skinny(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p_in,
                   int grid_limit, cudaStream_t stream) {
-  if (!prepare_kernel()) return MM_ERR_CUDA;
+  int num_sms = 0;
+  if (!prepare_kernel(&num_sms)) return MM_ERR_CUDA;
   GemmParams p = p_in;
 #ifdef MM_PROFILE
   p.prof = nullptr;
   p.prof_skip_mma = getenv("MM_PROFILE_SKIP_MMA") != nullptr;
 #endif
-  int grid = g_num_sms;
+  int grid = num_sms;
   if (grid_limit > 0 && grid_limit < grid) grid = grid_limit;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
@@ -285,8 +282,9 @@ extern "C" {
 
 int mm_fc1_swiglu(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void* act_out,
                   int64_t ld_act, void* raw_out,
-                  int64_t ld_raw, const float* row_weight, int activation, float beta,
-                  float linear_beta, float clamp_limit, cudaStream_t stream) {
+                  int64_t ld_raw, const float* row_weight, void* row_weight_bf16_out,
+                  int activation, float beta, float linear_beta, float clamp_limit,
+                  cudaStream_t stream) {
   if (!d || !act_out || !row_weight) {
     set_error("mm_fc1_swiglu: null argument");
     return MM_ERR_ARG;
@@ -297,6 +295,7 @@ int mm_fc1_swiglu(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void*
   p.out2 = reinterpret_cast<__nv_bfloat16*>(raw_out);
   p.ld_out2 = ld_raw;
   p.row_weight = row_weight;
+  p.row_weight_bf16 = reinterpret_cast<__nv_bfloat16*>(row_weight_bf16_out);
   p.act = activation;
   p.act_beta = beta;
   p.act_linear_beta = linear_beta;
@@ -315,12 +314,14 @@ int mm_fc1_swiglu(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void*
     g.out = reinterpret_cast<__nv_bfloat16*>(raw_out);
     g.ld_out = ld_raw;
     g.out2 = nullptr;
+    g.row_weight_bf16 = nullptr;
     const int rc = grouped_rows_gemm(kEpiStore, wide, g, stream);
     if (rc != MM_OK) return rc;
     GemmParams a{};
     a.out = p.out;
     a.ld_out = p.ld_out;
     a.row_weight = row_weight;
+    a.row_weight_bf16 = p.row_weight_bf16;
     a.act = activation;
     a.act_beta = beta;
     a.act_linear_beta = linear_beta;
@@ -329,7 +330,9 @@ int mm_fc1_swiglu(const mm_gemm_desc* d, const mm_dispatch_desc* dispatch, void*
     a.group_offs = d->group_offs;
     a.num_groups = d->num_groups;
     const int max_rows = (int)(d->a_rows_cap < (int64_t)INT32_MAX ? d->a_rows_cap : INT32_MAX);
-    int blocks = g_num_sms * 8;
+    int sms = 148;
+    mm_num_sms(&sms);
+    int blocks = sms * 8;
     if (blocks > max_rows) blocks = max_rows;
     if (blocks < 1) blocks = 1;
     swiglu_rows_kernel<<<blocks, kSwigluRowsThreads, 0, stream>>>(

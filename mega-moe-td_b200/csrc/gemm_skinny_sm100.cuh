@@ -285,6 +285,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll 1
         for (int j = 0; j < nchunks; ++j) {
           const float w_mine = w_next;
+          if (q == 0 && ti.n0 == 0 && p.row_weight_bf16 != nullptr &&
+              j * 32 + (int32_t)lane < ti.rows_valid)
+            p.row_weight_bf16[ti.row0 + j * 32 + (int32_t)lane] = __float2bfloat16_rn(w_mine);
           const int32_t rn = (j + 1) * 32 + (int32_t)lane;
           w_next = rn < ti.rows_valid ? p.row_weight[ti.row0 + rn] : 0.0f;
           uint32_t rg[32], ru[32];
@@ -362,6 +365,8 @@ swiglu_rows_kernel(const GemmParams p, const __nv_bfloat16* __restrict__ raw, in
     const uint4* up = reinterpret_cast<const uint4*>(raw + (int64_t)row * ld_raw + p.swiglu_F);
     uint4* act = reinterpret_cast<uint4*>(p.out + (int64_t)row * p.ld_out);
     const float w = p.row_weight[row];
+    if (threadIdx.x == 0 && p.row_weight_bf16 != nullptr)
+      p.row_weight_bf16[row] = __float2bfloat16_rn(w);
     for (int32_t i = threadIdx.x; i < chunks; i += kSwigluRowsThreads) {
       const uint4 g4 = gate[i];
       const uint4 u4 = up[i];

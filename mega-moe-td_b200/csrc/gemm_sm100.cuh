@@ -80,6 +80,7 @@ struct GemmParams {
   __nv_bfloat16* out2;          // kEpiSwiglu: raw gate|up rows, may be null
   int64_t ld_out2;
   const float* row_weight;      // kEpiSwiglu: fp32 weight of each row
+  __nv_bfloat16* row_weight_bf16;  // kEpiSwiglu: bf16 copy of the row weights (out), may be null
   const int32_t* row_dst_rank;  // kEpiScatter: destination rank of each row
   const int32_t* row_dst_pos;   // kEpiScatter: destination row index
   __nv_bfloat16* const* peer_bases;  // kEpiScatter: base pointer of the destination buffer per rank
@@ -99,7 +100,8 @@ struct GemmParams {
   const int32_t* disp_counts;         // rows per bucket (local count row)
   const int32_t* disp_order_prefix;   // [buckets + 1] prefix of the counts in dispatch order
   const int32_t* disp_num_send;       // device scalar: number of send rows
-  int32_t* disp_bucket_done;          // [buckets] rows delivered so far (zeroed before launch)
+  int32_t* disp_bucket_done;          // [buckets] rows delivered so far: zero at launch, and zero
+                                      // again once a bucket is complete
   void* const* disp_peer_rows;        // receive buffer base per rank
   float* const* disp_peer_weights;    // routing-weight buffer base per rank
   int32_t* const* disp_peer_flags;    // arrival flags base per rank: [world * epr] per rank
@@ -372,6 +374,8 @@ __device__ __forceinline__ void dispatch_warp_run(const GemmParams& p, int32_t d
           if (b < 0) continue;
           const int32_t done = atomicAdd(&p.disp_bucket_done[b], 1) + 1;
           if (done == p.disp_counts[b]) {
+            // the last row of the bucket: leave the counter at zero for the next launch
+            p.disp_bucket_done[b] = 0;
             __threadfence_system();
             int32_t* flag =
                 p.disp_peer_flags[dst_of[r]] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
@@ -996,6 +1000,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint8_t* raw_ptr =
             p.out2 ? reinterpret_cast<uint8_t*>(p.out2 + grow * p.ld_out2 + ti.n0) : nullptr;
         const float w = valid ? p.row_weight[grow] : 0.0f;
+        // the backward reads the received routing weights as bf16; the first column tile of
+        // every row tile leaves that copy
+        if (valid && ti.n0 == 0 && p.row_weight_bf16 != nullptr)
+          p.row_weight_bf16[grow] = __float2bfloat16_rn(w);
         uint8_t* sa = stg;          // activation, 64 columns per pass
         uint8_t* sg = stg + 4096;   // raw gate (first half of the pass), then raw up
 #pragma unroll 1

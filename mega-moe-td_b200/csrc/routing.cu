@@ -172,7 +172,9 @@ route_finalize_kernel(const int32_t* __restrict__ cube, int rank, int world, int
   int32_t* loc = sm + 2 * nb;
   __shared__ int warp_sums[32];
   __shared__ int scan_total;
+  __shared__ int max_required;   // largest per-destination receive total
   const int tid = threadIdx.x;
+  if (tid == 0) max_required = 0;
 
   for (int b = tid; b < nb; b += 1024) {
     int t = 0, p = 0;
@@ -252,6 +254,7 @@ route_finalize_kernel(const int32_t* __restrict__ cube, int rank, int world, int
       }
       if (lane == 0) {
         stats[2 + d] = base;
+        atomicMax(&max_required, base);
         if (d == rank) {
           recv_expert_offs[epr] = base;
           stats[0] = base;
@@ -304,10 +307,12 @@ route_finalize_kernel(const int32_t* __restrict__ cube, int rank, int world, int
   }
   __syncthreads();
 
-  // Row-tile tables of the local experts (128 rows per tile, and 256 for CTA pairs), receive
-  // total and capacity check.
+  // Capacity check first: the tile tables are sized for at most capacity_rows received rows
+  // (capacity / tile rows + epr entries), so on overflow no tile is written at all.
+  const bool overflow = max_required > capacity_rows;
+  // Row-tile tables of the local experts (128 rows per tile, and 256 for CTA pairs).
   int total_tiles[2] = {0, 0};
-  for (int pass = 0; pass < 2; ++pass) {
+  for (int pass = 0; pass < 2 && !overflow; ++pass) {
     const int shift = pass == 0 ? 7 : 8;
     const int rows_per_tile = 1 << shift;
     int32_t* tg = pass == 0 ? mtile_group : mtile2_group;
@@ -340,10 +345,8 @@ route_finalize_kernel(const int32_t* __restrict__ cube, int rank, int world, int
     __syncthreads();
   }
   if (tid == 0) {
-    int max_required = 0;
-    for (int d = 0; d < world; ++d) max_required = max(max_required, stats[2 + d]);
     stats[1] = max_required;
-    if (max_required > capacity_rows) {
+    if (overflow) {
       report_status(status, kCapacityOverflow, 0, 0, capacity_rows, max_required);
       *num_mtiles = 0;
       *num_mtiles2 = 0;
@@ -355,13 +358,37 @@ route_finalize_kernel(const int32_t* __restrict__ cube, int rank, int world, int
 }
 
 // Per received row: the rank that sent it and the row's position in that rank's send order.
-// One warp per (local expert, source) segment.
+// One warp per (local expert, source) segment.  Optionally also the permutation between this
+// receive order (expert-major, then source) and the source-major "arrival" order of an
+// all-to-all (source-major, then expert): row_arrival[row] = arrival index of the row,
+// arrival_row = its inverse.
 __global__ void __launch_bounds__(256)
 route_row_tables_kernel(const int32_t* __restrict__ recv_expert_offs,
                         const int32_t* __restrict__ recv_seg_starts,
-                        const int32_t* __restrict__ pull_dst_start, int world, int epr,
+                        const int32_t* __restrict__ pull_dst_start,
+                        const int32_t* __restrict__ recv_counts_re, int world, int epr,
                         int capacity_rows, int32_t* __restrict__ row_src_rank,
-                        int32_t* __restrict__ row_src_pos) {
+                        int32_t* __restrict__ row_src_pos, int32_t* __restrict__ row_arrival,
+                        int32_t* __restrict__ arrival_row) {
+  extern __shared__ int32_t src_start[];   // [world] rows received from the sources before s
+  const bool want_perm = row_arrival != nullptr;
+  if (want_perm) {
+    for (int s = threadIdx.x; s < world; s += blockDim.x) {
+      int t = 0;
+      for (int e = 0; e < epr; ++e) t += recv_counts_re[s * epr + e];
+      src_start[s] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int run = 0;
+      for (int s = 0; s < world; ++s) {
+        const int t = src_start[s];
+        src_start[s] = run;
+        run += t;
+      }
+    }
+    __syncthreads();
+  }
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int nseg = world * epr;
@@ -373,11 +400,17 @@ route_row_tables_kernel(const int32_t* __restrict__ recv_expert_offs,
     const int cnt = recv_seg_starts[le * (world + 1) + s + 1] - seg0;
     const int row0 = recv_expert_offs[le] + seg0;
     const int pos0 = pull_dst_start[le * world + s];
+    // the rows of source s arrive in its send order, which starts at this rank's expert 0
+    const int arr0 = want_perm ? src_start[s] + pos0 - pull_dst_start[s] : 0;
     for (int i = lane; i < cnt; i += 32) {
       const int row = row0 + i;
       if (row < capacity_rows) {
         row_src_rank[row] = s;
         row_src_pos[row] = pos0 + i;
+        if (want_perm) {
+          row_arrival[row] = arr0 + i;
+          if (arr0 + i < capacity_rows) arrival_row[arr0 + i] = row;
+        }
       }
     }
   }
@@ -386,11 +419,23 @@ route_row_tables_kernel(const int32_t* __restrict__ recv_expert_offs,
 // ---------------------------------------------------------------------------------
 // Router in front of the layer: top-k of the router logits and the softmax over the selected
 // logits.  One warp per token; every lane keeps its share of the row in registers and the
-// warp extracts the maximum k times (ties go to the lower expert id), so the selected experts
-// come out in descending order of their logits like torch.topk.
+// warp extracts the maximum k times, so the selected experts come out in the order of a
+// stable descending sort of the row: ties (equal logits, -inf included, +0 and -0) go to the
+// lower expert id and a NaN logit ranks above every number, like torch.sort / torch.topk.
+// A row with fewer than k finite logits therefore still selects k distinct real experts; its
+// weights follow the softmax's arithmetic (NaN when a NaN or only -inf logits are selected).
 // ---------------------------------------------------------------------------------
 constexpr int kRouterPerLane = 32;               // up to 1024 experts
 constexpr int kRouterWarps = 4;
+constexpr int32_t kRouterTaken = INT32_MIN;      // below the key of every logit, -inf included
+
+// Order-preserving integer key of a logit: a < b <=> key(a) < key(b); NaN above +inf.
+__device__ __forceinline__ int32_t router_key(float v) {
+  if (v != v) return INT32_MAX;
+  if (v == 0.0f) return 0;
+  const int32_t b = __float_as_int(v);
+  return b >= 0 ? b : (b ^ 0x7fffffff);
+}
 
 __global__ void __launch_bounds__(32 * kRouterWarps)
 router_topk_kernel(const float* __restrict__ logits, int64_t ld, int tokens, int experts, int top_k,
@@ -399,44 +444,46 @@ router_topk_kernel(const float* __restrict__ logits, int64_t ld, int tokens, int
   const int token = blockIdx.x * kRouterWarps + (threadIdx.x >> 5);
   if (token >= tokens) return;
   const float* row = logits + (int64_t)token * ld;
-  float v[kRouterPerLane];
+  int32_t key[kRouterPerLane];
 #pragma unroll
   for (int i = 0; i < kRouterPerLane; ++i) {
     const int e = i * 32 + lane;
-    v[i] = e < experts ? row[e] : -INFINITY;
+    key[i] = e < experts ? router_key(row[e]) : kRouterTaken;
   }
   float my_logit = 0.0f;   // lane j keeps the j-th selected logit
   int my_expert = 0;
   float top = 0.0f;
   for (int j = 0; j < top_k; ++j) {
-    float best = -INFINITY;
+    int32_t best = kRouterTaken;
     int best_e = 0x7fffffff;
 #pragma unroll
     for (int i = 0; i < kRouterPerLane; ++i) {
-      // strict > keeps the lowest expert id of this lane among equal values
-      if (v[i] > best) {
-        best = v[i];
+      // strict > keeps the lowest expert id of this lane among equal keys
+      if (key[i] > best) {
+        best = key[i];
         best_e = i * 32 + lane;
       }
     }
 #pragma unroll
     for (int k = 16; k > 0; k >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, k);
+      const int32_t ob = __shfl_xor_sync(0xffffffffu, best, k);
       const int oe = __shfl_xor_sync(0xffffffffu, best_e, k);
       if (ob > best || (ob == best && oe < best_e)) {
         best = ob;
         best_e = oe;
       }
     }
-    if (j == 0) top = best;
+    // top_k <= experts, so a real (not yet taken) expert always remains
+    const float best_v = row[best_e];
+    if (j == 0) top = best_v;
     if (lane == j) {
-      my_logit = best;
+      my_logit = best_v;
       my_expert = best_e;
     }
     if ((best_e & 31) == lane) {
 #pragma unroll
       for (int i = 0; i < kRouterPerLane; ++i)
-        if (i == (best_e >> 5)) v[i] = -INFINITY;
+        if (i == (best_e >> 5)) key[i] = kRouterTaken;
     }
   }
   // softmax over the selected logits (fp32, max-subtracted)
@@ -484,17 +531,18 @@ int mm_route_local(const int32_t* selected, int num_routes, int top_k, int num_e
   const int nblk = (num_routes + kRouteChunk - 1) / kRouteChunk;
   int32_t* block_hist = reinterpret_cast<int32_t*>(scratch);
   int32_t* bucket_start = block_hist + (size_t)nblk * bins;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(route_scatter_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (kRouteWarps + 1) * kMaxBins * (int)sizeof(int32_t));
-    if (e != cudaSuccess) {
-      set_error("cudaFuncSetAttribute(route_scatter_kernel): %s", cudaGetErrorString(e));
-      return MM_ERR_CUDA;
-    }
-    attr_done = true;
-  }
+  static PerDeviceOnce scatter_attr;
+  if (int rc = scatter_attr([] {
+        cudaError_t e = cudaFuncSetAttribute(route_scatter_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (kRouteWarps + 1) * kMaxBins * (int)sizeof(int32_t));
+        if (e != cudaSuccess) {
+          set_error("cudaFuncSetAttribute(route_scatter_kernel): %s", cudaGetErrorString(e));
+          return (int)MM_ERR_CUDA;
+        }
+        return (int)MM_OK;
+      }))
+    return rc;
   if (nblk > 0) {
     route_hist_kernel<<<nblk, kRouteThreads, bins * sizeof(int32_t), stream>>>(
         selected, num_routes, num_experts, bins, block_hist);
@@ -522,9 +570,14 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
                       int32_t* mtile_group, int32_t* mtile_row0, int32_t* num_mtiles,
                       int32_t* mtile2_group, int32_t* mtile2_row0, int32_t* num_mtiles2,
                       int32_t* row_src_rank, int32_t* row_src_pos, int32_t* order_prefix,
-                      int32_t* bucket_done, void* status, cudaStream_t stream) {
+                      int32_t* bucket_done, int32_t* row_arrival, int32_t* arrival_row,
+                      void* status, cudaStream_t stream) {
   if (!order_prefix || !bucket_done || !mtile2_group || !mtile2_row0 || !num_mtiles2) {
     set_error("mm_route_finalize: null argument");
+    return MM_ERR_ARG;
+  }
+  if ((row_arrival == nullptr) != (arrival_row == nullptr)) {
+    set_error("mm_route_finalize: row_arrival and arrival_row come together or not at all");
     return MM_ERR_ARG;
   }
   if (!count_cube || !send_bucket_starts || !send_bucket_dst_starts || !recv_counts_re ||
@@ -540,17 +593,18 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
     return MM_ERR_ARG;
   }
   const size_t smem = (size_t)(3 * nb + epr + 1) * sizeof(int32_t);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(route_finalize_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (4 * kMaxBins + 1) * (int)sizeof(int32_t));
-    if (e != cudaSuccess) {
-      set_error("cudaFuncSetAttribute(route_finalize_kernel): %s", cudaGetErrorString(e));
-      return MM_ERR_CUDA;
-    }
-    attr_done = true;
-  }
+  static PerDeviceOnce finalize_attr;
+  if (int rc = finalize_attr([] {
+        cudaError_t e = cudaFuncSetAttribute(route_finalize_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (4 * kMaxBins + 1) * (int)sizeof(int32_t));
+        if (e != cudaSuccess) {
+          set_error("cudaFuncSetAttribute(route_finalize_kernel): %s", cudaGetErrorString(e));
+          return (int)MM_ERR_CUDA;
+        }
+        return (int)MM_OK;
+      }))
+    return rc;
   route_finalize_kernel<<<1, 1024, smem, stream>>>(
       count_cube, rank, world, epr, bins, capacity_rows, send_bucket_starts, send_bucket_dst_starts,
       recv_counts_re, recv_per_expert, recv_expert_offs, recv_seg_starts, pull_dst_start, stats,
@@ -560,9 +614,9 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
   if (int rc = check_launch("route_finalize_kernel")) return rc;
   const int nseg = world * epr;
   const int blocks = (nseg + 7) / 8;
-  route_row_tables_kernel<<<blocks, 256, 0, stream>>>(recv_expert_offs, recv_seg_starts,
-                                                      pull_dst_start, world, epr, capacity_rows,
-                                                      row_src_rank, row_src_pos);
+  route_row_tables_kernel<<<blocks, 256, world * sizeof(int32_t), stream>>>(
+      recv_expert_offs, recv_seg_starts, pull_dst_start, recv_counts_re, world, epr, capacity_rows,
+      row_src_rank, row_src_pos, row_arrival, arrival_row);
   return check_launch("route_row_tables_kernel");
 }
 
@@ -578,7 +632,8 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
 //
 //  * The array is kRouteStaticScratchBytes (1 MiB) per GPU that loads the library, held
 //    until the process exits.  Requests whose scratch need (mm_route_scratch_bytes) exceeds it
-//    are rejected with MM_ERR_LIMIT; 1 MiB covers 262 144 routes at 1024 bins.
+//    are rejected with MM_ERR_LIMIT; 1 MiB covers 522 240 routes at 1024 bins
+//    ((blocks of 2048 routes + 1) x bins x 4 bytes).
 //  * The first call on each device looks the array's device address up
 //    (cudaGetSymbolAddress, with that device current) and caches it; make that first call
 //    outside any stream capture.  Later calls on the device do no set-up.

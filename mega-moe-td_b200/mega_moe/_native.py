@@ -64,14 +64,15 @@ SIGNATURES = {
     "mm_route_local_static": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, _c_i32p,
                                         _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_ptr]),
     "mm_route_finalize": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int] +
-                          [_c_i32p] * 18 + [_c_ptr, _c_ptr]),
+                          [_c_i32p] * 20 + [_c_ptr, _c_ptr]),
     "mm_dispatch_rows": (C.c_int, [_c_ptr, C.c_int, _c_ptr, _c_i32p, _c_i32p, _c_i32p, _c_i32p,
                                    _c_i32p, _c_i32p, C.c_int, C.c_int, C.c_int, _c_ptr, _c_ptr,
                                    _c_ptr]),
     "mm_topk_reduce": (C.c_int, [_c_ptr, C.c_int64, _c_i32p, C.c_int, C.c_int, C.c_int, _c_ptr,
                                  _c_ptr, _c_ptr, _c_ptr]),
-    "mm_fc1_swiglu": (C.c_int, [C.POINTER(GemmDesc), C.POINTER(DispatchDesc), _c_ptr, C.c_int64, _c_ptr, C.c_int64, _c_ptr,
-                                C.c_int, C.c_float, C.c_float, C.c_float, _c_ptr]),
+    "mm_fc1_swiglu": (C.c_int, [C.POINTER(GemmDesc), C.POINTER(DispatchDesc), _c_ptr, C.c_int64,
+                                _c_ptr, C.c_int64, _c_ptr, _c_ptr, C.c_int, C.c_float, C.c_float,
+                                C.c_float, _c_ptr]),
     "mm_grouped_gemm": (C.c_int, [C.POINTER(GemmDesc), C.POINTER(DispatchDesc), _c_ptr,
                                   C.c_int64, _c_ptr]),
     "mm_grouped_gemm_scatter": (C.c_int, [C.POINTER(GemmDesc), _c_i32p, _c_i32p, _c_ptr,

@@ -158,11 +158,11 @@ def fused_dispatch_enabled(ctx=None) -> bool:
 
 
 def make_dispatch_desc(ctx: MoEForwardContext, src: torch.Tensor, weights, plan=None,
-                       reset_counters: bool = False) -> N.DispatchDesc:
-    """Descriptor of the dispatch fused into the next grouped GEMM (rows of ``src``)."""
+                       region: str = "peer_mem") -> N.DispatchDesc:
+    """Descriptor of the dispatch fused into the next grouped GEMM: the rows of ``src`` go to
+    the owning ranks' ``region``.  The per-bucket delivery counters need no clearing: the
+    metadata kernel zeroes them and every fused launch leaves them at zero again."""
     p = plan if plan is not None else ctx
-    if reset_counters:
-        ctx.disp_bucket_done.zero_()
     d = N.DispatchDesc()
     d.src = src.data_ptr()
     d.weights = N.ptr(weights)
@@ -174,7 +174,7 @@ def make_dispatch_desc(ctx: MoEForwardContext, src: torch.Tensor, weights, plan=
     d.order_prefix = p.disp_order_prefix.data_ptr()
     d.local_stats = p.metadata_local_stats.data_ptr()
     d.bucket_done = ctx.disp_bucket_done.data_ptr()
-    d.peer_rows = ctx.symm.peer_table("peer_mem").data_ptr()
+    d.peer_rows = ctx.symm.peer_table(region).data_ptr()
     d.peer_weights = (ctx.symm.peer_table("routing_weight_mem").data_ptr()
                       if weights is not None else None)
     d.peer_flags = ctx.symm.peer_table("dispatch_flags").data_ptr()
@@ -209,13 +209,13 @@ def dispatch_rows(ctx: MoEForwardContext, src: torch.Tensor, weights, num_routes
 
 
 def fc1_swiglu(ctx, desc, act_out, raw_out, row_weight, activation, beta, linear_beta, clamp,
-               dispatch=None):
+               dispatch=None, weight_bf16_out=None):
     with _timed("fc1_swiglu"):
         N.check(N.lib().mm_fc1_swiglu(
             C.byref(desc), C.byref(dispatch) if dispatch is not None else None,
             act_out.data_ptr(), act_out.stride(0),
             N.ptr(raw_out), raw_out.stride(0) if raw_out is not None else 0,
-            row_weight.data_ptr(), N.ACT_IDS[activation], float(beta),
+            row_weight.data_ptr(), N.ptr(weight_bf16_out), N.ACT_IDS[activation], float(beta),
             float(linear_beta) if linear_beta is not None else 0.0, float(clamp),
             N.stream_ptr()), "mm_fc1_swiglu")
     # skinny tiles with a raw buffer: plain GEMM + activation pass (two kernels)

@@ -12,7 +12,18 @@ Given ``dy [T, H]`` the stages are the reference's (src/mega_moe/ops/backward.py
 5. FC1 weight gradient ``grad_fc1[e] = grad_fc1_output^T @ recv_hidden_sorted``.
 
 All GEMMs run on the tcgen05 grouped-GEMM kernel; the name ``moe_backward_triton`` is kept
-only because callers import it.
+only because callers import it.  ``MOE_BWD_MEGA=1`` (reference: ops/backward.py:100-224, one
+launch for all stages on Ascend) is accepted and selects this same chain of launches on one
+stream: on this hardware the stages already run back to back without host synchronisation,
+and the results are identical by construction.
+
+Execution order on the stream (the numbering above is the reference's): 1, 2, 4 (GEMM +
+stores to the source ranks), 5, barrier signal, 3, barrier wait, gather-sum of 4.  The dy
+rows are received in a second symmetric region (``peer_grad_mem``), so the forward's received
+rows in ``peer_mem`` stay readable until the next forward; stage 5 reads them and therefore
+runs before this rank signals (a peer that has seen every signal may start its next forward
+and overwrite them), while stage 3 reads only the dy rows, which no peer rewrites before the
+next backward, and absorbs the ranks' skew between the two halves of the barrier.
 """
 
 from __future__ import annotations
@@ -68,7 +79,8 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
             raise ValueError(
                 "saved is missing recv_hidden_sorted; the fused backward requires "
                 "the activation section (replay saved or return_saved=True)")
-        if recv_hidden_sorted.data_ptr() == peer_mem.data_ptr():
+        if (recv_hidden_sorted.data_ptr() == peer_mem.data_ptr()
+                and not saved.get("_saved_views")):
             raise ValueError(
                 "saved['recv_hidden_sorted'] aliases peer_mem; the receive buffer "
                 "is single-in-flight and was overwritten after dispatch")
@@ -110,37 +122,19 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     # ---- stage 1: dispatch dy + FC2 input gradient ------------------------------------
     # The dy dispatch is fused into the GEMM launch (it runs even when this rank received
     # nothing, because its rows are other ranks' input).
-    recv_dy = ctx.peer_mem.view(cap, hidden)
+    recv_dy = ctx.peer_grad_mem.view(cap, hidden)
     grad_swiglu = torch.empty(max(m, 1), ffn, dtype=dtype, device=device)[:m]
     desc = L.make_desc(ctx, recv_dy, cap, hidden, fc2, k_dim=1, n_dim=2, n_out=ffn,
                        k_extent=hidden, **tiles)
     if L.fused_dispatch_enabled(ctx) and not recompute:
-        disp = L.make_dispatch_desc(ctx, dy, None, plan=plan, reset_counters=True)
+        disp = L.make_dispatch_desc(ctx, dy, None, plan=plan, region="peer_grad_mem")
     else:
         disp = None
-        L.dispatch_rows(ctx, dy, None, num_routes, plan=plan)
+        L.dispatch_rows(ctx, dy, None, num_routes, plan=plan, region="peer_grad_mem")
         ctx.rank_barrier()
     L.grouped_gemm(desc, grad_swiglu if m > 0 else grad_swiglu.new_empty(1, ffn),
                    name="fc2_dgrad", dispatch=disp)
     grad_fc2_out_sorted = recv_dy[:m]
-
-    # ---- stage 3: FC2 weight gradient (reads the receive buffer, so it runs before the
-    #      barrier of stage 4 lets peers dispatch into it again) ---------------------------
-    if recompute:
-        # weighted activation rows from the saved FC1 rows and the saved bf16 routing weights
-        act = torch.empty(max(m, 1), ffn, dtype=dtype, device=device)[:m]
-        if m > 0:
-            L.swiglu_recompute(fc1_output, saved["recv_weights_sorted"], ffn, plan.metadata_stats,
-                               m, act, *act_args, fc1_scale=fc1_scale, scale_group=scale_group)
-    else:
-        act = saved["swiglu_out_weighted"]
-    grad_ws = saved.get("_grad_workspace")
-    if m > 0:
-        grad_fc2 = (grad_ws["grad_fc2"] if grad_ws is not None
-                    else torch.empty(epr, hidden, ffn, dtype=dtype, device=device))
-        L.grouped_wgrad(ctx, recv_dy, act, m, group_offs, epr, grad_fc2, name="fc2_wgrad")
-    else:
-        grad_fc2 = torch.zeros(epr, hidden, ffn, dtype=dtype, device=device)
 
     # ---- stage 2: gated-activation backward (+ gate gradient pushed to the source) -----
     grad_fc1_output = torch.empty(m, 2 * ffn, dtype=dtype, device=device)
@@ -150,17 +144,15 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
                      plan.metadata_stats, m, grad_fc1_output, grad_gate, *act_args, plan=plan,
                      fc1_scale=fc1_scale, scale_group=scale_group)
 
-    # ---- stage 4: FC1 input gradient -> source ranks, then gather-sum -------------------
+    # ---- stage 4: FC1 input gradient -> source ranks ------------------------------------
     if m > 0:
         desc = L.make_desc(ctx, grad_fc1_output, m, 2 * ffn, fc1_combined, k_dim=1, n_dim=2,
                            n_out=hidden, k_extent=2 * ffn, **tiles)
         L.grouped_gemm_scatter(ctx, desc, "combine_mem", hidden, plan=plan, name="fc1_dgrad_combine")
-    # Peers may read what this rank stored as soon as it has signalled; the FC1 weight
-    # gradient touches no peer-written memory, so it runs between the signal and the wait
-    # and absorbs the ranks' skew.
-    ctx.rank_signal()
 
-    # ---- stage 5: FC1 weight gradient -------------------------------------------------
+    # ---- stage 5: FC1 weight gradient (reads the forward's received rows, which a peer may
+    #      overwrite once it has seen this rank's signal) ---------------------------------
+    grad_ws = saved.get("_grad_workspace")
     if m > 0:
         grad_fc1 = (grad_ws["grad_fc1"] if grad_ws is not None
                     else torch.empty(epr, 2 * ffn, hidden, dtype=dtype, device=device))
@@ -168,6 +160,25 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
                         name="fc1_wgrad")
     else:
         grad_fc1 = torch.zeros(epr, 2 * ffn, hidden, dtype=dtype, device=device)
+
+    # Peers may read what this rank stored as soon as it has signalled.
+    ctx.rank_signal()
+
+    # ---- stage 3: FC2 weight gradient, between the two halves of the barrier ------------
+    if recompute:
+        # weighted activation rows from the saved FC1 rows and the saved bf16 routing weights
+        act = torch.empty(max(m, 1), ffn, dtype=dtype, device=device)[:m]
+        if m > 0:
+            L.swiglu_recompute(fc1_output, saved["recv_weights_sorted"], ffn, plan.metadata_stats,
+                               m, act, *act_args, fc1_scale=fc1_scale, scale_group=scale_group)
+    else:
+        act = saved["swiglu_out_weighted"]
+    if m > 0:
+        grad_fc2 = (grad_ws["grad_fc2"] if grad_ws is not None
+                    else torch.empty(epr, hidden, ffn, dtype=dtype, device=device))
+        L.grouped_wgrad(ctx, recv_dy, act, m, group_offs, epr, grad_fc2, name="fc2_wgrad")
+    else:
+        grad_fc2 = torch.zeros(epr, hidden, ffn, dtype=dtype, device=device)
 
     ctx.rank_wait()
     grad_hidden = torch.empty(tokens, hidden, dtype=dtype, device=device)

@@ -16,6 +16,7 @@ synchronisation unless ``return_saved`` or a reduced receive capacity asks for o
 
 from __future__ import annotations
 
+import os
 import types
 import weakref
 from dataclasses import dataclass
@@ -31,7 +32,7 @@ from ..runtime.routing import (
     check_receive_capacity,
     launch_routing_metadata,
 )
-from ..runtime.workspace import create_moe_forward_context
+from ..runtime.workspace import carve_plan, create_moe_forward_context
 from . import _launch as L
 
 
@@ -46,19 +47,15 @@ class DispatchFC1Result:
     send_route_indices: torch.Tensor
 
 
-_PLAN_FIELDS = (
-    "send_token_indices", "send_route_indices", "send_bucket", "route_to_send",
-    "metadata_send_bucket_starts", "metadata_send_bucket_dst_starts", "metadata_local_stats",
-    "metadata_stats", "metadata_recv_expert_offs", "metadata_recv_counts_re",
-    "metadata_recv_per_expert", "mtile_group", "mtile_row0", "num_mtiles", "row_src_rank",
-    "row_src_pos", "metadata_count_row", "disp_order_prefix", "mtile2_group", "mtile2_row0",
-    "num_mtiles2",
-)
+def snapshot_plan(context, copy: bool = True) -> types.SimpleNamespace:
+    """The routing tables of the last metadata launch as one object.
 
-
-def snapshot_plan(context) -> types.SimpleNamespace:
-    """Clone the routing tables of the last metadata launch (a few MB of int32)."""
-    return types.SimpleNamespace(**{name: getattr(context, name).clone() for name in _PLAN_FIELDS})
+    All tables are slices of one int32 arena (a few MB), so a snapshot is a single device
+    copy; ``copy=False`` returns views of the live tables (valid until the next metadata
+    launch on the operator).
+    """
+    arena = context.plan_arena.clone() if copy else context.plan_arena
+    return types.SimpleNamespace(**carve_plan(arena, context.plan_layout))
 
 
 class FusedMoEForward(torch.nn.Module):
@@ -151,6 +148,7 @@ class FusedMoEForward(torch.nn.Module):
         self._act_buf = None
         self._fc1_buf = None
         self._routing_weights_keepalive = None
+        self._fwd_timing_last = None
         # When True, the backward writes the expert-weight gradients into buffers that are
         # allocated once and handed out again every step (the caller must consume or
         # accumulate them before the next backward), like the fixed-address saved-activation
@@ -257,8 +255,20 @@ class FusedMoEForward(torch.nn.Module):
         self.context.finalize()
 
     def read_last_forward_phase_timing(self):
-        """Per-phase device stamps are not recorded by this build."""
-        return None
+        """Device time of each phase of the last forward, recorded under ``MOE_FWD_TIMING=1``
+        (the reference's switch, ops/forward.py:1555-1570; there the products are SYS_CNT
+        ticks per Ascend core, here CUDA-event times on the caller's stream).
+
+        Returns ``{"phase_ms": {phase: ms}, "total_ms": ms}`` with the phases
+        ``routing_metadata``, ``dispatch_fc1_activation`` (dispatch, FC1 and the weighted
+        activation are one launch, or a chain without gaps), ``fc2_combine``, ``rank_barrier``
+        and ``topk_reduce``.  Waits for the last stamp.  Raises ``RuntimeError`` when no forward
+        has run with the switch set.
+        """
+        if self._fwd_timing_last is None:
+            raise RuntimeError("no forward has run on this operator with MOE_FWD_TIMING=1")
+        phases = self._fwd_timing_last.phase_ms()
+        return {"phase_ms": phases, "total_ms": sum(phases.values())}
 
     # ===================== validation =====================
     def _validate_topk_indices(self, selected_experts: torch.Tensor):
@@ -398,7 +408,8 @@ class FusedMoEForward(torch.nn.Module):
         desc = L.make_desc(ctx, recv, ctx.max_received_routes, self.hidden_size, fc1_weight,
                            k_dim=1, n_dim=2, n_out=n_out, k_extent=self.hidden_size)
         if L.fused_dispatch_enabled(ctx):
-            disp = L.make_dispatch_desc(ctx, hidden_states, routing_weights)
+            # a plan may be dispatched more than once: the delivery counters start at zero
+            disp = L.make_dispatch_desc(ctx, hidden_states, routing_weights, reset_counters=True)
         else:
             disp = None
             L.dispatch_rows(ctx, hidden_states, routing_weights, selected_experts.numel())
@@ -475,8 +486,11 @@ class FusedMoEForward(torch.nn.Module):
         two_step_fc1 = L.gemm_tile_mode(ctx) == L.TILE_SKINNY
         self._ensure_activation_buffers(ffn_size, need_fc1=return_saved or two_step_fc1)
         out = torch.empty(tokens, hidden, dtype=self.activation_dtype, device=hidden_states.device)
+        stamps = _PhaseStamps() if os.environ.get("MOE_FWD_TIMING") == "1" else None
 
         launch_routing_metadata(ctx, selected_experts)
+        if stamps:
+            stamps.mark("routing_metadata")
         self._routing_generation += 1
         self._routing_weights_keepalive = routing_weights
         # Dispatch is fused into the FC1 launch: extra warps push the rows while the GEMM
@@ -490,22 +504,27 @@ class FusedMoEForward(torch.nn.Module):
             disp = None
             L.dispatch_rows(ctx, hidden_states, routing_weights, num_routes)
             ctx.rank_barrier()
+        # The received routing weights live in symmetric memory that the next forward's
+        # dispatch rewrites; FC1 leaves the bf16 copy the backward reads in a private buffer.
         L.fc1_swiglu(ctx, fc1_desc, self._act_buf,
                      self._fc1_buf if (return_saved or two_step_fc1) else None,
                      ctx.routing_weight_mem, self.activation, self.situ_beta,
-                     self.situ_linear_beta, self.clamp_limit, dispatch=disp)
-        saved = None
-        if return_saved:
-            # The receive buffer is rewritten by the next dispatch (forward or backward), so
-            # the rows the FC1 weight gradient needs are copied out here, before the barrier
-            # that lets peers write again (reference: ops/forward.py:2074-2080).
-            recv_copy = recv.clone()
-            weights_copy = ctx.routing_weight_mem.to(torch.bfloat16)
+                     self.situ_linear_beta, self.clamp_limit, dispatch=disp,
+                     weight_bf16_out=ctx.recv_weights_bf16 if return_saved else None)
+        if stamps:
+            stamps.mark("dispatch_fc1_activation")
         fc2_desc = L.make_desc(ctx, self._act_buf, cap, ffn_size, down_weight, k_dim=2, n_dim=1,
                                n_out=hidden, k_extent=ffn_size)
         L.grouped_gemm_scatter(ctx, fc2_desc, "combine_mem", hidden, name="fc2_combine")
+        if stamps:
+            stamps.mark("fc2_combine")
         ctx.rank_barrier()
+        if stamps:
+            stamps.mark("rank_barrier")
         L.topk_reduce(ctx.combine_mem, ctx.route_to_send, tokens, self.top_k, hidden, out)
+        if stamps:
+            stamps.mark("topk_reduce")
+            self._fwd_timing_last = stamps
         if self.host_sync_free:
             self._defer_capacity_check()
         else:
@@ -513,7 +532,6 @@ class FusedMoEForward(torch.nn.Module):
         if not return_saved:
             return out
 
-        plan = snapshot_plan(ctx)
         if self.host_sync_free:
             num_received_routes = num_sent_routes = None
             m = cap
@@ -523,10 +541,24 @@ class FusedMoEForward(torch.nn.Module):
             num_sent_routes = int(ctx.metadata_local_stats[0].item())
             m = num_received_routes
             sent = num_sent_routes
+            if num_sent_routes != num_routes:
+                # reference: ops/_single_saved_adapter.py:116-121
+                raise ValueError(
+                    "droless routing required for the single-kernel backward "
+                    f"contract: {num_sent_routes} routes kept of {num_routes} — raise "
+                    "receive_capacity_factor to >= world_size")
+        # With saved_views the saved tensors are views of this operator's buffers, valid until
+        # its next forward: the backward's dy rows land in a second receive region, so the
+        # forward's received rows stay in place.  Otherwise every saved tensor is a copy and a
+        # later forward on the same operator does not disturb it (reference: clone-out at
+        # ops/forward.py:2074-2080 and the full-snapshot marker of the saved adapter).
+        views = self.saved_views
+        keep = (lambda t: t) if views else (lambda t: t.clone())
+        plan = snapshot_plan(ctx, copy=not views)
         save_fmt = self.config.save_fc1_dtype
         fc1_scale = None
         if save_fmt == "bf16":
-            fc1_output = self._fc1_buf[:m] if self.saved_views else self._fc1_buf[:m].clone()
+            fc1_output = keep(self._fc1_buf[:m])
         else:
             # Saved-format pass (reference: quantise leg of the FC1 epilogue,
             # kernels/fused_forward.py:877-949): the raw bf16 rows stay in the operator's
@@ -543,7 +575,7 @@ class FusedMoEForward(torch.nn.Module):
             # minimal contract of the reference's single-launch forward
             # (ops/forward.py:1813-1873)
             "fc1_output": fc1_output,
-            "recv_weights_sorted": weights_copy[:m],
+            "recv_weights_sorted": keep(ctx.recv_weights_bf16[:m]),
             "hidden_states": hidden_states,
             "selected_experts": selected_experts,
             "routing_weights": routing_weights,
@@ -552,16 +584,16 @@ class FusedMoEForward(torch.nn.Module):
             "send_token_indices": plan.send_token_indices[:sent],
             "send_route_indices": plan.send_route_indices[:sent],
             "total_send": num_sent_routes,
-            "total_recv": m,
-            "M": m,
+            "total_recv": num_received_routes,
+            "M": num_received_routes,
             "_routing_generation": self._routing_generation,
             "_owner_token": id(self._routing_owner_token),
-            "_single_kernel_snapshot": True,
+            "_single_kernel_snapshot": not views,
+            "_saved_views": views,
             # activation section and scalars of the full backward contract
             # (ops/_torch_forward.py:294-320)
-            "recv_hidden_sorted": recv_copy[:m],
-            "swiglu_out_weighted": (self._act_buf[:m] if self.saved_views
-                                    else self._act_buf[:m].clone()),
+            "recv_hidden_sorted": keep(recv[:m]),
+            "swiglu_out_weighted": keep(self._act_buf[:m]),
             "gate": fc1_output[:, :ffn_size],
             "up": fc1_output[:, ffn_size:],
             "expert_counts": plan.metadata_recv_per_expert,
@@ -580,12 +612,78 @@ class FusedMoEForward(torch.nn.Module):
             "output": out, "dy": None,
             "_plan": plan,
         }
+        saved.update(self._saved_index_section(plan, m, sent, num_received_routes is not None))
         if fc1_scale is not None:
             saved["fc1_output_scale"] = fc1_scale
             saved["fc1_scale_group_size"] = self._fc1_scale_group(ffn_size)
         if self.persistent_weight_grads:
             saved["_grad_workspace"] = self._get_grad_workspace(ffn_size)
         return out, saved
+
+    def _saved_index_section(self, plan, m: int, sent: int, host_values: bool) -> dict:
+        """Index keys of the saved contract after the reference's enrichment
+        (ops/_single_saved_adapter.py:247-340), all from the routing tables of this forward.
+
+        ``sort_idxs`` is the forward's own send order and ``inv_sort`` its inverse
+        (= ``route_to_send`` for dropless routes); ``local_sort_idxs`` / ``inv_local`` map
+        between the receive order (expert-major, then source) and the source-major arrival
+        order of an all-to-all (written by the metadata kernel).  The per-rank split lists and
+        the 64-row tile tables of the reference's grouped GEMMs need host values, so they are
+        ``None`` in ``host_sync_free`` mode (``host_values`` False).
+        """
+        out = {
+            "forward_send_route": plan.send_route_indices[:sent],
+            "sort_idxs": plan.send_route_indices[:sent],
+            "inv_sort": plan.route_to_send[:sent],
+            "local_sort_idxs": plan.row_arrival[:m],
+            "inv_local": plan.arrival_row[:m],
+        }
+        keys = ("splits_send_list", "splits_recv_list", "num_tiles_total", "meta_expert_ids",
+                "meta_split_cum", "meta_tile_num", "meta_tile_num_cum")
+        if not host_values:
+            out.update({k: None for k in keys})
+            return out
+        counts = plan.metadata_recv_counts_re.cpu().to(torch.int64)          # [W, EPR]
+        send_row = plan.metadata_count_row[:self.num_experts].cpu().to(torch.int64)
+        out["splits_send_list"] = send_row.view(self.world_size, -1).sum(1).tolist()
+        out["splits_recv_list"] = counts.sum(1).tolist()
+        per_expert = counts.sum(0)
+        tile_rows = 64                       # BLOCK_SIZE_M of the reference's metadata builder
+        tiles = (per_expert + tile_rows - 1) // tile_rows
+        row_starts = per_expert.cumsum(0) - per_expert
+        tile_starts = tiles.cumsum(0) - tiles
+        total = int(tiles.sum())
+        dev = plan.metadata_recv_counts_re.device
+        i32 = lambda t: t.to(torch.int32).to(dev)
+        out["num_tiles_total"] = i32(torch.tensor([total]))
+        out["meta_expert_ids"] = i32(torch.repeat_interleave(torch.arange(tiles.numel()), tiles))
+        out["meta_split_cum"] = i32(torch.repeat_interleave(row_starts, tiles))
+        out["meta_tile_num_cum"] = i32(torch.repeat_interleave(tile_starts, tiles))
+        out["meta_tile_num"] = i32(torch.arange(total) - torch.repeat_interleave(tile_starts, tiles))
+        return out
+
+
+class _PhaseStamps:
+    """CUDA events at the phase boundaries of one forward (``MOE_FWD_TIMING=1``)."""
+
+    def __init__(self):
+        self.names = []
+        self.events = [self._now()]
+
+    @staticmethod
+    def _now():
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        return ev
+
+    def mark(self, name: str) -> None:
+        self.names.append(name)
+        self.events.append(self._now())
+
+    def phase_ms(self) -> dict:
+        self.events[-1].synchronize()
+        return {n: self.events[i].elapsed_time(self.events[i + 1])
+                for i, n in enumerate(self.names)}
 
 
 def pack_gate_up_weights(gate_weight_local: torch.Tensor,

@@ -88,6 +88,7 @@ def launch_routing_metadata(context: MoEForwardContext, selected_experts: torch.
         ctx.mtile2_group.data_ptr(), ctx.mtile2_row0.data_ptr(), ctx.num_mtiles2.data_ptr(),
         ctx.row_src_rank.data_ptr(), ctx.row_src_pos.data_ptr(),
         ctx.disp_order_prefix.data_ptr(), ctx.disp_bucket_done.data_ptr(),
+        ctx.row_arrival.data_ptr(), ctx.arrival_row.data_ptr(),
         ctx.status.data_ptr(), stream),
         "mm_route_finalize")
     timer.__exit__()

@@ -19,6 +19,22 @@ import torch.distributed as dist
 from .. import _native as N
 
 
+# Routing tables of one metadata launch that a saved dict carries to the backward.
+PLAN_FIELDS = (
+    "send_token_indices", "send_route_indices", "send_bucket", "route_to_send",
+    "metadata_send_bucket_starts", "metadata_send_bucket_dst_starts", "metadata_local_stats",
+    "metadata_stats", "metadata_recv_expert_offs", "metadata_recv_counts_re",
+    "metadata_recv_per_expert", "mtile_group", "mtile_row0", "num_mtiles", "row_src_rank",
+    "row_src_pos", "metadata_count_row", "disp_order_prefix", "mtile2_group", "mtile2_row0",
+    "num_mtiles2", "row_arrival", "arrival_row",
+)
+
+
+def carve_plan(arena: torch.Tensor, layout) -> dict:
+    """Views of the plan tables inside an int32 arena laid out by ``layout``."""
+    return {name: arena[off:off + numel].view(shape) for name, off, numel, shape in layout}
+
+
 def next_power_of_2(n: int) -> int:
     return 1 if n <= 1 else 1 << (n - 1).bit_length()
 
@@ -145,6 +161,12 @@ class MoEForwardContext:
     row_src_pos: Optional[torch.Tensor] = None
     status: Optional[torch.Tensor] = None
     dispatch_flags: Optional[torch.Tensor] = None
+    peer_grad_mem: Optional[torch.Tensor] = None
+    recv_weights_bf16: Optional[torch.Tensor] = None
+    row_arrival: Optional[torch.Tensor] = None
+    arrival_row: Optional[torch.Tensor] = None
+    plan_arena: Optional[torch.Tensor] = None
+    plan_layout: Optional[list] = None
     redispatch_mem: Optional[torch.Tensor] = None
     disp_order_prefix: Optional[torch.Tensor] = None
     disp_bucket_done: Optional[torch.Tensor] = None
@@ -301,6 +323,9 @@ def create_moe_forward_context(
     regions = {
         "flags": 4096,
         "peer_mem": max_received_routes * hidden_size * 2,
+        # receive buffer of the backward's dy rows: the forward's rows stay readable in
+        # peer_mem until the next forward, so the FC1 weight gradient needs no copy of them
+        "peer_grad_mem": max_received_routes * hidden_size * 2,
         "routing_weight_mem": max_received_routes * 4,
         "combine_mem": num_routes * hidden_size * 2,
         "combine_gate_mem": num_routes * 2,
@@ -317,6 +342,7 @@ def create_moe_forward_context(
     ctx.combine_mem = ctx.symm.local("combine_mem", torch.bfloat16).view(num_routes, hidden_size)
     ctx.combine_gate_mem = ctx.symm.local("combine_gate_mem", torch.bfloat16)
     ctx.dispatch_flags = ctx.symm.local("dispatch_flags", torch.int32)
+    ctx.peer_grad_mem = ctx.symm.local("peer_grad_mem", torch.bfloat16)
     ctx.redispatch_mem = (ctx.symm.local("redispatch_mem", torch.bfloat16)
                           if "redispatch_mem" in regions else None)
 
@@ -325,37 +351,48 @@ def create_moe_forward_context(
     ctx.metadata_num_bins = bins
     i32 = dict(dtype=torch.int32, device=device)
     ctx.metadata_counts_mem = torch.zeros(world_size * bins, **i32)
-    ctx.metadata_count_row = torch.zeros(bins, **i32)
-    ctx.metadata_send_bucket_starts = torch.empty(num_buckets, **i32)
-    ctx.metadata_send_bucket_dst_starts = torch.empty(num_buckets, **i32)
-    ctx.metadata_recv_counts_re = torch.empty((world_size, experts_per_rank), **i32)
     ctx.metadata_recv_seg_starts = torch.empty((experts_per_rank, world_size + 1), **i32)
-    ctx.metadata_recv_per_expert = torch.empty(experts_per_rank, **i32)
-    ctx.metadata_recv_expert_offs = torch.zeros(experts_per_rank + 1, **i32)
-    ctx.metadata_stats = torch.zeros(2 + world_size, **i32)
     ctx.metadata_pull_dst_start = torch.empty(experts_per_rank * world_size, **i32)
-    ctx.metadata_local_stats = torch.zeros(2, **i32)
     ctx.row_token_indices = torch.arange(num_routes, **i32) // top_k
     ctx.row_route_indices = torch.arange(num_routes, **i32)
-    ctx.send_token_indices = torch.zeros(num_routes, **i32)
-    ctx.send_route_indices = torch.zeros(num_routes, **i32)
-    ctx.send_bucket = torch.zeros(num_routes, **i32)
-    ctx.route_to_send = torch.full((num_routes,), -1, **i32)
     scratch_bytes = N.lib().mm_route_scratch_bytes(num_routes, bins)
     ctx.route_scratch = torch.empty(max(scratch_bytes, 16), dtype=torch.uint8, device=device)
     max_tiles = max_received_routes // 128 + experts_per_rank + 1
-    ctx.mtile_group = torch.zeros(max_tiles, **i32)
-    ctx.mtile_row0 = torch.zeros(max_tiles, **i32)
-    ctx.num_mtiles = torch.zeros(1, **i32)
     max_tiles2 = max_received_routes // 256 + experts_per_rank + 1
-    ctx.mtile2_group = torch.zeros(max_tiles2, **i32)
-    ctx.mtile2_row0 = torch.zeros(max_tiles2, **i32)
-    ctx.num_mtiles2 = torch.zeros(1, **i32)
-    ctx.row_src_rank = torch.zeros(max(max_received_routes, 1), **i32)
-    ctx.row_src_pos = torch.zeros(max(max_received_routes, 1), **i32)
+    cap_rows = max(max_received_routes, 1)
+    # Every table a saved dict has to keep (PLAN_FIELDS) is a slice of one int32 arena, so a
+    # snapshot of the plan is a single device copy.
+    shapes = {
+        "send_token_indices": (num_routes,), "send_route_indices": (num_routes,),
+        "send_bucket": (num_routes,), "route_to_send": (num_routes,),
+        "metadata_send_bucket_starts": (num_buckets,),
+        "metadata_send_bucket_dst_starts": (num_buckets,),
+        "metadata_local_stats": (2,), "metadata_stats": (2 + world_size,),
+        "metadata_recv_expert_offs": (experts_per_rank + 1,),
+        "metadata_recv_counts_re": (world_size, experts_per_rank),
+        "metadata_recv_per_expert": (experts_per_rank,),
+        "mtile_group": (max_tiles,), "mtile_row0": (max_tiles,), "num_mtiles": (1,),
+        "row_src_rank": (cap_rows,), "row_src_pos": (cap_rows,),
+        "metadata_count_row": (bins,), "disp_order_prefix": (num_buckets + 1,),
+        "mtile2_group": (max_tiles2,), "mtile2_row0": (max_tiles2,), "num_mtiles2": (1,),
+        "row_arrival": (cap_rows,), "arrival_row": (cap_rows,),
+    }
+    assert tuple(shapes) == PLAN_FIELDS
+    layout, off = [], 0
+    for name in PLAN_FIELDS:
+        numel = 1
+        for d in shapes[name]:
+            numel *= d
+        layout.append((name, off, numel, shapes[name]))
+        off += (numel + 3) // 4 * 4            # 16-byte aligned tables
+    ctx.plan_arena = torch.zeros(max(off, 4), **i32)
+    ctx.plan_layout = layout
+    for name, view in carve_plan(ctx.plan_arena, layout).items():
+        setattr(ctx, name, view)
+    ctx.route_to_send.fill_(-1)
     ctx.status = torch.zeros(8, **i32)
-    ctx.disp_order_prefix = torch.zeros(num_buckets + 1, **i32)
     ctx.disp_bucket_done = torch.zeros(num_buckets, **i32)
+    ctx.recv_weights_bf16 = torch.zeros(cap_rows, dtype=torch.bfloat16, device=device)
     register_context(ctx)
     return ctx
 

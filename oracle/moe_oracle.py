@@ -22,6 +22,10 @@ Reference functions restated here (paths inside the reference project):
 * five-stage backward        tests/_moe_baselines.py:96-226    (moe_backward_torch)
 * top-k reduce with drops    tests/function/test_single_kernel_reduce.py:41-77
 * tolerances                 tests/_numeric.py:24-68
+* saved-contract tables      src/mega_moe/ops/_torch_forward.py:103-128 (prepare_moe_metadata),
+                             src/mega_moe/ops/_moonep_torch_forward.py:192-223
+                             (_arrival_to_slot_permutation),
+                             src/mega_moe/ops/_single_saved_adapter.py:247-340 (enrichment)
 
 Parity pin: ``tests/golden/`` holds outputs of the reference's own functions, produced by
 ``tests/golden/make_golden.py`` by importing the reference in a gloo process group;
@@ -142,6 +146,72 @@ def routing_metadata(selected: list[np.ndarray], num_experts: int):
         )
         out.append({k: (v.astype(np.int32) if isinstance(v, np.ndarray) and v.dtype == np.int64
                         else v) for k, v in d.items()})
+    return out
+
+
+SAVED_TILE_ROWS = 64   # BLOCK_SIZE_M of ops/_torch_forward.py:28
+
+
+def tile_metadata(expert_counts):
+    """prepare_moe_metadata (ops/_torch_forward.py:103-128): per 64-row tile of the grouped
+    GEMMs its expert, the expert's first row, the tile's index inside the expert and the
+    expert's first tile; plus the row prefix and the tile total.  int32 numpy arrays."""
+    counts = np.asarray(expert_counts).astype(np.int64)
+    tiles = (counts + SAVED_TILE_ROWS - 1) // SAVED_TILE_ROWS
+    token_starts = np.cumsum(counts) - counts
+    tile_starts = np.cumsum(tiles) - tiles
+    i32 = lambda a: np.asarray(a).astype(np.int32)
+    total = int(tiles.sum())
+    return dict(
+        split_size_cum_per_expert=i32(np.r_[0, np.cumsum(counts)]),
+        meta_expert_ids=i32(np.repeat(np.arange(counts.shape[0]), tiles)),
+        meta_split_cum=i32(np.repeat(token_starts, tiles)),
+        meta_tile_num=i32(np.arange(total) - np.repeat(tile_starts, tiles)),
+        meta_tile_num_cum=i32(np.repeat(tile_starts, tiles)),
+        num_tiles_total=i32([total]),
+    )
+
+
+def arrival_to_slot_permutation(recv_counts_re, slot_starts):
+    """_arrival_to_slot_permutation (ops/_moonep_torch_forward.py:192-223): entry p of the
+    result is the arrival index (source-major, inside a source expert-major) of the row at
+    position p of the receive order (expert-major, inside an expert source-major)."""
+    counts = np.asarray(recv_counts_re).astype(np.int64)            # [W, EPR]
+    source_totals = counts.sum(1)
+    source_starts = np.cumsum(source_totals) - source_totals
+    within_source = np.cumsum(counts, axis=1) - counts
+    within_slot = np.cumsum(counts, axis=0) - counts
+    arrival_start = source_starts[:, None] + within_source
+    sorted_start = np.asarray(slot_starts).astype(np.int64)[None, :] + within_slot
+    perm = np.zeros(int(counts.sum()), dtype=np.int64)
+    for s in range(counts.shape[0]):
+        for e in range(counts.shape[1]):
+            c = counts[s, e]
+            perm[sorted_start[s, e]:sorted_start[s, e] + c] = arrival_start[s, e] + np.arange(c)
+    return perm
+
+
+def saved_contract_tables(meta_r: dict, selected_r, world: int):
+    """The index section the fused forward's saved dict carries after enrichment
+    (ops/_single_saved_adapter.py:247-340) for one rank, from its routing tables: the
+    forward's own send order as ``sort_idxs``, its inverse, the arrival permutation pair,
+    the per-rank split lists and the 64-row tile tables.  Dropless routes only."""
+    flat = np.asarray(selected_r).reshape(-1).astype(np.int64)
+    send_route = meta_r["send_route_indices"].astype(np.int64)
+    if send_route.shape[0] != flat.shape[0]:
+        raise ValueError("droless routing required for the saved contract")
+    counts_re = meta_r["recv_counts_re"].astype(np.int64)
+    epr = counts_re.shape[1]
+    local = arrival_to_slot_permutation(counts_re, meta_r["recv_expert_offs"][:-1])
+    out = dict(
+        sort_idxs=send_route, inv_sort=np.argsort(send_route, kind="stable"),
+        forward_send_route=send_route.astype(np.int32),
+        local_sort_idxs=local, inv_local=np.argsort(local, kind="stable"),
+        splits_send_list=np.bincount(flat // epr, minlength=world).tolist(),
+        splits_recv_list=counts_re.sum(1).tolist(),
+        expert_counts=counts_re.sum(0).astype(np.int32),
+    )
+    out.update(tile_metadata(counts_re.sum(0)))
     return out
 
 
@@ -454,9 +524,13 @@ def router_topk(logits: torch.Tensor, top_k: int):
 
 # ---------------------------------------------------------------------------------------
 # saved-activation formats and the recompute backward.  The reference implements these only
-# in its Triton-Ascend kernels, which cannot run here, so this part restates the kernel source
-# and is NOT pinned by reference outputs ("parity unpinned" for these four functions); the
-# bounds the reference's own tests place on them are checked in tests/test_oracle_formats.py.
+# in its Triton-Ascend kernels, which cannot be launched here; their arithmetic is plain ``tl``
+# tensor code, so tests/golden/make_golden_saved.py executes the reference's own source text
+# (the FC1 save leg, kernels/fused_forward.py:891-949, and _recompute_act_rows,
+# kernels/mega_bwd.py:1414-1465) against a torch-backed stand-in for ``tl`` and stores the
+# results in tests/golden/saved_formats.npz; tests/test_oracle_formats.py requires the four
+# functions below to reproduce them bit-exactly (formulas, operation order, rounding points
+# and table layout are pinned; the Ascend vector unit's own sigmoid/tanh are not).
 # ---------------------------------------------------------------------------------------
 FP8_E4M3_MAX = 448.0
 

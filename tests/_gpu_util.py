@@ -73,7 +73,7 @@ def run_grouped_gemm(a, weight, k_dim, n_dim, counts):
 
 
 def run_fc1_swiglu(a, gate_up, row_weight, counts, activation="swiglu", beta=1.0,
-                   linear_beta=None, clamp=7.0, want_raw=True):
+                   linear_beta=None, clamp=7.0, want_raw=True, weight_bf16=None):
     status = new_status(a.device)
     ffn = gate_up.shape[2] // 2
     d, keep = gemm_desc(a, gate_up, 1, 2, ffn, gate_up.shape[1], counts, status)
@@ -82,7 +82,7 @@ def run_fc1_swiglu(a, gate_up, row_weight, counts, activation="swiglu", beta=1.0
                      device=a.device) if want_raw else None
     N.check(N.lib().mm_fc1_swiglu(
         C.byref(d), None, act.data_ptr(), act.stride(0), N.ptr(raw), raw.stride(0) if want_raw else 0,
-        row_weight.data_ptr(), N.ACT_IDS[activation], float(beta),
+        row_weight.data_ptr(), N.ptr(weight_bf16), N.ACT_IDS[activation], float(beta),
         float(linear_beta) if linear_beta is not None else 0.0, float(clamp), N.stream_ptr()),
         "mm_fc1_swiglu")
     torch.cuda.synchronize()

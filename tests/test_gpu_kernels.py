@@ -37,7 +37,10 @@ def _route_local(sel_np, num_experts, top_k):
     return {k: v.cpu().numpy() for k, v in outs.items()}, bins
 
 
-def _finalize(cube_np, rank, world, epr, bins, capacity):
+def _finalize(cube_np, rank, world, epr, bins, capacity, tile_tail=0):
+    """Run mm_route_finalize on fresh tables.  ``tile_tail`` extra entries are appended to the
+    four row-tile tables (the documented size is capacity / tile rows + epr) so a caller can
+    check that nothing is written past the documented end."""
     from mega_moe import _native as N
     lib = N.lib()
     i32 = dict(dtype=torch.int32, device=DEV)
@@ -51,22 +54,24 @@ def _finalize(cube_np, rank, world, epr, bins, capacity):
              recv_seg_starts=torch.full((epr * (world + 1),), -7, **i32),
              pull_dst_start=torch.full((epr * world,), -7, **i32),
              stats=torch.full((2 + world,), -7, **i32),
-             mtile_group=torch.full((capacity // 128 + epr + 1,), -7, **i32),
-             mtile_row0=torch.full((capacity // 128 + epr + 1,), -7, **i32),
+             mtile_group=torch.full((capacity // 128 + epr + tile_tail,), -7, **i32),
+             mtile_row0=torch.full((capacity // 128 + epr + tile_tail,), -7, **i32),
              num_mtiles=torch.full((1,), -7, **i32),
-             mtile2_group=torch.full((capacity // 256 + epr + 1,), -7, **i32),
-             mtile2_row0=torch.full((capacity // 256 + epr + 1,), -7, **i32),
+             mtile2_group=torch.full((capacity // 256 + epr + tile_tail,), -7, **i32),
+             mtile2_row0=torch.full((capacity // 256 + epr + tile_tail,), -7, **i32),
              num_mtiles2=torch.full((1,), -7, **i32),
              row_src_rank=torch.full((max(capacity, 1),), -7, **i32),
              row_src_pos=torch.full((max(capacity, 1),), -7, **i32),
              order_prefix=torch.full((nb + 1,), -7, **i32),
-             bucket_done=torch.full((nb,), -7, **i32))
+             bucket_done=torch.full((nb,), -7, **i32),
+             row_arrival=torch.full((max(capacity, 1),), -7, **i32),
+             arrival_row=torch.full((max(capacity, 1),), -7, **i32))
     status = torch.zeros(8, **i32)
     order = ["send_bucket_starts", "send_bucket_dst_starts", "recv_counts_re", "recv_per_expert",
              "recv_expert_offs", "recv_seg_starts", "pull_dst_start", "stats", "mtile_group",
              "mtile_row0", "num_mtiles", "mtile2_group", "mtile2_row0", "num_mtiles2",
              "row_src_rank", "row_src_pos", "order_prefix",
-             "bucket_done"]
+             "bucket_done", "row_arrival", "arrival_row"]
     N.check(lib.mm_route_finalize(cube.data_ptr(), rank, world, epr, bins, capacity,
                                   *[t[k].data_ptr() for k in order], status.data_ptr(),
                                   N.stream_ptr()), "mm_route_finalize")
@@ -157,6 +162,31 @@ def test_routing_capacity_overflow_sets_status():
     assert status[0] == 2 and status[3] == 100 and status[4] == 512
     assert out["num_mtiles"][0] == 0 and out["num_mtiles2"][0] == 0
     assert out["stats"][1] == meta[0]["stats"][1]
+
+
+@pytest.mark.parametrize("world,epr,rows_per_bucket,capacity", [
+    (1, 8, 4000, 100),        # 32 000 rows into room for 100: 250 tiles against 8 entries
+    (8, 112, 300, 20000),     # headline bucket count, 2.1x the capacity of every rank
+    (4, 2, 70000, 128),
+])
+def test_routing_capacity_overflow_writes_no_tile_entry(world, epr, rows_per_bucket, capacity):
+    """A receive total far above capacity_rows must leave the row-tile tables untouched: they are
+    sized for capacity_rows, and entries past them would land in someone else's memory."""
+    from mega_moe.runtime.workspace import next_power_of_2
+    nb = world * epr
+    bins = next_power_of_2(nb)
+    cube = np.zeros((world, bins), dtype=np.int32)
+    cube[:, :nb] = rows_per_bucket // world
+    tail = 8192
+    for rank in range(world):
+        out, status = _finalize(cube, rank, world, epr, bins, capacity, tile_tail=tail)
+        assert status[0] == 2 and status[3] == capacity
+        assert status[4] == (rows_per_bucket // world) * world * epr
+        assert out["num_mtiles"][0] == 0 and out["num_mtiles2"][0] == 0
+        for key in ("mtile_group", "mtile_row0", "mtile2_group", "mtile2_row0"):
+            assert (out[key] == -7).all(), key
+        # the per-row tables are guarded by capacity_rows as before
+        assert out["row_src_rank"].shape[0] == capacity
 
 
 @pytest.fixture(params=[1, 0, 2], ids=["pair", "single", "skinny"])

@@ -39,6 +39,31 @@ def test_router_ties_go_to_the_lower_expert_and_strides_are_honoured():
     torch.testing.assert_close(w.cpu(), want_w, rtol=1e-5, atol=1e-7)
 
 
+def test_router_masked_and_nan_logits_follow_a_stable_descending_sort():
+    """Rows with fewer than k finite logits (masked experts) still select k distinct real experts,
+    -inf ties in expert order; a NaN logit ranks first, as in torch.sort / torch.topk."""
+    import mega_moe
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(6, 40, generator=g)
+    logits[0, 3:] = float("-inf")              # 3 finite logits, k = 6
+    logits[1, :] = float("-inf")               # nothing finite
+    logits[2, 17] = float("nan")
+    logits[3, 5] = float("inf")
+    logits[3, 9] = float("-inf")
+    logits[4, 0] = 0.0
+    logits[4, 1] = -0.0                        # equal: expert 0 before expert 1
+    logits[4, 2:] = -1.0
+    want_sel, want_w = O.router_topk(logits, 6)
+    sel, w = mega_moe.router_topk(logits.to(DEV), 6)
+    assert torch.equal(sel.cpu(), want_sel)
+    assert sel[0].tolist()[3:] == [3, 4, 5] and sel[1].tolist() == [0, 1, 2, 3, 4, 5]
+    assert int(sel[2, 0]) == 17 and sel[4].tolist()[:2] == [0, 1]
+    assert int(sel.min()) >= 0 and int(sel.max()) < 40
+    torch.testing.assert_close(w.cpu(), want_w, rtol=1e-5, atol=1e-7, equal_nan=True)
+    assert torch.isnan(w[1]).all() and torch.isnan(w[2]).all()      # softmax arithmetic
+    torch.testing.assert_close(w[0, :3].sum().cpu(), torch.tensor(1.0), rtol=1e-5, atol=1e-6)
+
+
 def test_router_validation():
     import mega_moe
     x = torch.randn(4, 16, device=DEV)

@@ -57,3 +57,63 @@ def test_recompute_matches_forward_activation_up_to_the_weight_rounding():
         rec = O.recompute_act(gate, up, w.to(torch.bfloat16), act, **kw)
         fwd = (O.gated_activation(gate, up, act, **kw) * w.unsqueeze(-1)).to(torch.bfloat16)
         torch.testing.assert_close(rec.float(), fwd.float(), rtol=2e-2, atol=2e-2)
+
+
+# ---- pinned by the reference's own source text (tests/golden/make_golden_saved.py) ----------
+def _fixture(name):
+    import numpy as np
+    from conftest import GOLDEN_DIR
+    with np.load(GOLDEN_DIR / name) as z:
+        return {k: z[k] for k in z.files}
+
+
+def _bf16(a):
+    return torch.from_numpy(a.copy()).view(torch.bfloat16)
+
+
+def test_saved_formats_reproduce_the_reference_save_leg_bit_exactly():
+    """fp16 / fp8 save of raw FC1 rows: the reference's store statement
+    (kernels/fused_forward.py:891-949) executed on the same rows."""
+    z = _fixture("saved_formats.npz")
+    rows, ffn, group = (int(v) for v in z["meta"])
+    raw = _bf16(z["in_raw"])
+    assert torch.equal(_bf16(z["save_bf16"]), raw)
+    h = O.convert_fc1_fp16(raw)
+    assert torch.equal(h.view(torch.int16), torch.from_numpy(z["save_fp16"].copy()))
+    q, scale = O.quantize_fc1_fp8(raw, group)
+    assert torch.equal(q.view(torch.uint8), torch.from_numpy(z["save_fp8"].copy()))
+    assert torch.equal(scale, torch.from_numpy(z["save_fp8_scale"].copy()))
+
+
+def test_recompute_reproduces_the_reference_helper_bit_exactly():
+    """_recompute_act_rows (kernels/mega_bwd.py:1414-1465) on bf16 and fp8 saved rows."""
+    z = _fixture("saved_formats.npz")
+    rows, ffn, group = (int(v) for v in z["meta"])
+    raw = _bf16(z["in_raw"])
+    w = _bf16(z["in_weights"])
+    q = torch.from_numpy(z["save_fp8"].copy()).view(torch.float8_e4m3fn)
+    scale = torch.from_numpy(z["save_fp8_scale"].copy())
+    acts = {"swiglu": ("swiglu", {}),
+            "situglu": ("situglu", dict(situ_beta=1.5, situ_linear_beta=2.0)),
+            "situglu_plain_up": ("situglu", dict(situ_beta=0.75, situ_linear_beta=None)),
+            "clamp_swiglu": ("clamp_swiglu", dict(clamp_limit=0.5))}
+    for fmt in ("bf16", "fp8"):
+        vals = raw.float() if fmt == "bf16" else O.dequantize_fc1(q, scale, group)
+        for name, (act, kw) in acts.items():
+            got = O.recompute_act(vals[:, :ffn], vals[:, ffn:], w, act, **kw)
+            want = _bf16(z[f"recompute_{fmt}_{name}"])
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (fmt, name)
+
+
+def test_saved_contract_tables_reproduce_the_reference_helpers():
+    """prepare_moe_metadata and _arrival_to_slot_permutation of the reference on seeded counts."""
+    import numpy as np
+    z = _fixture("saved_tables.npz")
+    for i, (world, epr) in enumerate(z["cases"]):
+        counts = z[f"c{i}_counts"]
+        per_expert = counts.sum(0)
+        perm = O.arrival_to_slot_permutation(counts, np.cumsum(per_expert) - per_expert)
+        np.testing.assert_array_equal(perm, z[f"c{i}_local_sort_idxs"])
+        meta = O.tile_metadata(per_expert)
+        for key, val in meta.items():
+            np.testing.assert_array_equal(val, z[f"c{i}_{key}"], err_msg=key)
