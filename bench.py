@@ -40,24 +40,40 @@ WORKLOADS = {
     # the configuration the headline metric is quoted on
     "kimi_k3_e896_k16_t8192": dict(tokens=8192, hidden=7168, ffn=2048, experts=896, top_k=16,
                                    capacity=1.25),
-    # one rank's share of the headline layer at 8 GPUs (112 local experts, same rows per rank):
-    # the per-GPU GEMM shapes of the 8-GPU run on a single GPU, for kernel tuning and ncu
+    # the same layer at the other token counts the reference sweeps (multi-GPU runs; at one GPU
+    # 16384 tokens per rank exceed the memory left beside 158 GB of weights and gradients)
+    "kimi_k3_e896_k16_t4096": dict(tokens=4096, hidden=7168, ffn=2048, experts=896, top_k=16,
+                                   capacity=1.25),
+    "kimi_k3_e896_k16_t16384": dict(tokens=16384, hidden=7168, ffn=2048, experts=896, top_k=16,
+                                    capacity=1.25),
+    # Qwen3-30B-A3B-like layer, forward only
+    "qwen3_30b_e128_k8_t4096": dict(tokens=4096, hidden=2048, ffn=768, experts=128, top_k=8,
+                                    capacity=1.25, forward_only=True),
+    # 32 experts with a Zipf(1.2) router bias: the hottest expert receives several times the
+    # mean load; the receive capacity is sized from the measured hottest rank
+    "e32_zipf12_k8_t8192": dict(tokens=8192, hidden=7168, ffn=2048, experts=32, top_k=8,
+                                capacity="measured", zipf=1.2),
+    # Qwen3-235B-A22B-like layer with a Zipf(1.0) router bias, and its small-batch case
+    "qwen3_235b_e128_k8_t8192": dict(tokens=8192, hidden=4096, ffn=1536, experts=128, top_k=8,
+                                     capacity="measured", zipf=1.0),
+    "qwen3_235b_e128_k8_t128": dict(tokens=128, hidden=4096, ffn=1536, experts=128, top_k=8,
+                                    capacity="measured", zipf=1.0),
+    # ---- slices for profiler captures (ncu replays every kernel ~40 times, so a capture must
+    # hold a few GB at most): the headline layer's H, F and rows per expert on fewer experts --
+    # one rank's share of the headline layer at 8 GPUs (112 local experts, same rows per rank)
     "kimi_k3_rank_share_e112_k16_t8192": dict(tokens=8192, hidden=7168, ffn=2048, experts=112,
                                               top_k=16, capacity=1.25),
-    # a slice of that share small enough for multi-pass ncu captures (16 experts, 1170 rows each)
+    # 16 experts with 1170 rows each (the per-expert load at 8 GPUs)
     "kimi_k3_rank_share_slice_e16_t1170": dict(tokens=1170, hidden=7168, ffn=2048, experts=16,
                                                top_k=16, capacity=1.25),
-    # a slice of the single-GPU headline run: 32 experts with 146 rows each (weights 2.8 GB)
+    # 32 experts with 146 rows each (the per-expert load on one GPU; weights 2.8 GB)
     "kimi_k3_single_gpu_slice_e32_t292": dict(tokens=292, hidden=7168, ffn=2048, experts=32,
                                               top_k=16, capacity=1.25),
-    # slices with the rows per expert of the 2- and 4-GPU runs (292 and 585)
+    # 292 and 585 rows per expert (2 and 4 GPUs)
     "kimi_k3_two_gpu_slice_e32_t584": dict(tokens=584, hidden=7168, ffn=2048, experts=32,
                                            top_k=16, capacity=1.25),
     "kimi_k3_four_gpu_slice_e32_t1170": dict(tokens=1170, hidden=7168, ffn=2048, experts=32,
                                              top_k=16, capacity=1.25),
-    # smaller shapes for quick checks and ncu captures (not bench lines)
-    "qwen3_30b_e128_k8_t4096": dict(tokens=4096, hidden=2048, ffn=768, experts=128, top_k=8,
-                                    capacity=1.25),
     "small_e32_k4_t1024": dict(tokens=1024, hidden=1024, ffn=512, experts=32, top_k=4,
                                capacity=2.0),
 }
@@ -180,17 +196,31 @@ def bind_host_threads_near_gpu(local_rank, nvml=None, uuid=None):
         return None
 
 
+def make_routes(w, rank, device):
+    """Seeded router outputs of one rank: top-k of N(0,1) logits (plus the workload's Zipf bias)
+    and the softmax over the selected logits."""
+    T, E, k = w["tokens"], w["experts"], w["top_k"]
+    g = torch.Generator(device=device).manual_seed(2000 + rank)
+    logits = torch.randn(T, E, generator=g, device=device)
+    if w.get("zipf"):
+        # per-expert bias 2 * log(1 / rank_e ** s) over a seeded permutation of the experts,
+        # the same on every rank
+        perm = torch.randperm(E, generator=torch.Generator().manual_seed(7))
+        pos = torch.empty(E, dtype=torch.float32)
+        pos[perm] = torch.arange(1, E + 1, dtype=torch.float32)
+        logits = logits + (2.0 * torch.log(1.0 / pos ** float(w["zipf"]))).to(device)
+    top_v, top_i = torch.topk(logits, k, dim=-1)
+    return top_i.to(torch.int32).contiguous(), torch.softmax(top_v, dim=-1).float().contiguous()
+
+
 def make_device_inputs(w, rank, world, device):
     """Seeded synthetic inputs of one rank, created on the device (weights are tens of GB)."""
     epr = w["experts"] // world
     g = torch.Generator(device=device).manual_seed(1000 + rank)
-    T, H, F, E, k = w["tokens"], w["hidden"], w["ffn"], w["experts"], w["top_k"]
+    T, H, F = w["tokens"], w["hidden"], w["ffn"]
     x = torch.randn(T, H, generator=g, device=device).to(torch.bfloat16)
     dy = torch.randn(T, H, generator=g, device=device).to(torch.bfloat16)
-    logits = torch.randn(T, E, generator=g, device=device)
-    top_v, top_i = torch.topk(logits, k, dim=-1)
-    rw = torch.softmax(top_v, dim=-1).float().contiguous()
-    sel = top_i.to(torch.int32).contiguous()
+    sel, rw = make_routes(w, rank, device)
     gate_up = torch.empty(epr, H, 2 * F, dtype=torch.bfloat16, device=device)
     down = torch.empty(epr, H, F, dtype=torch.bfloat16, device=device)
     for e0 in range(0, epr, 64):
@@ -218,6 +248,19 @@ class GemmTimer:
         return per
 
 
+def measured_capacity_factor(sel, experts, world, top_k, group, device):
+    """Receive capacity for a skewed router: rows of the hottest rank over the rows a rank
+    sends, plus 2 % head room, rounded up to 1/64 (the whole group routes first, then every
+    rank sizes its buffers alike)."""
+    epr = experts // world
+    per_rank = torch.bincount((sel.reshape(-1).long() // epr), minlength=world).to(device)
+    if world > 1:
+        dist.all_reduce(per_rank, group=group)
+    hottest = int(per_rank.max().item())
+    factor = hottest / float(sel.numel()) * 1.02
+    return min(float(world), max(1.0, -(-factor * 64 // 1) / 64)), hottest
+
+
 def run_ours(args, w, name):
     import mega_moe
     from mega_moe import _native as N
@@ -236,16 +279,29 @@ def run_ours(args, w, name):
         dist.init_process_group("nccl", device_id=device)
         group = dist.group.WORLD
     T, H, F, E, k = w["tokens"], w["hidden"], w["ffn"], w["experts"], w["top_k"]
-    cfg = mega_moe.MoEForwardConfig(receive_capacity_factor=min(float(w["capacity"]), float(world)),
+    forward_only = bool(w.get("forward_only"))
+    # the routes come first: a skewed router sizes the receive buffers from the hottest rank
+    hottest_rows = None
+    if w["capacity"] == "measured":
+        capacity, hottest_rows = measured_capacity_factor(make_routes(w, rank, device)[0], E,
+                                                          world, k, group, device)
+    else:
+        capacity = min(float(w["capacity"]), float(world))
+    cfg = mega_moe.MoEForwardConfig(receive_capacity_factor=capacity,
                                     enable_single_kernel_forward=True)
     # symmetric buffers first: they are plain cudaMalloc blocks outside torch's allocator
     op = mega_moe.FusedMoEForward(group, max_tokens_per_rank=T, hidden_size=H, top_k=k,
                                   num_experts=E, config=cfg)
-    # expert-weight gradients land in buffers allocated once (the work per step is unchanged)
-    op.persistent_weight_grads = True
-    # no host synchronisation inside a step; saved activations are views of fixed buffers
-    op.host_sync_free = True
-    op.saved_views = True
+
+    def set_mode(fast: bool):
+        # fast: expert-weight gradients land in buffers allocated once, no host synchronisation
+        # inside a step, saved activations are views of fixed buffers (the work per step is the
+        # same); otherwise the drop-in defaults of the reference API
+        op.persistent_weight_grads = fast
+        op.host_sync_free = fast
+        op.saved_views = fast
+
+    set_mode(True)
     x, dy, rw, sel, gate_up, down = make_device_inputs(w, rank, world, device)
     x.requires_grad_(True)
     rw.requires_grad_(True)
@@ -259,6 +315,9 @@ def run_ours(args, w, name):
     state = __import__("types").SimpleNamespace()
 
     def step(xx, rr, ss, dd):
+        if forward_only:
+            with torch.no_grad():
+                return op(xx, ss, gate_up, down, rr), None
         out = mega_moe.MegaMoEFunction.apply(op, xx, rr, ss, gate_up, down, op.context.peer_mem,
                                              state)
         grads = torch.autograd.grad(out, [xx, rr, gate_up, down], dd)
@@ -286,45 +345,73 @@ def run_ours(args, w, name):
     def resident_step():
         step(x, rw, sel, dy)
 
+    def forward_step():
+        with torch.no_grad():
+            op(x, sel, gate_up, down, rw)
+
     # End-to-end step: this step's inputs come from pinned host memory and its results go back
-    # to pinned host memory, every step.  Copies run on their own streams so that the upload
-    # of step i+1 and the download of step i-1 overlap the kernels of step i, as an input
-    # pipeline of a training loop would.
+    # to pinned host memory, every step.  Two sets of device staging buffers are allocated once;
+    # the upload of step i+1 (copy stream) overlaps the kernels of step i, the download of step
+    # i's results (second copy stream) overlaps step i+1, as the input pipeline of a training
+    # loop would.  No allocation and no allocator bookkeeping happens inside the timed region.
     copy_in = torch.cuda.Stream(device)
     copy_out = torch.cuda.Stream(device)
-    staged = []
+    stage = [dict(x=torch.empty_like(x.detach()), rw=torch.empty_like(rw.detach()),
+                  sel=torch.empty_like(sel), dy=torch.empty_like(dy)) for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    copy_events = []            # (kind, start, end) of the timed copies
+    in_flight = []              # results whose download may still be running
+    e2e_state = dict(step=0, primed=False, record=False)
 
-    def stage_inputs():
+    def upload(slot):
         with torch.cuda.stream(copy_in):
-            tensors = (host["x"].to(device, non_blocking=True),
-                       host["rw"].to(device, non_blocking=True),
-                       host["sel"].to(device, non_blocking=True),
-                       host["dy"].to(device, non_blocking=True))
-            ev = torch.cuda.Event()
-            ev.record(copy_in)
-        staged.append((tensors, ev))
+            copy_in.wait_event(consumed[slot])
+            ev0 = torch.cuda.Event(enable_timing=True)
+            ev1 = torch.cuda.Event(enable_timing=True)
+            ev0.record(copy_in)
+            for key in ("x", "rw", "sel", "dy"):
+                stage[slot][key].copy_(host[key], non_blocking=True)
+            ev1.record(copy_in)
+            in_ready[slot].record(copy_in)
+        if e2e_state["record"]:
+            copy_events.append(("h2d", ev0, ev1))
 
     def e2e_step():
         main = torch.cuda.current_stream(device)
-        if not staged:
-            stage_inputs()
-        (xx, rr, ss, dd), ev = staged.pop(0)
-        main.wait_event(ev)
-        for t in (xx, rr, ss, dd):
-            t.record_stream(main)
-        stage_inputs()
-        xx.requires_grad_(True)
-        rr.requires_grad_(True)
-        out, grads = step(xx, rr, ss, dd)
+        i = e2e_state["step"]
+        slot = i % 2
+        if not e2e_state["primed"]:
+            consumed[0].record(main)
+            consumed[1].record(main)
+            upload(slot)
+            e2e_state["primed"] = True
+        upload(1 - slot)                       # next step's inputs, behind this step's kernels
+        main.wait_event(in_ready[slot])
+        buf = stage[slot]
+        xx = buf["x"].detach().requires_grad_(True)
+        rr = buf["rw"].detach().requires_grad_(True)
+        out, grads = step(xx, rr, buf["sel"], buf["dy"])
+        consumed[slot].record(main)
         done = torch.cuda.Event()
         done.record(main)
         with torch.cuda.stream(copy_out):
             copy_out.wait_event(done)
+            ev0 = torch.cuda.Event(enable_timing=True)
+            ev1 = torch.cuda.Event(enable_timing=True)
+            ev0.record(copy_out)
             host_out.copy_(out.detach(), non_blocking=True)
-            host_gh.copy_(grads[0], non_blocking=True)
-            host_grw.copy_(grads[1], non_blocking=True)
-        for t in (out, grads[0], grads[1]):
-            t.record_stream(copy_out)
+            if grads is not None:
+                host_gh.copy_(grads[0], non_blocking=True)
+                host_grw.copy_(grads[1], non_blocking=True)
+            ev1.record(copy_out)
+        if e2e_state["record"]:
+            copy_events.append(("d2h", ev0, ev1))
+        # keep the results alive until their download has finished (two steps are plenty)
+        in_flight.append((out, grads, ev1))
+        if len(in_flight) > 2:
+            in_flight.pop(0)[2].synchronize()
+        e2e_state["step"] = i + 1
 
     for _ in range(args.warmup):
         resident_step()
@@ -343,30 +430,66 @@ def run_ours(args, w, name):
     torch.cuda.synchronize()
     launches_per_step = N.launch_count - before
 
+    # forward alone (the metric also asks for the forward's time)
+    forward_step()
+    fwd_ms = timed(forward_step, args.steps) / args.steps
+
     for _ in range(max(1, min(args.warmup, 2))):
         e2e_step()
+    e2e_state["record"] = True
     e2e_ms = timed(e2e_step, args.steps)
+    e2e_state["record"] = False
+    while in_flight:
+        in_flight.pop(0)[2].synchronize()
+    copy_ms = {"h2d": 0.0, "d2h": 0.0}
+    for kind, ev0, ev1 in copy_events:
+        copy_ms[kind] += ev0.elapsed_time(ev1)
     status = op.context.read_status()
     m_rows = int(op.context.metadata_stats[0].item())
+
+    # The same step with the reference API's defaults: host reads of the row counts, copies of
+    # the saved activations, freshly allocated weight gradients.  Skipped when the allocator
+    # has no room for the copies.
+    default_ms = None
+    if not forward_only and not os.environ.get("MOE_BENCH_NO_DEFAULT_MODE"):
+        free_b, _total = torch.cuda.mem_get_info(device)
+        weights_b = (gate_up.numel() + down.numel()) * 2
+        need = weights_b + 4 * m_rows * (H + 3 * F) * 2
+        roomy = torch.tensor([1 if free_b > need else 0], device=device)
+        if world > 1:
+            dist.all_reduce(roomy, op=dist.ReduceOp.MIN, group=group)
+        if int(roomy.item()):
+            set_mode(False)
+            op._grad_ws = None
+            torch.cuda.empty_cache()
+            for _ in range(2):
+                resident_step()
+            default_ms = timed(resident_step, args.steps) / args.steps
+            set_mode(True)
 
     ms_per_step = total_ms / args.steps
     tokens_per_s = world * T / (ms_per_step / 1e3)
     e2e_tokens_per_s = world * T / (e2e_ms / args.steps / 1e3)
     h2d = sum(t.numel() * t.element_size() for t in host.values())
-    d2h = sum(t.numel() * t.element_size() for t in (host_out, host_gh, host_grw))
+    d2h = sum(t.numel() * t.element_size() for t in
+              ((host_out,) if forward_only else (host_out, host_gh, host_grw)))
 
     # roofline of the dominant kernel (the grouped GEMM, six launches per step)
     peaks = measured_peaks()
     epr = E // world
-    gemm_names = ("fc1_swiglu", "fc2_combine", "fc2_dgrad", "fc2_wgrad", "fc1_wgrad",
-                  "fc1_dgrad_combine")
+    gemm_names = ("fc1_swiglu", "fc2_combine") if forward_only else (
+        "fc1_swiglu", "fc2_combine", "fc2_dgrad", "fc2_wgrad", "fc1_wgrad", "fc1_dgrad_combine")
     gemm_total_ms = max(sum(sum(gemm_ms.get(n, [])) for n in gemm_names) / args.steps, 1e-9)
-    flops = 18.0 * m_rows * H * F
     weight_bytes = epr * 3 * H * F * 2
-    # weights are read twice (forward, input gradient) and their gradients written once;
-    # every [M, *] operand or result of the six GEMMs is read or written once
-    act_bytes = m_rows * 2 * (H + 2 * F + F + H + H + F + 2 * F + H + H + F + 2 * F + H)
-    bytes_alg = 3 * weight_bytes + act_bytes
+    if forward_only:
+        flops = 6.0 * m_rows * H * F
+        bytes_alg = weight_bytes + m_rows * 2 * (H + F + F + H)
+    else:
+        flops = 18.0 * m_rows * H * F
+        # weights are read twice (forward, input gradient) and their gradients written once;
+        # every [M, *] operand or result of the six GEMMs is read or written once
+        act_bytes = m_rows * 2 * (H + 2 * F + F + H + H + F + 2 * F + H + H + F + 2 * F + H)
+        bytes_alg = 3 * weight_bytes + act_bytes
     t_tensor = flops / (peaks["tflops"] * 1e12)
     t_hbm = bytes_alg / (peaks["hbm_gbs"] * 1e9)
     if t_hbm >= t_tensor:
@@ -377,40 +500,62 @@ def run_ours(args, w, name):
         achieved = flops / (gemm_total_ms / 1e3) / 1e12
         roofline = dict(bound="tensor", achieved=round(achieved, 1), peak=peaks["tflops"],
                         unit="TFLOP/s", frac=round(achieved / peaks["tflops"], 4), traffic=None)
-    roofline["traffic"] = measured_traffic(H, F, k, m_rows, epr)
+    roofline["traffic"] = None if forward_only else measured_traffic(H, F, k, m_rows, epr)
     roofline["traffic_unit"] = "bytes per step (six launches), ncu capture of a slice scaled by local experts"
     roofline["algorithmic_bytes"] = bytes_alg
-    roofline["kernel"] = "grouped_gemm_kernel / skinny_gemm_kernel (6 GEMM launches per step)"
+    roofline["algorithmic_flops"] = flops
+    roofline["kernel"] = "grouped_gemm_kernel / skinny_gemm_kernel (the GEMM launches of a step)"
     roofline["kernel_ms_per_step"] = round(gemm_total_ms, 3)
     roofline["peak_source"] = peaks["source"]
     roofline["per_launch_ms"] = {k_: round(sum(v) / len(v), 3) for k_, v in gemm_ms.items()}
+    # north_star's roofline: the slower of the step's FLOPs at the dense bf16 peak and the
+    # dispatch + combine bytes that leave a rank at the NVLink rate, against the whole step
+    remote = (world - 1) / world
+    nvlink_bytes = (2 if forward_only else 4) * T * k * H * 2 * remote
+    step_floor_ms = max(flops / (peaks["tflops"] * 1e12), nvlink_bytes / 770e9) * 1e3
+    roofline["step"] = {
+        "floor_ms": round(step_floor_ms, 3), "frac_of_measured": round(step_floor_ms / ms_per_step, 4),
+        "frac_of_nominal_2250_tflops_900_gbs": round(
+            max(flops / 2.25e15, nvlink_bytes / 900e9) * 1e3 / ms_per_step, 4),
+        "nvlink_bytes_out_per_rank": int(nvlink_bytes),
+        "literal_6kHF_ratio": round(6.0 * T * k * H * F / 2.25e15 * 1e3 / ms_per_step, 4)}
 
     line = None
     if rank == 0:
         # MOE_BENCH_NO_CPU=1 skips the CPU leg (profiler runs, where only the launches matter)
         cpu = (cpu_baseline_sample(w, seconds_hint=20.0)
                if world == 1 and not os.environ.get("MOE_BENCH_NO_CPU") else None)
+        what = "fwd" if forward_only else "fwd+bwd"
         line = {
-            "metric": METRIC if name == DEFAULT_WORKLOAD else f"MoE fwd+bwd tokens/s ({name})",
+            "metric": METRIC if name == DEFAULT_WORKLOAD else f"MoE {what} tokens/s ({name})",
             "value": round(tokens_per_s, 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3),
+            "fwd_ms": round(fwd_ms, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": name, "tokens_per_rank": T, "hidden": H, "ffn": F,
                        "experts": E, "top_k": k, "experts_per_rank": epr,
-                       "receive_capacity_factor": cfg.receive_capacity_factor
-                       if cfg.receive_capacity_factor is not None else world,
+                       "router": f"zipf s={w['zipf']}" if w.get("zipf") else "balanced",
+                       "receive_capacity_factor": capacity,
+                       "hottest_rank_rows": hottest_rows,
                        "received_rows_rank0": m_rows, "parallelism": f"ep{world}",
+                       "pass": what,
                        "gemm_tile_mode": ("single", "pair", "skinny")[L.gemm_tile_mode(op.context)],
                        "wgrad_tile_mode": ("single", "pair", "unit")[L.wgrad_tile_mode(op.context)],
                        "fused_dispatch": bool(L.fused_dispatch_enabled(op.context)),
+                       "operator_mode": "persistent_weight_grads + host_sync_free + saved_views",
                        "host_threads_bound_to_gpu_local_cpus": host_cpus,
                        "l2": "inputs larger than L2 (expert weights and their gradients "
                              f"are {3 * weight_bytes / 1e9:.1f} GB per rank and step)"},
             "tokens_per_s_per_gpu": round(tokens_per_s / world, 1),
+            "value_default_mode": (round(world * T / (default_ms / 1e3), 1)
+                                   if default_ms else None),
+            "ms_per_step_default_mode": round(default_ms, 3) if default_ms else None,
             "e2e": {"value": round(e2e_tokens_per_s, 1), "unit": "tokens/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": round(e2e_ms / args.steps, 3)},
+                    "ms_per_step": round(e2e_ms / args.steps, 3),
+                    "h2d_gbs": round(h2d * args.steps / max(copy_ms["h2d"], 1e-6) / 1e6, 1),
+                    "d2h_gbs": round(d2h * args.steps / max(copy_ms["d2h"], 1e-6) / 1e6, 1)},
             "gpu_launches": launches_per_step * args.steps,
             "gpu_launches_per_step": launches_per_step,
             "roofline": roofline,
@@ -442,20 +587,26 @@ def cpu_baseline_sample(w, seconds_hint=20.0, steps=1, warmup=0):
     flop_per_expert = 18.0 * rows_per_expert * H * F
     budget = seconds_hint * 0.15e12          # assume ~0.15 TFLOP/s of bf16 matmul on the host
     sample_experts = int(max(1, min(E, 64, budget // flop_per_expert)))
-    routes = rows_per_expert * sample_experts
-    tokens = max(1, routes)                  # top-1 over the sampled experts keeps rows/expert
+    # top-k' routes per token over the sampled experts (k' = k when the sample holds at least k
+    # experts), token t taking experts (t * k' + j) mod sample: every expert gets the workload's
+    # rows per expert and every token's k' rows are summed back, as in the layer
+    kk = min(k, sample_experts)
+    tokens = max(1, rows_per_expert * sample_experts // kk)
+    routes = tokens * kk
     g = torch.Generator().manual_seed(0)
     x = torch.randn(tokens, H, generator=g).to(torch.bfloat16)
     dy = torch.randn(tokens, H, generator=g).to(torch.bfloat16)
-    sel = (torch.arange(tokens) % sample_experts).to(torch.int32).view(tokens, 1)
-    rw = torch.rand(tokens, 1, generator=g)
+    sel = (torch.arange(tokens * kk) % sample_experts).to(torch.int32).view(tokens, kk)
+    rw = torch.softmax(torch.randn(tokens, kk, generator=g), dim=-1)
     w1 = (torch.randn(sample_experts, F, H, generator=g) * 0.02).to(torch.bfloat16)
     w2 = (torch.randn(sample_experts, F, H, generator=g) * 0.02).to(torch.bfloat16)
     w3 = (torch.randn(sample_experts, H, F, generator=g) * 0.02).to(torch.bfloat16)
+    forward_only = bool(w.get("forward_only"))
 
     def one():
-        _, saved = O.forward_saved([x], [rw], [sel], [w1], [w2], [w3], 1)
-        O.backward(saved, [dy])
+        _, saved = O.forward_saved([x], [rw], [sel], [w1], [w2], [w3], kk)
+        if not forward_only:
+            O.backward(saved, [dy])
 
     for _ in range(warmup):
         one()
@@ -463,11 +614,13 @@ def cpu_baseline_sample(w, seconds_hint=20.0, steps=1, warmup=0):
     for _ in range(steps):
         one()
     dt = (time.perf_counter() - t0) / steps
+    # a token of the workload carries k routes: the sample's routes / k are its tokens
     return {"value": round(routes / k / dt, 2), "unit": "tokens/s", "cores": threads,
             "kind": "port",
-            "sample": f"{sample_experts} of {E} experts with {rows_per_expert} rows each "
-                      f"(H={H}, F={F}): {routes} routes = {routes / k:.1f} tokens at top-{k}; "
-                      f"{dt:.2f} s per forward+backward",
+            "sample": f"{sample_experts} of {E} experts with {routes // sample_experts} rows each "
+                      f"(H={H}, F={F}), {tokens} tokens at top-{kk}: {routes} routes = "
+                      f"{routes / k:.1f} tokens of the workload at top-{k}; "
+                      f"{dt:.2f} s per {'forward' if forward_only else 'forward+backward'}",
             "seconds_per_pass": round(dt, 3)}
 
 

@@ -3,8 +3,10 @@
 Usage: ``python mega-moe-td_b200/build.py [--force] [--verbose] [--profile]``.  The shared
 library lands in ``mega-moe-td_b200/lib/`` next to the sources, so a copy of the repository
 carries it.  ``--profile`` builds a second, instrumented library
-(``libmegamoe_sm100_prof.so``, ``-DMM_PROFILE``) whose GEMM kernels count the clocks each warp
-role spends in its waits; ``profile_roles.py`` reads them.  The product never loads it.
+(``libmegamoe_sm100_prof.so``, ``-DMM_PROFILE``) whose GEMM kernels also count the clocks each
+warp role spends in its waits; the package loads it instead of the plain one when
+``MOE_FWD_TIMING=1`` is set, and ``FusedMoEForward.read_last_forward_phase_timing()`` returns
+the counters (``python -m mega_moe.phase_timing`` prints them).
 """
 from __future__ import annotations
 

@@ -6,6 +6,7 @@ and :func:`lib` raises ``RuntimeError`` when the library is missing.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 from typing import Optional
 
@@ -13,6 +14,18 @@ import torch
 
 _PKG_ROOT = Path(__file__).resolve().parent.parent
 LIB_PATH = _PKG_ROOT / "lib" / "libmegamoe_sm100.so"
+# Same sources compiled with -DMM_PROFILE: every warp role of the GEMM kernels also sums the SM
+# clocks it spends in each of its waits.  Loaded instead of LIB_PATH when MOE_FWD_TIMING=1 is
+# set before the first call into the library (and the file has been built).
+TIMING_LIB_PATH = _PKG_ROOT / "lib" / "libmegamoe_sm100_prof.so"
+# Per-CTA counters a GEMM launch of the instrumented library writes, in this order.
+ROLE_COUNTER_SLOTS = (
+    "prod_empty", "prod_bempty", "prod_flag", "mma_acc_empty", "mma_full", "mma_tail",
+    "mma_total", "epi_acc_full", "epi_store_read", "epi_total", "tiles", "prod_issue",
+    "prod_total", "mma_issue", "mma_decode")
+# launch name -> int64 [160, 16] counters of the latest launch of that name (instrumented
+# library only; see ops/_launch.py)
+role_counters: dict = {}
 
 MM_OK = 0
 ACT_IDS = {"swiglu": 0, "situglu": 1, "clamp_swiglu": 2}
@@ -115,13 +128,37 @@ def lib() -> C.CDLL:
             raise RuntimeError(
                 f"{LIB_PATH} is missing: build it with `python mega-moe-td_b200/build.py` "
                 "(there is no CPU or PyTorch fallback for the MoE kernels)")
-        handle = C.CDLL(str(LIB_PATH))
+        path = LIB_PATH
+        if forward_timing_enabled() and TIMING_LIB_PATH.exists():
+            path = TIMING_LIB_PATH
+        handle = C.CDLL(str(path))
         for name, (restype, argtypes) in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.restype = restype
             fn.argtypes = argtypes
+        if path == TIMING_LIB_PATH:
+            handle.mm_profile_buffer.restype = None
+            handle.mm_profile_buffer.argtypes = [C.c_void_p]
         _lib = handle
     return _lib
+
+
+def forward_timing_enabled() -> bool:
+    """``MOE_FWD_TIMING=1``, the reference's switch for in-kernel phase timing
+    (kernels/fused_forward.py:53-130)."""
+    return os.environ.get("MOE_FWD_TIMING") == "1"
+
+
+def role_counters_available() -> bool:
+    """True when the loaded library is the instrumented one."""
+    return hasattr(lib(), "mm_profile_buffer") and forward_timing_enabled()
+
+
+def begin_role_counters(name: str) -> None:
+    """Point the next GEMM launch's role counters at a fresh buffer filed under ``name``."""
+    buf = torch.zeros(160, 16, dtype=torch.int64, device=torch.cuda.current_device())
+    role_counters[name] = buf
+    lib().mm_profile_buffer(buf.data_ptr())
 
 
 def check(rc: int, what: str) -> None:

@@ -21,8 +21,11 @@ EVENT_HOOK = None
 class _timed:
     def __init__(self, name):
         self.pair = EVENT_HOOK(name) if EVENT_HOOK is not None else None
+        self.name = name
 
     def __enter__(self):
+        if N.forward_timing_enabled() and N.role_counters_available():
+            N.begin_role_counters(self.name)
         if self.pair is not None:
             self.pair[0].record()
 

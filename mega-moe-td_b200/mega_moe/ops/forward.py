@@ -33,6 +33,7 @@ from ..runtime.routing import (
     launch_routing_metadata,
 )
 from ..runtime.workspace import carve_plan, create_moe_forward_context
+from .. import _native as N
 from . import _launch as L
 
 
@@ -259,16 +260,22 @@ class FusedMoEForward(torch.nn.Module):
         (the reference's switch, ops/forward.py:1555-1570; there the products are SYS_CNT
         ticks per Ascend core, here CUDA-event times on the caller's stream).
 
-        Returns ``{"phase_ms": {phase: ms}, "total_ms": ms}`` with the phases
-        ``routing_metadata``, ``dispatch_fc1_activation`` (dispatch, FC1 and the weighted
-        activation are one launch, or a chain without gaps), ``fc2_combine``, ``rank_barrier``
-        and ``topk_reduce``.  Waits for the last stamp.  Raises ``RuntimeError`` when no forward
-        has run with the switch set.
+        Returns ``{"phase_ms": {phase: ms}, "total_ms": ms, "acc": {...}, "acc_slots": (...)}``
+        with the phases ``routing_metadata``, ``dispatch_fc1_activation`` (dispatch, FC1 and
+        the weighted activation are one launch, or a chain without gaps), ``fc2_combine``,
+        ``rank_barrier`` and ``topk_reduce``.  ``acc`` is the counterpart of the reference's
+        issue-stream busy ticks: when the instrumented library is built
+        (``python mega-moe-td_b200/build.py --profile``) and the switch was set before the
+        first call into the library, every grouped-GEMM launch since the forward began
+        (backward launches included) has an int64 ``[160, 16]`` device tensor of SM clocks per
+        CTA and warp role, columns named by ``acc_slots``; otherwise ``acc`` is empty.  Waits
+        for the last stamp.  Raises ``RuntimeError`` when no forward has run with the switch set.
         """
         if self._fwd_timing_last is None:
             raise RuntimeError("no forward has run on this operator with MOE_FWD_TIMING=1")
         phases = self._fwd_timing_last.phase_ms()
-        return {"phase_ms": phases, "total_ms": sum(phases.values())}
+        return {"phase_ms": phases, "total_ms": sum(phases.values()),
+                "acc": dict(N.role_counters), "acc_slots": N.ROLE_COUNTER_SLOTS}
 
     # ===================== validation =====================
     def _validate_topk_indices(self, selected_experts: torch.Tensor):
@@ -486,7 +493,9 @@ class FusedMoEForward(torch.nn.Module):
         two_step_fc1 = L.gemm_tile_mode(ctx) == L.TILE_SKINNY
         self._ensure_activation_buffers(ffn_size, need_fc1=return_saved or two_step_fc1)
         out = torch.empty(tokens, hidden, dtype=self.activation_dtype, device=hidden_states.device)
-        stamps = _PhaseStamps() if os.environ.get("MOE_FWD_TIMING") == "1" else None
+        stamps = _PhaseStamps() if N.forward_timing_enabled() else None
+        if stamps:
+            N.role_counters.clear()
 
         launch_routing_metadata(ctx, selected_experts)
         if stamps:

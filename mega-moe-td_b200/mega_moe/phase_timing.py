@@ -1,46 +1,39 @@
-"""Wait-time accounting of the GEMM kernels' warp roles (instrumented build, one GPU).
+"""Where the time of one layer step goes: phases of the forward and the waits of the GEMM
+kernels' warp roles, through the operator's own timing switch (one GPU).
 
     python mega-moe-td_b200/build.py --profile
-    python mega-moe-td_b200/profile_roles.py --experts 32 --rows-per-expert 146
+    PYTHONPATH=mega-moe-td_b200 MOE_FWD_TIMING=1 python -m mega_moe.phase_timing \
+        --experts 32 --rows-per-expert 146
 
-Runs a few forward+backward steps of the layer on synthetic, balanced routes with the
-``-DMM_PROFILE`` library, in which every role of ``grouped_gemm_kernel`` sums the SM clocks it
-spends in each of its waits, and prints per GEMM launch of the last step the mean over the CTAs:
+Runs a few forward+backward steps of the layer on synthetic, balanced routes with
+``MOE_FWD_TIMING=1`` and prints what ``FusedMoEForward.read_last_forward_phase_timing()``
+returns for the last step: the device time of each forward phase and, per GEMM launch, the mean
+over the CTAs of the SM clocks every role spent
 
-* producer: waiting for a free A slot / B slot / the dispatch arrival flags, time inside the TMA
-  issue, total;
-* MMA issuer (warp 1): waiting for a free accumulator, for loads ("full"), for the tail rows, time
-  inside the MMA issue, tile lookup - as fractions of its total;
+* producer: waiting for a free A slot / B slot / the dispatch arrival flags, inside the TMA
+  issue, in total;
+* MMA issuer (warp 1): waiting for a free accumulator, for loads ("full"), for the tail rows,
+  inside the MMA issue, in tile lookup - as fractions of its total;
 * epilogue (first epilogue warp): waiting for the accumulator, for the previous TMA store's read
   of the staging buffer - as fractions of its total.
 
 ``MM_PROFILE_SKIP_MMA=1`` frees the stages without issuing MMAs: what remains is the time of the
 load / epilogue pipeline alone.  ``skinny_gemm_kernel`` is not instrumented (its launches print
-zeros); use ``MOE_GEMM_MODE=single`` to look at the ragged-row GEMMs.
+nothing); use ``MOE_GEMM_MODE=single`` to look at the ragged-row GEMMs.
 """
 from __future__ import annotations
 
 import argparse
-import ctypes as C
 import os
-import sys
 import types
-from pathlib import Path
 
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
-HERE = Path(__file__).resolve().parent
-sys.path.insert(0, str(HERE))
+os.environ["MOE_FWD_TIMING"] = "1"
 
 import torch  # noqa: E402
 
-import build as native_build  # noqa: E402
 import mega_moe  # noqa: E402
 from mega_moe import _native as N  # noqa: E402
-from mega_moe.ops import _launch as L  # noqa: E402
-
-COLUMNS = ("prod_empty", "prod_bempty", "prod_flag", "mma_acc_empty", "mma_full", "mma_tail",
-           "mma_total", "epi_acc_full", "epi_store_read", "epi_total", "tiles", "prod_issue",
-           "prod_total", "mma_issue", "mma_decode")
 
 
 def main():
@@ -51,13 +44,9 @@ def main():
     ap.add_argument("--ffn", type=int, default=2048)
     ap.add_argument("--top-k", type=int, default=16)
     args = ap.parse_args()
-    if not native_build.PROFILE_LIB_PATH.exists():
-        raise SystemExit("build the instrumented library first: python build.py --profile")
-    N.LIB_PATH = native_build.PROFILE_LIB_PATH          # before the first N.lib() call
-    lib = N.lib()
-    lib.mm_profile_buffer.argtypes = [C.c_void_p]
-    lib.mm_profile_buffer.restype = None
-
+    if not N.TIMING_LIB_PATH.exists():
+        raise SystemExit("build the instrumented library first: "
+                         "python mega-moe-td_b200/build.py --profile")
     dev = torch.device("cuda", 0)
     E, k, H, F = args.experts, args.top_k, args.hidden, args.ffn
     tokens = args.rows_per_expert * E // k
@@ -86,23 +75,14 @@ def main():
     for _ in range(3):
         step()
     torch.cuda.synchronize()
-    buffers: dict[str, list[torch.Tensor]] = {}
-
-    def hook(name):
-        buf = torch.zeros(160, 16, dtype=torch.int64, device=dev)
-        buffers.setdefault(name, []).append(buf)
-        lib.mm_profile_buffer(buf.data_ptr())
-        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-
-    L.EVENT_HOOK = hook
     for _ in range(2):
         step()
-    torch.cuda.synchronize()
-    L.EVENT_HOOK = None
-    lib.mm_profile_buffer(None)
+    rec = op.read_last_forward_phase_timing()
+    print("forward phases, ms:", {k: round(v, 3) for k, v in rec["phase_ms"].items()})
     print("mean SM clocks per CTA, last step")
-    for name, bufs in buffers.items():
-        v = dict(zip(COLUMNS, bufs[-1][:148, :len(COLUMNS)].double().mean(0).tolist()))
+    slots = rec["acc_slots"]
+    for name, buf in rec["acc"].items():
+        v = dict(zip(slots, buf[:148, :len(slots)].double().mean(0).tolist()))
         if v["tiles"] == 0:
             continue
         mt, et = max(v["mma_total"], 1.0), max(v["epi_total"], 1.0)

@@ -25,6 +25,9 @@ CASES = [
     (512, 256, 384, 16, 4, 0.25, None, None),
     (1024, 512, 256, 32, 8, 0.0, 1.2, None),
     (300, 256, 128, 8, 3, 1.0, None, None),      # nothing is routed anywhere
+    # the real hidden / FFN size of the headline layer on a few experts (K = 7168: 112 k-blocks,
+    # 28 column tiles of the FC2 output, the 4096-wide packed FC1 table)
+    (64, 7168, 2048, 16, 8, 0.0, None, None),
 ]
 
 
@@ -46,7 +49,8 @@ def main():
             continue
         bias = O.zipf_expert_bias(experts, zipf) if zipf else None
         inp = O.make_inputs(world, tokens, hidden, ffn, experts, top_k, seed=50 + case_id,
-                            expert_bias=bias, drop_frac=drop, weight_std=0.05)
+                            expert_bias=bias, drop_frac=drop,
+                            weight_std=0.02 if hidden > 1024 else 0.05)
         want_out = O.forward_golden(inp["hidden"], inp["routing_weights"], inp["selected"],
                                     inp["w_gate"], inp["w_up"], inp["w_down"], experts)[rank]
         meta = O.routing_metadata([s.numpy() for s in inp["selected"]], experts)[rank]
@@ -78,6 +82,11 @@ def main():
                                    atol=O.OUTPUT_ATOL)
         if want_out.float().abs().max() > 0:
             check("fwd cosine", O.cosine(out.cpu(), want_out) > O.MIN_COSINE)
+        # epoch reuse: a second call on the same operator is bit-identical
+        # (reference gate: tests/layer/test_moe_suite.py:4636-4827)
+        out_again = op(x, sel, gate_up, down, rw)
+        check("repeated forward is bit-identical", torch.equal(out_again, out),
+              f"case {case_id} rank {rank}")
         # forward + backward through autograd (dropless routes only: the saved contract)
         if drop == 0.0:
             _, saved = O.forward_saved(inp["hidden"], inp["routing_weights"], inp["selected"],
@@ -103,6 +112,18 @@ def main():
                                 f"bad={n_bad}")
                 if gold.float().abs().max() > 0:
                     check(name + " cosine", O.cosine(got.cpu(), gold) > O.MIN_COSINE)
+            # a second forward + backward on the same operator reproduces every gradient bit
+            # for bit
+            first = {name: got.clone() for name, (got, _) in pairs.items()}
+            for t in (xg, rwg, gu, dn):
+                t.grad = None
+            o3 = mega_moe.MegaMoEFunction.apply(op, xg, rwg, sel, gu, dn, op.context.peer_mem,
+                                                types.SimpleNamespace())
+            o3.backward(inp["dy"][rank].to(dev))
+            for name, t in (("grad_hidden", xg), ("grad_routing_weights", rwg),
+                            ("grad_down", dn), ("grad_gate_up", gu)):
+                check("repeated " + name, torch.equal(t.grad, first[name]),
+                      f"case {case_id} rank {rank}")
             # the five-stage backward also accepts the Torch functional forward's saved dict
             sd = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v)
                   for k, v in saved[rank].items()}
@@ -159,6 +180,44 @@ def main():
                                    atol=O.OUTPUT_ATOL)
         check("skewed routes status", op.context.read_status().code == 0)
         op.finalize()
+    # zero-receive: every route goes to rank 0, whose buffer (capacity factor = world) holds
+    # them all; the other ranks receive nothing but still dispatch, combine and reduce
+    # (reference: tests/layer/test_moe_suite.py:327-357,464-500)
+    tokens, hidden, ffn, experts, top_k = 96, 256, 128, 4 * world, 3
+    inp = O.make_inputs(world, tokens, hidden, ffn, experts, top_k, seed=123, weight_std=0.05)
+    epr = experts // world
+    to_rank0 = [((torch.arange(tokens * top_k) * 7 + r) % epr).to(torch.int32).view(tokens, top_k)
+                for r in range(world)]
+    want_out = O.forward_golden(inp["hidden"], inp["routing_weights"], to_rank0, inp["w_gate"],
+                                inp["w_up"], inp["w_down"], experts)[rank]
+    _, saved = O.forward_saved(inp["hidden"], inp["routing_weights"], to_rank0, inp["w_gate"],
+                               inp["w_up"], inp["w_down"], top_k)
+    want = O.backward(saved, inp["dy"])[rank]
+    op = mega_moe.FusedMoEForward(group, max_tokens_per_rank=tokens, hidden_size=hidden,
+                                  top_k=top_k, num_experts=experts,
+                                  config=mega_moe.MoEForwardConfig(receive_capacity_factor=None))
+    xg = inp["hidden"][rank].to(dev).requires_grad_(True)
+    rwg = inp["routing_weights"][rank].to(dev).requires_grad_(True)
+    gu = mega_moe.pack_gate_up_weights(inp["w_gate"][rank].to(dev),
+                                       inp["w_up"][rank].to(dev)).requires_grad_(True)
+    dn = inp["w_down"][rank].to(dev).requires_grad_(True)
+    out = mega_moe.MegaMoEFunction.apply(op, xg, rwg, to_rank0[rank].to(dev), gu, dn,
+                                         op.context.peer_mem, types.SimpleNamespace())
+    received = int(op.context.metadata_stats[0].item())
+    check("zero-receive row count", received == (world * tokens * top_k if rank == 0 else 0))
+    torch.testing.assert_close(out.detach().cpu().float(), want_out.float(), rtol=O.OUTPUT_RTOL,
+                               atol=O.OUTPUT_ATOL)
+    out.backward(inp["dy"][rank].to(dev))
+    for name, got, gold in (("grad_hidden", xg.grad, want["grad_hidden"]),
+                            ("grad_routing_weights", rwg.grad, want["grad_routing_weights"]),
+                            ("grad_down", dn.grad, want["grad_fc2"]),
+                            ("grad_gate_up", gu.grad,
+                             torch.cat((want["grad_fc1_1"], want["grad_fc1_2"]),
+                                       dim=1).transpose(1, 2))):
+        ok, max_d, rel, n_bad = O.cmp_grad(got.cpu(), gold)
+        check("zero-receive " + name, ok, f"rank {rank} max_abs={max_d:.3e} bad={n_bad}")
+    check("zero-receive status", op.context.read_status().code == 0)
+    op.finalize()
     # receive-capacity overflow: every rank must raise ValueError, and the device stays usable
     tokens, hidden, ffn, experts, top_k = 256, 128, 128, 2 * world, 2
     inp = O.make_inputs(world, tokens, hidden, ffn, experts, top_k, seed=99)

@@ -15,12 +15,32 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.fixture(autouse=True, params=["auto", "single"])
+# (name, MOE_GEMM_MODE, MOE_WGRAD_MODE, MOE_FUSED_DISPATCH): every operator test runs with the
+# automatic choice of a single rank (transposed "skinny" tiles and the unit walk at these rows
+# per expert, separate row-push kernel), with the 128-row single-CTA tiles, with CTA pairs, and
+# with the dispatch warps fused into the GEMM launches -- the form every multi-GPU run uses
+# (on one GPU all peer pointers are local, the arrival flags and the per-expert waits run
+# unchanged).
+MODES = [
+    ("auto", "auto", "auto", None),
+    ("single", "single", "single", "0"),
+    ("pair", "pair", "pair", None),
+    ("auto-fused", "auto", "auto", "1"),
+    ("single-fused", "single", "single", "1"),
+    ("pair-fused-unit", "pair", "unit", "1"),
+]
+
+
+@pytest.fixture(autouse=True, params=MODES, ids=[m[0] for m in MODES])
 def tile_mode(request, monkeypatch):
-    """Every operator test runs with the automatic tile choice (the transposed "skinny" tiles at
-    these rows per expert) and with the 128-row single-CTA tiles."""
-    monkeypatch.setenv("MOE_GEMM_MODE", request.param)
-    return request.param
+    name, gemm, wgrad, fused = request.param
+    monkeypatch.setenv("MOE_GEMM_MODE", gemm)
+    monkeypatch.setenv("MOE_WGRAD_MODE", wgrad)
+    if fused is None:
+        monkeypatch.delenv("MOE_FUSED_DISPATCH", raising=False)
+    else:
+        monkeypatch.setenv("MOE_FUSED_DISPATCH", fused)
+    return name
 
 
 def _pow2_divisor(n, cap):
