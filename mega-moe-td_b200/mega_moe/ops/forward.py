@@ -415,8 +415,7 @@ class FusedMoEForward(torch.nn.Module):
         desc = L.make_desc(ctx, recv, ctx.max_received_routes, self.hidden_size, fc1_weight,
                            k_dim=1, n_dim=2, n_out=n_out, k_extent=self.hidden_size)
         if L.fused_dispatch_enabled(ctx):
-            # a plan may be dispatched more than once: the delivery counters start at zero
-            disp = L.make_dispatch_desc(ctx, hidden_states, routing_weights, reset_counters=True)
+            disp = L.make_dispatch_desc(ctx, hidden_states, routing_weights)
         else:
             disp = None
             L.dispatch_rows(ctx, hidden_states, routing_weights, selected_experts.numel())
