@@ -361,6 +361,7 @@ def run_ours(args, w, name):
     in_ready = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
     copy_events = []            # (kind, start, end) of the timed copies
+    step_marks = []             # per timed step: before / after the wait for inputs, step end
     in_flight = []              # results whose download may still be running
     e2e_state = dict(step=0, primed=False, record=False)
 
@@ -387,7 +388,13 @@ def run_ours(args, w, name):
             upload(slot)
             e2e_state["primed"] = True
         upload(1 - slot)                       # next step's inputs, behind this step's kernels
+        marks = None
+        if e2e_state["record"]:
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            marks[0].record(main)
         main.wait_event(in_ready[slot])
+        if marks:
+            marks[1].record(main)
         buf = stage[slot]
         xx = buf["x"].detach().requires_grad_(True)
         rr = buf["rw"].detach().requires_grad_(True)
@@ -395,6 +402,9 @@ def run_ours(args, w, name):
         consumed[slot].record(main)
         done = torch.cuda.Event()
         done.record(main)
+        if marks:
+            marks[2].record(main)
+            step_marks.append(marks)
         with torch.cuda.stream(copy_out):
             copy_out.wait_event(done)
             ev0 = torch.cuda.Event(enable_timing=True)
@@ -444,6 +454,8 @@ def run_ours(args, w, name):
     copy_ms = {"h2d": 0.0, "d2h": 0.0}
     for kind, ev0, ev1 in copy_events:
         copy_ms[kind] += ev0.elapsed_time(ev1)
+    input_wait_ms = sum(a.elapsed_time(b) for a, b, _ in step_marks) / max(len(step_marks), 1)
+    e2e_compute_ms = sum(b.elapsed_time(c) for _, b, c in step_marks) / max(len(step_marks), 1)
     status = op.context.read_status()
     m_rows = int(op.context.metadata_stats[0].item())
 
@@ -555,7 +567,11 @@ def run_ours(args, w, name):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": round(e2e_ms / args.steps, 3),
                     "h2d_gbs": round(h2d * args.steps / max(copy_ms["h2d"], 1e-6) / 1e6, 1),
-                    "d2h_gbs": round(d2h * args.steps / max(copy_ms["d2h"], 1e-6) / 1e6, 1)},
+                    "d2h_gbs": round(d2h * args.steps / max(copy_ms["d2h"], 1e-6) / 1e6, 1),
+                    # device time of a step's kernels inside the end-to-end loop, and how long
+                    # the compute stream waited for the step's inputs (rank 0)
+                    "kernels_ms_per_step": round(e2e_compute_ms, 3),
+                    "input_wait_ms_per_step": round(input_wait_ms, 3)},
             "gpu_launches": launches_per_step * args.steps,
             "gpu_launches_per_step": launches_per_step,
             "roofline": roofline,
