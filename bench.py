@@ -307,11 +307,17 @@ def run_ours(args, w, name):
     rw.requires_grad_(True)
     gate_up.requires_grad_(True)
     down.requires_grad_(True)
-    host = dict(x=x.detach().cpu().pin_memory(), dy=dy.cpu().pin_memory(),
-                rw=rw.detach().cpu().pin_memory(), sel=sel.cpu().pin_memory())
-    host_out = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
-    host_gh = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
-    host_grw = torch.empty(T, k, dtype=torch.float32).pin_memory()
+    def pinned_copy(t):
+        # straight into pinned memory, without a pageable intermediate (host memory is scarce
+        # when eight ranks share one box)
+        h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+        h.copy_(t.detach())
+        return h
+
+    host = dict(x=pinned_copy(x), dy=pinned_copy(dy), rw=pinned_copy(rw), sel=pinned_copy(sel))
+    host_out = torch.empty(T, H, dtype=torch.bfloat16, pin_memory=True)
+    host_gh = torch.empty(T, H, dtype=torch.bfloat16, pin_memory=True)
+    host_grw = torch.empty(T, k, dtype=torch.float32, pin_memory=True)
     state = __import__("types").SimpleNamespace()
 
     def step(xx, rr, ss, dd):
@@ -447,7 +453,15 @@ def run_ours(args, w, name):
     for _ in range(max(1, min(args.warmup, 2))):
         e2e_step()
     e2e_state["record"] = True
+    e2e_sampler = ClockSampler(local_rank)
+    if rank == 0 and not os.environ.get("MOE_BENCH_NO_CLOCKS"):
+        e2e_sampler.start()
+    e2e_timer = GemmTimer()
+    if not os.environ.get("MOE_BENCH_NO_EVENTS"):
+        L.EVENT_HOOK = e2e_timer
     e2e_ms = timed(e2e_step, args.steps)
+    L.EVENT_HOOK = None
+    e2e_clocks = e2e_sampler.stop() if rank == 0 else None
     e2e_state["record"] = False
     while in_flight:
         in_flight.pop(0)[2].synchronize()
@@ -571,7 +585,10 @@ def run_ours(args, w, name):
                     # device time of a step's kernels inside the end-to-end loop, and how long
                     # the compute stream waited for the step's inputs (rank 0)
                     "kernels_ms_per_step": round(e2e_compute_ms, 3),
-                    "input_wait_ms_per_step": round(input_wait_ms, 3)},
+                    "input_wait_ms_per_step": round(input_wait_ms, 3),
+                    "per_launch_ms": {k_: round(sum(v) / len(v), 3)
+                                      for k_, v in e2e_timer.summary().items()},
+                    "clocks": e2e_clocks},
             "gpu_launches": launches_per_step * args.steps,
             "gpu_launches_per_step": launches_per_step,
             "roofline": roofline,

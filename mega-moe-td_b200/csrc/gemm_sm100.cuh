@@ -364,8 +364,14 @@ __device__ __forceinline__ void dispatch_warp_run(const GemmParams& p, int32_t d
         }
         if (p.disp_weights != nullptr && lane == 0) p.disp_peer_weights[dst_rank][dst_row] = wgt;
       }
-      // every lane's stores must be visible system-wide before the rows are counted
-      __threadfence_system();
+      // Publication of a bucket is a release chain: every lane orders its row stores before
+      // the warp's count at GPU scope (fence + atomic on the counter, which all CTAs of this
+      // GPU share), and the one thread that completes the bucket acquires those counts and
+      // releases the flag at system scope -- a release is cumulative, so the destination's
+      // acquire of the flag also covers the rows counted by the other warps.  Only one
+      // system-scope fence per bucket is issued: such a fence drains everything this GPU has
+      // in flight towards peers and the host, which is slow while host copies are running.
+      __threadfence();
       __syncwarp();
       if (lane == 0) {
 #pragma unroll
