@@ -153,6 +153,29 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int32_t c0, int32_t c1, int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int32_t c0, int32_t c1, int32_t c2, int32_t c3,
+                                            int32_t c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(c3), "r"(c4)
+      : "memory");
+}
+
 // Ask L2 to fetch a box of a 3-D tensor map from DRAM; nothing returns to the SM.
 __device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int32_t c0, int32_t c1,
                                                    int32_t c2) {
@@ -188,6 +211,18 @@ __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorM
       :
       : "r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(leader_bar_addr(bar)), "r"(c0), "r"(c1),
         "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d_pair(void* smem_dst, const CUtensorMap* map,
+                                                 uint64_t* bar, int32_t c0, int32_t c1,
+                                                 int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(leader_bar_addr(bar)), "r"(c0), "r"(c1),
+        "r"(c2), "r"(c3)
       : "memory");
 }
 

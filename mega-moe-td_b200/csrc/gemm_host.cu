@@ -36,10 +36,10 @@ bool encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* di
     set_error("cuTensorMapEncodeTiled is not available from this driver");
     return false;
   }
-  cuuint64_t gdim[3];
-  cuuint64_t gstr[2];
-  cuuint32_t bdim[3];
-  cuuint32_t estr[3] = {1, 1, 1};
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[4];
+  cuuint32_t bdim[5];
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   for (int i = 0; i < rank; ++i) {
     gdim[i] = dims[i];
     bdim[i] = box[i];
@@ -231,6 +231,20 @@ int grouped_rows_gemm(int epi, const mm_gemm_desc& d, GemmParams p, cudaStream_t
     uint64_t str[2] = {(uint64_t)d.b_ld * 2, (uint64_t)d.b_group_stride * 2};
     uint32_t box[3] = {64, (uint32_t)(d.pair ? kBlockN / 2 : kBlockN), 1};  // 128 rows in modes 1, 2
     if (!encode_map(&tmB, d.b, 3, dims, str, box)) return MM_ERR_CUDA;
+  } else if (!skinny && epi == kEpiSwiglu && d.pair == 0 && (d.N % 64) == 0 && b_cols == 2 * d.N) {
+    // fused FC1 on one CTA: gate boxes and up boxes of a tile come with one instruction
+    uint64_t dims[5] = {64, (uint64_t)d.K, (uint64_t)d.N / 64, 2, (uint64_t)d.num_groups};
+    uint64_t str[4] = {(uint64_t)d.b_ld * 2, 128, (uint64_t)d.N * 2,
+                       (uint64_t)d.b_group_stride * 2};
+    uint32_t box[5] = {64, 64, 2, 2, 1};
+    if (!encode_map(&tmB, d.b, 5, dims, str, box)) return MM_ERR_CUDA;
+    p.b_multibox = 2;
+  } else if (!skinny && (b_cols % 64) == 0 && !(epi == kEpiSwiglu && d.pair == 0)) {
+    uint64_t dims[4] = {64, (uint64_t)d.K, (uint64_t)b_cols / 64, (uint64_t)d.num_groups};
+    uint64_t str[3] = {(uint64_t)d.b_ld * 2, 128, (uint64_t)d.b_group_stride * 2};
+    uint32_t box[4] = {64, 64, (uint32_t)(d.pair ? 2 : 4), 1};
+    if (!encode_map(&tmB, d.b, 4, dims, str, box)) return MM_ERR_CUDA;
+    p.b_multibox = 1;
   } else {
     uint64_t dims[3] = {(uint64_t)b_cols, (uint64_t)d.K, (uint64_t)d.num_groups};
     uint64_t str[2] = {(uint64_t)d.b_ld * 2, (uint64_t)d.b_group_stride * 2};
@@ -403,19 +417,31 @@ int mm_grouped_wgrad(const void* grad_out, int64_t ld_go, int32_t Mw, const void
       return MM_ERR_ARG;
     }
   }
-  {
+  GemmParams p{};
+  if ((Mw % 64) == 0) {
+    uint64_t dims[3] = {64, (uint64_t)rows_cap, (uint64_t)Mw / 64};
+    uint64_t str[2] = {(uint64_t)ld_go * 2, 128};
+    uint32_t box[3] = {64, 64, 2};
+    if (!encode_map(&tmA, grad_out, 3, dims, str, box)) return MM_ERR_CUDA;
+    p.a_multibox = 1;
+  } else {
     uint64_t dims[2] = {(uint64_t)Mw, (uint64_t)rows_cap};
     uint64_t str[1] = {(uint64_t)ld_go * 2};
     uint32_t box[2] = {64, 64};
     if (!encode_map(&tmA, grad_out, 2, dims, str, box)) return MM_ERR_CUDA;
   }
-  {
+  if ((Nw % 64) == 0) {
+    uint64_t dims[4] = {64, (uint64_t)rows_cap, (uint64_t)Nw / 64, 1};
+    uint64_t str[3] = {(uint64_t)ld_in * 2, 128, (uint64_t)ld_in * 2 * (uint64_t)rows_cap};
+    uint32_t box[4] = {64, 64, (uint32_t)(pair == 1 ? 2 : 4), 1};
+    if (!encode_map(&tmB, orig_in, 4, dims, str, box)) return MM_ERR_CUDA;
+    p.b_multibox = 1;
+  } else {
     uint64_t dims[3] = {(uint64_t)Nw, (uint64_t)rows_cap, 1};
     uint64_t str[2] = {(uint64_t)ld_in * 2, (uint64_t)ld_in * 2 * (uint64_t)rows_cap};
     uint32_t box[3] = {64, 64, 1};
     if (!encode_map(&tmB, orig_in, 3, dims, str, box)) return MM_ERR_CUDA;
   }
-  GemmParams p{};
   p.kind = kGroupedReduce;
   p.epi = kEpiStore;
   p.num_groups = num_groups;

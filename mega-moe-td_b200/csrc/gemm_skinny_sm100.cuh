@@ -188,58 +188,59 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    int stage = 0;
-    uint32_t phase = 0;
-    uint32_t acc_phase = 0;
-    bool alive = true;
-    const uint32_t w_lbo = p.b_mn ? (uint32_t)kBoxBytes : 16u;
-    const uint32_t w_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
-    for (int32_t t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
-      const SkinnyTile ti = skinny_tile(p, t);
-      if (!mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, p.status, kSiteTmemEmpty, 0)) break;
-      tc_fence_after_sync();
-      const uint32_t idesc = make_idesc_bf16(128, ti.ntok, p.b_mn, 0);
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kSiteSmemFull, stage)) {
-          alive = false;
-          break;
-        }
+    // One lane runs the loop alone: every clock between two MMA issues idles the tensor pipe.
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase = 0;
+      bool alive = true;
+      const uint32_t w_lbo = p.b_mn ? (uint32_t)kBoxBytes : 16u;
+      const uint32_t w_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+      for (int32_t t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
+        const SkinnyTile ti = skinny_tile(p, t);
+        if (!mbar_wait(tmem_empty, acc_phase ^ 1, abort_flag, p.status, kSiteTmemEmpty, 0)) break;
         tc_fence_after_sync();
+        const uint32_t idesc = make_idesc_bf16(128, ti.ntok, p.b_mn, 0);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kSiteSmemFull, stage)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after_sync();
+#ifdef MM_PROFILE
+          if (p.prof_skip_mma) {
+            mbar_arrive(&empty_bar[stage]);
+          } else
+#endif
+          {
+            const uint32_t w_addr = smem_u32(stages + stage * kSkinnyStageBytes);
+            const uint64_t w0_desc = make_smem_desc(w_addr, w_lbo, 1024);
+            const uint64_t w1_desc = make_smem_desc(w_addr + kSkinnyHalfBytes, w_lbo, 1024);
+            const uint64_t x_desc = make_smem_desc(w_addr + 2 * kSkinnyHalfBytes, 16u, 1024);
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+              const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+              umma_f16(tmem_base, w0_desc + (uint64_t)(k * w_kstep), x_desc + (uint64_t)(k * 2),
+                       idesc, accumulate);
+              umma_f16(tmem_base + 256, w1_desc + (uint64_t)(k * w_kstep),
+                       x_desc + (uint64_t)(k * 2), idesc, accumulate);
+            }
+            umma_commit(&empty_bar[stage]);
+          }
+          if (++stage == kSkinnyStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!alive) break;
 #ifdef MM_PROFILE
         if (p.prof_skip_mma) {
-          if (lane == 0) mbar_arrive(&empty_bar[stage]);
+          mbar_arrive(tmem_full);
         } else
 #endif
-        if (lane == 0) {
-          const uint32_t w_addr = smem_u32(stages + stage * kSkinnyStageBytes);
-          const uint64_t w0_desc = make_smem_desc(w_addr, w_lbo, 1024);
-          const uint64_t w1_desc = make_smem_desc(w_addr + kSkinnyHalfBytes, w_lbo, 1024);
-          const uint64_t x_desc = make_smem_desc(w_addr + 2 * kSkinnyHalfBytes, 16u, 1024);
-#pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
-            umma_f16(tmem_base, w0_desc + (uint64_t)(k * w_kstep), x_desc + (uint64_t)(k * 2), idesc,
-                     accumulate);
-            umma_f16(tmem_base + 256, w1_desc + (uint64_t)(k * w_kstep), x_desc + (uint64_t)(k * 2),
-                     idesc, accumulate);
-          }
-          umma_commit(&empty_bar[stage]);
-        }
-        __syncwarp();
-        if (++stage == kSkinnyStages) {
-          stage = 0;
-          phase ^= 1;
-        }
+        umma_commit(tmem_full);
+        acc_phase ^= 1;
       }
-      if (!alive) break;
-#ifdef MM_PROFILE
-      if (p.prof_skip_mma) {
-        if (lane == 0) mbar_arrive(tmem_full);
-      } else
-#endif
-      if (lane == 0) umma_commit(tmem_full);
-      __syncwarp();
-      acc_phase ^= 1;
     }
   } else if (warp >= 2 + kEpiWarps) {
     // ----------------------------- dispatch warps -----------------------------

@@ -65,6 +65,12 @@ struct GemmParams {
   int32_t pair;          // 1: cta_group::2, clusters of two CTAs, 256-row tiles
   int32_t prefetch_kb;   // skinny kernel: k-blocks of weights requested into L2 ahead of the loads
   int32_t unit_walk;     // single-CTA ragged reduction: walk whole units (see TileCursor)
+  // MN-major operands are 64x64 boxes in shared memory.  When the operand's extent allows it
+  // the tensor map carries the box index as an extra dimension, so that one TMA instruction
+  // brings all boxes of a stage (the producer lane is bound by the number of instructions):
+  int32_t a_multibox;    // kGroupedReduce: tmA is {64, rows, Mw / 64}, box {64, 64, 2}
+  int32_t b_multibox;    // 1: tmB is {64, k, cols / 64, groups}, box {64, 64, boxes, 1}
+                         // 2: fused FC1, one CTA: {64, k, F / 64, 2, groups}, box {64, 64, 2, 2, 1}
   int32_t act;
   float act_beta;
   float act_linear_beta; // <= 0: no transform on up
@@ -274,6 +280,19 @@ __device__ __forceinline__ void load2d(bool direct, void* dst, const CUtensorMap
     }
   }
   tma_load_2d(dst, map, bar, c0, c1);
+}
+
+template <bool kPair>
+__device__ __forceinline__ void load4d(bool direct, void* dst, const CUtensorMap* map,
+                                       uint64_t* bar, int32_t c0, int32_t c1, int32_t c2,
+                                       int32_t c3) {
+  if constexpr (kPair) {
+    if (direct) {
+      tma_load_4d_pair(dst, map, bar, c0, c1, c2, c3);
+      return;
+    }
+  }
+  tma_load_4d(dst, map, bar, c0, c1, c2, c3);
 }
 
 template <bool kPair>
@@ -643,8 +662,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if constexpr (!kPair) {
             sB = b_slot(bstage);
             const long long c2 = prof_now();
-            if (load_b && !mbar_wait(&bempty_bar[bstage], bphase ^ 1, abort_flag, p.status,
-                                     kSiteSmemEmpty, 8 + bstage)) {
+            // ragged rows: A and B of a stage are consumed together, one barrier covers both
+            if (p.kind == kGroupedReduce && load_b &&
+                !mbar_wait(&bempty_bar[bstage], bphase ^ 1, abort_flag, p.status, kSiteSmemEmpty,
+                           8 + bstage)) {
               alive = false;
               break;
             }
@@ -670,6 +691,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (!p.b_mn) {
               // K-major weights: one box of 256 (or, per CTA of a pair, 128) output columns
               load3d<kPair>(direct, sB, &tmB, fb, k0, ti.n0 + b_col_off, ti.group);
+            } else if (p.b_multibox == 2) {
+              // fused FC1: the gate boxes and the up boxes of the tile in one instruction
+              tma_load_5d(sB, &tmB, fb, 0, k0, ti.n0 >> 6, 0, ti.group);
+            } else if (p.b_multibox == 1) {
+              int32_t col = ti.n0 + b_col_off;
+              if (p.epi == kEpiSwiglu) col = (cta_rank ? p.swiglu_F : 0) + ti.n0;   // pair: one half
+              load4d<kPair>(direct, sB, &tmB, fb, 0, k0, col >> 6, ti.group);
             } else {
 #pragma unroll
               for (int i = 0; i < b_boxes; ++i) {
@@ -687,11 +715,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           } else {
             const int32_t kr = ti.krow0 + kb * kBlockK;
+            if (p.a_multibox) {
+              load3d<kPair>(direct, sA, &tmA, fb, 0, kr, ti.row0 >> 6);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              load2d<kPair>(direct, sA + i * kBoxBytes, &tmA, fb, ti.row0 + 64 * i, kr);
+              for (int i = 0; i < 2; ++i) {
+                load2d<kPair>(direct, sA + i * kBoxBytes, &tmA, fb, ti.row0 + 64 * i, kr);
+              }
             }
-            if (load_b) {
+            if (load_b && p.b_multibox) {
+              load4d<kPair>(direct, sB, &tmB, fb, 0, kr, (ti.n0 + b_col_off) >> 6, 0);
+            } else if (load_b) {
 #pragma unroll
               for (int i = 0; i < b_boxes; ++i) {
                 const int32_t col = ti.n0 + b_col_off + 64 * i;
@@ -722,6 +756,126 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
     }
+  } else if (!kPair && warp == 1 && p.kind == kGroupedRows) {
+    // ---------------------- MMA issuer, ragged rows, one CTA per tile ----------------------
+    // One lane runs the whole loop: per k-block a wait for the stage, four MMAs and one commit.
+    // tcgen05.mma issue blocks for about the instruction's duration, so every clock spent
+    // between two issues is a clock the tensor pipe idles; the loop carries nothing else.
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      const uint32_t b_lbo = p.b_mn ? (uint32_t)kBoxBytes : 16u;
+      const uint64_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+      const uint32_t stage0 = smem_u32(stages);
+      long long mw_acc = 0, mw_full = 0, mw_issue = 0;
+      const long long m_begin = prof_now();
+      bool alive = true;
+      const int32_t num_kb = (p.K + kBlockK - 1) / kBlockK;
+      for (int32_t t = (int32_t)blockIdx.x; t < ntiles && alive; t += (int32_t)gridDim.x) {
+        const long long c3 = prof_now();
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kSiteTmemEmpty, acc))
+          break;
+        tc_fence_after_sync();
+        mw_acc += prof_now() - c3;
+        const uint32_t d_tmem = tmem_base + acc * kBlockN;
+        for (int32_t kb = 0; kb < num_kb; ++kb) {
+          const long long c4 = prof_now();
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kSiteSmemFull, stage)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const long long c5 = prof_now();
+          mw_full += c5 - c4;
+#ifdef MM_PROFILE
+          if (p.prof_skip_mma) {
+            mbar_arrive(&empty_bar[stage]);
+          } else
+#endif
+          {
+            const uint32_t a_addr = stage0 + stage * kStageBytes;
+            const uint64_t a_desc = make_smem_desc(a_addr, 16u, 1024);
+            const uint64_t b_desc = make_smem_desc(a_addr + kStageABytes, b_lbo, 1024);
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              umma_f16(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)k * b_kstep, p.idesc,
+                       (kb | k) != 0 ? 1u : 0u);
+            umma_commit(&empty_bar[stage]);
+          }
+          mw_issue += prof_now() - c5;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!alive) break;
+#ifdef MM_PROFILE
+        if (p.prof_skip_mma) {
+          mbar_arrive(&tmem_full[acc]);
+        } else
+#endif
+        umma_commit(&tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+      prof_store(p, 3, mw_acc);
+      prof_store(p, 4, mw_full);
+      prof_store(p, 5, 0);
+      prof_store(p, 6, prof_now() - m_begin);
+      prof_store(p, 13, mw_issue);
+      prof_store(p, 14, 0);
+    }
+  } else if (kPair && warp == 1 && p.kind == kGroupedRows) {
+    // ---------------------- MMA issuer, ragged rows, CTA pair per tile ----------------------
+    // The same lean loop on the leader CTA: both CTAs' loads complete on the leader's barrier,
+    // one lane issues the cta_group::2 MMAs, and the multicast commit frees the stage in both
+    // CTAs.  The peer CTA's warp has nothing to do for this problem kind.
+    if constexpr (kPair) {
+      if (leader && lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const uint32_t b_lbo = p.b_mn ? (uint32_t)kBoxBytes : 16u;
+        const uint64_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+        const uint32_t stage0 = smem_u32(stages);
+        bool alive = true;
+        const int32_t num_kb = (p.K + kBlockK - 1) / kBlockK;
+        for (int32_t t = (int32_t)(blockIdx.x >> 1); t < ntiles && alive;
+             t += (int32_t)(gridDim.x >> 1)) {
+          if (!mbar_wait_cluster(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status,
+                                 kSiteTmemEmpty, acc))
+            break;
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + acc * kBlockN;
+          for (int32_t kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kSiteSmemFull, stage)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t a_addr = stage0 + stage * kPairStageBytes;
+            const uint64_t a_desc = make_smem_desc(a_addr, 16u, 1024);
+            const uint64_t b_desc = make_smem_desc(a_addr + kStageABytes, b_lbo, 1024);
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              umma_f16_pair(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)k * b_kstep,
+                            p.idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_commit_pair(&empty_bar[stage]);
+            if (++stage == kPairStages) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          if (!alive) break;
+          umma_commit_pair(&tmem_full[acc]);
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1;
+        }
+      }
+    }
   } else if (warp == 1 || (dual_issue && warp == 3 + kEpiWarps)) {
     // ------------------------------- MMA issuer -------------------------------
     // A single-CTA ragged reduction has two issuing warps (warp 1 and the last warp): tile i of
@@ -748,7 +902,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int unit_b0 = 0;   // first B slot of the resident unit in progress
     long long mw_acc = 0, mw_full = 0, mw_tail = 0, mw_issue = 0, mw_decode = 0;
     const long long m_begin = prof_now();
-    for (TileCursor cur = cursor_begin<kPair>(p, ntiles); cur.t < cur.limit && alive;
+    // Without pairing one lane runs the loop alone (no warp-wide step is needed, and every
+    // clock between two MMA issues idles the tensor pipe); a pair needs the whole warp for the
+    // tail rows and the cluster-scope waits.
+    const bool run_loop = kPair || lane == 0;
+    for (TileCursor cur = cursor_begin<kPair>(p, ntiles); run_loop && cur.t < cur.limit && alive;
          cursor_next(cur, p)) {
       const long long c9 = prof_now();
       const TileInfo ti = cursor_tile(cur, p, cta_rank);
@@ -892,7 +1050,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (release_b) umma_commit(&bempty_bar[bslot]);
           }
         }
-        __syncwarp();
+        if constexpr (kPair) __syncwarp();
         mw_issue += prof_now() - c10;
         if (!resident && ++bstage == nb) bstage = 0;
         if (++stage == na) {
@@ -912,7 +1070,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if constexpr (kPair) umma_commit_pair(&tmem_full[acc]); else umma_commit(&tmem_full[acc]);
         }
       }
-      __syncwarp();
+      if constexpr (kPair) __syncwarp();
       ++seq;
       if (dual_issue) {
         if (mine) acc_phase ^= 1;        // this issuer's buffer is used once per own tile
