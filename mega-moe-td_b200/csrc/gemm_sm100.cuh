@@ -326,11 +326,12 @@ __device__ __forceinline__ void dispatch_warp_run(const GemmParams& p, int32_t d
     }
     const int32_t n_send = *p.disp_num_send;
     const int32_t chunks = p.disp_row_bytes >> 4;
-    constexpr int kRowsPerFence = 4;   // rows pushed between two system-scope fences
-    constexpr int kBatch = 14;         // 16-byte loads in flight per lane
+    constexpr int kRowsPerFence = 4;   // rows pushed between two fences
+    constexpr int kBatch = 14;         // 16-byte chunks per lane and segment (7 KB per warp)
+    const int32_t segs_per_row = (chunks + 32 * kBatch - 1) / (32 * kBatch);
     for (int32_t j0 = gid * kRowsPerFence; j0 < n_send; j0 += nd * kRowsPerFence) {
       // Lanes 0..3 resolve one row each (their dependent table lookups overlap), then the
-      // warp copies the rows one after the other.
+      // warp copies the rows.
       int32_t my_b = -1, my_dst = 0, my_row = 0, my_tok = 0;
       float my_w = 0.0f;
       if ((int32_t)lane < kRowsPerFence && j0 + (int32_t)lane < n_send) {
@@ -351,6 +352,8 @@ __device__ __forceinline__ void dispatch_warp_run(const GemmParams& p, int32_t d
       }
       int32_t bucket_of[kRowsPerFence];
       int32_t dst_of[kRowsPerFence];
+      const uint8_t* src_of[kRowsPerFence];
+      uint8_t* dst_ptr_of[kRowsPerFence];
 #pragma unroll
       for (int r = 0; r < kRowsPerFence; ++r) {
         const int32_t b = __shfl_sync(0xffffffffu, my_b, r);
@@ -360,28 +363,56 @@ __device__ __forceinline__ void dispatch_warp_run(const GemmParams& p, int32_t d
         const float wgt = __shfl_sync(0xffffffffu, my_w, r);
         bucket_of[r] = b;
         dst_of[r] = dst_rank;
-        if (b < 0 || dst_row >= p.disp_capacity) continue;  // overflow: metadata kernel reports
-        const uint8_t* src = p.disp_src + (size_t)tok * p.disp_row_bytes;
-        uint8_t* dst = reinterpret_cast<uint8_t*>(p.disp_peer_rows[dst_rank]) +
-                       (size_t)dst_row * p.disp_row_bytes;
-        for (int32_t c0 = 0; c0 < chunks; c0 += 32 * kBatch) {
-          uint4 v[kBatch];
+        // overflow (the metadata kernel reports it) and rows past the end: nothing to copy
+        const bool live = b >= 0 && dst_row < p.disp_capacity;
+        src_of[r] = live ? p.disp_src + (size_t)tok * p.disp_row_bytes : nullptr;
+        dst_ptr_of[r] = live ? reinterpret_cast<uint8_t*>(p.disp_peer_rows[dst_rank]) +
+                                   (size_t)dst_row * p.disp_row_bytes
+                             : nullptr;
+        if (live && p.disp_weights != nullptr && lane == 0)
+          p.disp_peer_weights[dst_rank][dst_row] = wgt;
+      }
+      // The rows are cut into segments of 32 x kBatch chunks and copied through two register
+      // buffers: the loads of segment s + 1 are in flight while segment s is stored, so the
+      // warp never drains its memory pipeline inside an iteration.
+      const int32_t nseg = kRowsPerFence * segs_per_row;
+      uint4 va[kBatch], vb[kBatch];
+      auto seg_load = [&](int32_t sgm, uint4 (&v)[kBatch]) {
+        const int32_t r = sgm / segs_per_row;
+        const int32_t c0 = (sgm - r * segs_per_row) * 32 * kBatch;
+        const uint8_t* src = src_of[0];
 #pragma unroll
-          for (int k = 0; k < kBatch; ++k) {
-            const int32_t c = c0 + k * 32 + (int32_t)lane;
-            if (c < chunks) {
-              asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(v[k].x), "=r"(v[k].y), "=r"(v[k].z), "=r"(v[k].w)
-                           : "l"(src + (size_t)c * 16));
-            }
-          }
+        for (int q = 1; q < kRowsPerFence; ++q) src = r == q ? src_of[q] : src;
+        if (src == nullptr) return;
 #pragma unroll
-          for (int k = 0; k < kBatch; ++k) {
-            const int32_t c = c0 + k * 32 + (int32_t)lane;
-            if (c < chunks) *reinterpret_cast<uint4*>(dst + (size_t)c * 16) = v[k];
+        for (int k = 0; k < kBatch; ++k) {
+          const int32_t c = c0 + k * 32 + (int32_t)lane;
+          if (c < chunks) {
+            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v[k].x), "=r"(v[k].y), "=r"(v[k].z), "=r"(v[k].w)
+                         : "l"(src + (size_t)c * 16));
           }
         }
-        if (p.disp_weights != nullptr && lane == 0) p.disp_peer_weights[dst_rank][dst_row] = wgt;
+      };
+      auto seg_store = [&](int32_t sgm, const uint4 (&v)[kBatch]) {
+        const int32_t r = sgm / segs_per_row;
+        const int32_t c0 = (sgm - r * segs_per_row) * 32 * kBatch;
+        uint8_t* dst = dst_ptr_of[0];
+#pragma unroll
+        for (int q = 1; q < kRowsPerFence; ++q) dst = r == q ? dst_ptr_of[q] : dst;
+        if (dst == nullptr) return;
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+          const int32_t c = c0 + k * 32 + (int32_t)lane;
+          if (c < chunks) *reinterpret_cast<uint4*>(dst + (size_t)c * 16) = v[k];
+        }
+      };
+      seg_load(0, va);
+      for (int32_t sgm = 0; sgm < nseg; sgm += 2) {
+        if (sgm + 1 < nseg) seg_load(sgm + 1, vb);
+        seg_store(sgm, va);
+        if (sgm + 2 < nseg) seg_load(sgm + 2, va);
+        if (sgm + 1 < nseg) seg_store(sgm + 1, vb);
       }
       // Publication of a bucket is a release chain: every lane orders its row stores before
       // the warp's count at GPU scope (fence + atomic on the counter, which all CTAs of this
