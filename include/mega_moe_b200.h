@@ -117,6 +117,19 @@ int mm_route_local_static(const int32_t* selected, int num_routes, int top_k, in
                           int32_t* send_bucket, int32_t* route_to_send, int32_t* count_row,
                           int32_t* local_stats, cudaStream_t stream);
 
+/* Count exchange (reference: the count publication inside the forward kernel,
+ * kernels/fused_forward.py:158-238; on the host path the all_gather of
+ * runtime/routing.py:164-192).  Stores this rank's count_row [bins] into row `rank` of every
+ * rank's count cube (peer_cubes[d] + cube_offset is rank d's [world, bins] cube), flags it with
+ * `epoch` in peer_flags[d][rank] and waits, bounded, until my_flags[0..world) all carry
+ * `epoch`; afterwards this rank's cube is complete.  `epoch` must grow with every call; two
+ * cubes used alternately (cube_offset) keep a fast rank's next row out of a cube that a slow
+ * rank is still reading.  One small kernel, no host synchronisation. */
+int mm_count_exchange(const int32_t* count_row, int bins, int rank, int world,
+                      int32_t* const* peer_cubes, int64_t cube_offset,
+                      int32_t* const* peer_flags, const int32_t* my_flags, int epoch,
+                      void* status, cudaStream_t stream);
+
 /* Offsets from the replicated count cube [world, bins]
  * (reference: runtime/routing.py:93-140,318-416; kernels/fused_forward.py:241-304,337-358,
  * 450-480).  Also builds the 128-row tile table of the grouped GEMMs (the counterpart of

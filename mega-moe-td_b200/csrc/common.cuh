@@ -37,6 +37,7 @@ enum WaitSite : int32_t {
   kSiteDrain = 6,
   kSiteDispatchFlag = 7,
   kSitePairReady = 8,
+  kSiteCountFlag = 9,
 };
 
 // Wall-clock budget of one device-side wait.

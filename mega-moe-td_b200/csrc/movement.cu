@@ -326,11 +326,65 @@ __global__ void rank_barrier_kernel(int32_t* const* __restrict__ peer_flags, int
   }
 }
 
+// ---------------------------------------------------------------------------------
+// Count exchange: every rank stores its count row into slot `rank` of every rank's count
+// cube (plain peer stores), flags the row with the launch's epoch and waits (bounded) until
+// all `world` rows of its own cube carry that epoch.  One block.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+count_exchange_kernel(const int32_t* __restrict__ count_row, int bins, int rank, int world,
+                      int32_t* const* __restrict__ peer_cubes, int64_t cube_offset,
+                      int32_t* const* __restrict__ peer_flags, const int32_t* my_flags, int epoch,
+                      StatusRecord* status) {
+  for (int i = threadIdx.x; i < world * bins; i += blockDim.x) {
+    const int d = i / bins;
+    const int b = i - d * bins;
+    peer_cubes[d][cube_offset + (int64_t)rank * bins + b] = count_row[b];
+  }
+  // every thread's stores are visible system-wide before the flags that announce the row
+  __threadfence_system();
+  __syncthreads();
+  for (int d = threadIdx.x; d < world; d += blockDim.x) {
+    int32_t* flag = peer_flags[d] + rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+  }
+  for (int s = threadIdx.x; s < world; s += blockDim.x) {
+    const int32_t* mine = my_flags + s;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    int32_t seen;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (seen >= epoch) break;
+      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
+        report_status(status, kWaitTimeout, kSiteCountFlag, s, epoch, seen);
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+}
+
 }  // namespace mm
 
 using namespace mm;
 
 extern "C" {
+
+int mm_count_exchange(const int32_t* count_row, int bins, int rank, int world,
+                      int32_t* const* peer_cubes, int64_t cube_offset,
+                      int32_t* const* peer_flags, const int32_t* my_flags, int epoch,
+                      void* status, cudaStream_t stream) {
+  if (!count_row || !peer_cubes || !peer_flags || !my_flags || bins <= 0 || world <= 0 ||
+      rank < 0 || rank >= world || epoch <= 0 || cube_offset < 0) {
+    set_error("mm_count_exchange: bad arguments");
+    return MM_ERR_ARG;
+  }
+  count_exchange_kernel<<<1, 1024, 0, stream>>>(count_row, bins, rank, world, peer_cubes,
+                                                cube_offset, peer_flags, my_flags, epoch,
+                                                reinterpret_cast<StatusRecord*>(status));
+  return check_launch("count_exchange_kernel");
+}
 
 int mm_dispatch_rows(const void* src, int hidden, const float* weights, const int32_t* send_token,
                      const int32_t* send_route, const int32_t* send_bucket,

@@ -76,6 +76,8 @@ SIGNATURES = {
                                  _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_ptr, C.c_size_t, _c_ptr]),
     "mm_route_local_static": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, _c_i32p,
                                         _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_i32p, _c_ptr]),
+    "mm_count_exchange": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, _c_ptr, C.c_int64, _c_ptr,
+                                    _c_i32p, C.c_int, _c_ptr, _c_ptr]),
     "mm_route_finalize": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int] +
                           [_c_i32p] * 20 + [_c_ptr, _c_ptr]),
     "mm_dispatch_rows": (C.c_int, [_c_ptr, C.c_int, _c_ptr, _c_i32p, _c_i32p, _c_i32p, _c_i32p,

@@ -2,9 +2,11 @@
 
 Counterpart of the reference's ``runtime/routing.py`` (MoERoutingPlan at lines 21-54,
 build_routing_plan at 621-768).  The metadata is produced by CUDA kernels
-(``mm_route_local`` / ``mm_route_finalize``); the per-rank count rows are exchanged with one
-small NCCL all-gather so that every rank holds the whole ``[world, bins]`` count cube, which
-``send_bucket_dst_starts`` needs (it sums *other* sources' counts to a destination).
+(``mm_route_local`` / ``mm_route_finalize``); between them every rank stores its count row
+into all ranks' count cubes (``mm_count_exchange``: peer stores behind an epoch flag, like the
+reference's in-kernel publication, kernels/fused_forward.py:158-238), so that every rank holds
+the whole ``[world, bins]`` count cube, which ``send_bucket_dst_starts`` needs (it sums *other*
+sources' counts to a destination).
 """
 
 from __future__ import annotations
@@ -12,7 +14,6 @@ from __future__ import annotations
 from dataclasses import dataclass
 
 import torch
-import torch.distributed as dist
 
 from .. import _native as N
 from .workspace import MoEForwardContext
@@ -72,11 +73,19 @@ def launch_routing_metadata(context: MoEForwardContext, selected_experts: torch.
         ctx.metadata_local_stats.data_ptr(), ctx.route_scratch.data_ptr(),
         ctx.route_scratch.numel(), stream), "mm_route_local")
     bins = ctx.metadata_num_bins
-    if ctx.world_size > 1:
-        dist.all_gather_into_tensor(ctx.metadata_counts_mem, ctx.metadata_count_row,
-                                    group=ctx.ep_group)
-    else:
-        ctx.metadata_counts_mem[:bins].copy_(ctx.metadata_count_row)
+    # Count exchange: the row goes into every rank's cube by peer stores behind an epoch flag
+    # (no collective library call on the path); two cubes alternate so that a rank that is
+    # already one launch ahead never writes into the cube a slower rank still reads.
+    ctx.count_epoch += 1
+    if ctx.count_epoch >= 2**31 - 1:
+        raise RuntimeError("count-exchange epoch exhausted; recreate the operator")
+    parity = ctx.count_epoch & 1
+    ctx.metadata_counts_mem = ctx.count_cubes[parity]
+    N.check(lib.mm_count_exchange(
+        ctx.metadata_count_row.data_ptr(), bins, ctx.rank, ctx.world_size,
+        ctx.symm.peer_table("count_cubes").data_ptr(), parity * ctx.world_size * bins,
+        ctx.symm.peer_table("count_flags").data_ptr(), ctx.count_flags.data_ptr(),
+        ctx.count_epoch, ctx.status.data_ptr(), stream), "mm_count_exchange")
     N.check(lib.mm_route_finalize(
         ctx.metadata_counts_mem.data_ptr(), ctx.rank, ctx.world_size, ctx.experts_per_rank, bins,
         ctx.max_received_routes,
@@ -92,7 +101,7 @@ def launch_routing_metadata(context: MoEForwardContext, selected_experts: torch.
         ctx.status.data_ptr(), stream),
         "mm_route_finalize")
     timer.__exit__()
-    N.count_launches(5)  # histogram, scan, scatter, offsets, row tables
+    N.count_launches(6)  # histogram, scan, scatter, count exchange, offsets, row tables
 
 
 def check_receive_capacity(context: MoEForwardContext) -> None:

@@ -170,6 +170,9 @@ class MoEForwardContext:
     redispatch_mem: Optional[torch.Tensor] = None
     disp_order_prefix: Optional[torch.Tensor] = None
     disp_bucket_done: Optional[torch.Tensor] = None
+    count_cubes: Optional[torch.Tensor] = None
+    count_flags: Optional[torch.Tensor] = None
+    count_epoch: int = 0
     dispatch_epoch: int = 0
     barrier_epoch: int = 0
     ep_group: object = None
@@ -330,6 +333,9 @@ def create_moe_forward_context(
         "combine_mem": num_routes * hidden_size * 2,
         "combine_gate_mem": num_routes * 2,
         "dispatch_flags": world_size * experts_per_rank * 4,
+        # two count cubes [world, bins] used alternately, and one epoch flag per source rank
+        "count_cubes": 2 * world_size * next_power_of_2(world_size * experts_per_rank) * 4,
+        "count_flags": world_size * 4,
     }
     if saved_recompute_enabled():
         # re-dispatch slab of the recompute backward (reference: kernels/mega_bwd.py:2962-3030):
@@ -350,7 +356,9 @@ def create_moe_forward_context(
     bins = next_power_of_2(num_buckets)
     ctx.metadata_num_bins = bins
     i32 = dict(dtype=torch.int32, device=device)
-    ctx.metadata_counts_mem = torch.zeros(world_size * bins, **i32)
+    ctx.count_cubes = ctx.symm.local("count_cubes", torch.int32).view(2, world_size * bins)
+    ctx.count_flags = ctx.symm.local("count_flags", torch.int32)
+    ctx.metadata_counts_mem = ctx.count_cubes[0]
     ctx.metadata_recv_seg_starts = torch.empty((experts_per_rank, world_size + 1), **i32)
     ctx.metadata_pull_dst_start = torch.empty(experts_per_rank * world_size, **i32)
     ctx.row_token_indices = torch.arange(num_routes, **i32) // top_k
