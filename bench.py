@@ -369,7 +369,7 @@ def run_ours(args, w, name):
     copy_events = []            # (kind, start, end) of the timed copies
     step_marks = []             # per timed step: before / after the wait for inputs, step end
     in_flight = []              # results whose download may still be running
-    e2e_state = dict(step=0, primed=False, record=False)
+    e2e_state = dict(step=0, primed=False, record=False, h2d=True, d2h=True)
 
     def upload(slot):
         with torch.cuda.stream(copy_in):
@@ -377,8 +377,9 @@ def run_ours(args, w, name):
             ev0 = torch.cuda.Event(enable_timing=True)
             ev1 = torch.cuda.Event(enable_timing=True)
             ev0.record(copy_in)
-            for key in ("x", "rw", "sel", "dy"):
-                stage[slot][key].copy_(host[key], non_blocking=True)
+            if e2e_state["h2d"]:
+                for key in ("x", "rw", "sel", "dy"):
+                    stage[slot][key].copy_(host[key], non_blocking=True)
             ev1.record(copy_in)
             in_ready[slot].record(copy_in)
         if e2e_state["record"]:
@@ -416,8 +417,9 @@ def run_ours(args, w, name):
             ev0 = torch.cuda.Event(enable_timing=True)
             ev1 = torch.cuda.Event(enable_timing=True)
             ev0.record(copy_out)
-            host_out.copy_(out.detach(), non_blocking=True)
-            if grads is not None:
+            if e2e_state["d2h"]:
+                host_out.copy_(out.detach(), non_blocking=True)
+            if grads is not None and e2e_state["d2h"]:
                 host_gh.copy_(grads[0], non_blocking=True)
                 host_grw.copy_(grads[1], non_blocking=True)
             ev1.record(copy_out)
@@ -468,7 +470,29 @@ def run_ours(args, w, name):
     copy_ms = {"h2d": 0.0, "d2h": 0.0}
     for kind, ev0, ev1 in copy_events:
         copy_ms[kind] += ev0.elapsed_time(ev1)
+    # MOE_BENCH_E2E_PROBE=1: the same loop with only the uploads, and with only the downloads,
+    # to see which direction of host traffic the step is sensitive to
+    e2e_probe = None
+    if os.environ.get("MOE_BENCH_E2E_PROBE"):
+        e2e_probe = {}
+        for label, h2d_on, d2h_on in (("h2d_only", True, False), ("d2h_only", False, True)):
+            e2e_state.update(h2d=h2d_on, d2h=d2h_on, record=False)
+            e2e_step()
+            probe_timer = GemmTimer()
+            L.EVENT_HOOK = probe_timer
+            ms = timed(e2e_step, args.steps) / args.steps
+            L.EVENT_HOOK = None
+            per = probe_timer.summary()
+            e2e_probe[label] = {"ms_per_step": round(ms, 3),
+                                "fc1_swiglu_ms": round(sum(per["fc1_swiglu"]) / len(per["fc1_swiglu"]), 3)}
+        e2e_state.update(h2d=True, d2h=True)
+        while in_flight:
+            in_flight.pop(0)[2].synchronize()
     input_wait_ms = sum(a.elapsed_time(b) for a, b, _ in step_marks) / max(len(step_marks), 1)
+    waits = torch.tensor([input_wait_ms], device=device)
+    if world > 1:
+        dist.all_reduce(waits, op=dist.ReduceOp.MAX, group=group)
+    input_wait_max_ms = float(waits.item())
     e2e_compute_ms = sum(b.elapsed_time(c) for _, b, c in step_marks) / max(len(step_marks), 1)
     status = op.context.read_status()
     m_rows = int(op.context.metadata_stats[0].item())
@@ -586,6 +610,8 @@ def run_ours(args, w, name):
                     # the compute stream waited for the step's inputs (rank 0)
                     "kernels_ms_per_step": round(e2e_compute_ms, 3),
                     "input_wait_ms_per_step": round(input_wait_ms, 3),
+                    "input_wait_ms_per_step_max_over_ranks": round(input_wait_max_ms, 3),
+                    "probe": e2e_probe,
                     "per_launch_ms": {k_: round(sum(v) / len(v), 3)
                                       for k_, v in e2e_timer.summary().items()},
                     "clocks": e2e_clocks},

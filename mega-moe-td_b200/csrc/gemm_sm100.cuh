@@ -310,137 +310,159 @@ __device__ __forceinline__ void load3d(bool direct, void* dst, const CUtensorMap
 // Body of one dispatch warp of a fused launch: push this rank's send rows into the owning
 // ranks' receive buffers in dispatch order, count delivered rows per (destination, expert)
 // bucket and flag a bucket's arrival at the destination once it is complete.  Never waits.
+//
+// A warp works in batches of kDispatchBatchRows consecutive rows of the dispatch order.  Lane r
+// (r < batch rows) owns row r of the batch: it keeps the row's source and destination
+// pointers, and the warp copies the rows in 7 KB segments through two register buffers, so the
+// loads of one segment are in flight while the previous one is stored.  The lookups of the
+// next batch are issued before the fence of the current one and overlap its draining stores.
+constexpr int kDispatchBatchRows = 8;
+constexpr int kDispatchSegChunks = 14;   // 16-byte chunks per lane and segment
+
+struct DispatchRow {       // held by lane r for row r of a batch
+  const uint8_t* src;      // nullptr: nothing to copy (past the end, or receive overflow)
+  uint8_t* dst;
+  int32_t bucket;          // -1: no row
+  int32_t dst_rank;
+};
+
+// Position of dispatch-order index j: the largest q with order_prefix[q] <= j (empty buckets
+// share their successor's prefix).  All lanes take part; two 32-way steps cover 1024 buckets,
+// a third 32 768.
+__device__ __forceinline__ int32_t dispatch_find_bucket(const int32_t* __restrict__ prefix,
+                                                        int32_t nb, int32_t j, uint32_t lane) {
+  int32_t lo = 0, span = nb;          // the answer lies in [lo, lo + span)
+  while (span > 1) {
+    const int32_t step = (span + 31) >> 5;
+    const int32_t off = (int32_t)lane * step;
+    const bool le = off < span && prefix[lo + off] <= j;
+    const uint32_t m = __ballot_sync(0xffffffffu, le);
+    const int32_t seg = 31 - __clz((int)m);        // lane 0 always qualifies: prefix[lo] <= j
+    lo += seg * step;
+    span = min(step, span - seg * step);
+  }
+  return lo;
+}
+
+__device__ __forceinline__ DispatchRow dispatch_resolve(const GemmParams& p, int32_t j0,
+                                                        int32_t n_send, int32_t nb, uint32_t lane) {
+  DispatchRow row;
+  row.src = nullptr;
+  row.dst = nullptr;
+  row.bucket = -1;
+  row.dst_rank = 0;
+  if (j0 >= n_send) return row;
+  int32_t q = dispatch_find_bucket(p.disp_order_prefix, nb, j0, lane);
+  const int32_t j = j0 + (int32_t)lane;
+  if ((int32_t)lane < kDispatchBatchRows && j < n_send) {
+    // the rows after the first lie in the same bucket or a few buckets further on
+    while (q + 1 < nb && p.disp_order_prefix[q + 1] <= j) ++q;
+    const int32_t b = dispatch_order_bucket(q, p.disp_rank, p.disp_world, p.disp_epr);
+    const int32_t in_bucket = j - p.disp_order_prefix[q];
+    const int32_t i = p.disp_bucket_starts[b] + in_bucket;
+    const int32_t dst_row = p.disp_dst_starts[b] + in_bucket;
+    row.bucket = b;
+    row.dst_rank = b / p.disp_epr;
+    if (dst_row < p.disp_capacity) {     // overflow: the metadata kernel reports it
+      row.src = p.disp_src + (size_t)p.disp_send_token[i] * p.disp_row_bytes;
+      row.dst = reinterpret_cast<uint8_t*>(p.disp_peer_rows[row.dst_rank]) +
+                (size_t)dst_row * p.disp_row_bytes;
+      if (p.disp_weights != nullptr)
+        p.disp_peer_weights[row.dst_rank][dst_row] = p.disp_weights[p.disp_send_route[i]];
+    }
+  }
+  return row;
+}
+
 __device__ __forceinline__ void dispatch_warp_run(const GemmParams& p, int32_t dispatch_warp,
                                                   uint32_t lane) {
-  if (p.disp_src != nullptr) {
-    const int32_t gid = blockIdx.x * kDispatchWarps + dispatch_warp;
-    const int32_t nd = gridDim.x * kDispatchWarps;
-    const int32_t nb = p.disp_world * p.disp_epr;
-    // buckets without rows are complete from the start
-    for (int32_t q = gid * 32 + (int32_t)lane; q < nb; q += nd * 32) {
-      const int32_t b = dispatch_order_bucket(q, p.disp_rank, p.disp_world, p.disp_epr);
-      if (p.disp_counts[b] == 0) {
-        int32_t* flag = p.disp_peer_flags[b / p.disp_epr] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch) : "memory");
+  if (p.disp_src == nullptr) return;
+  const int32_t gid = blockIdx.x * kDispatchWarps + dispatch_warp;
+  const int32_t nd = gridDim.x * kDispatchWarps;
+  const int32_t nb = p.disp_world * p.disp_epr;
+  // buckets without rows are complete from the start
+  for (int32_t q = gid * 32 + (int32_t)lane; q < nb; q += nd * 32) {
+    const int32_t b = dispatch_order_bucket(q, p.disp_rank, p.disp_world, p.disp_epr);
+    if (p.disp_counts[b] == 0) {
+      int32_t* flag = p.disp_peer_flags[b / p.disp_epr] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch) : "memory");
+    }
+  }
+  const int32_t n_send = *p.disp_num_send;
+  const int32_t chunks = p.disp_row_bytes >> 4;
+  constexpr int kBatch = kDispatchSegChunks;
+  const int32_t segs_per_row = (chunks + 32 * kBatch - 1) / (32 * kBatch);
+  const int32_t nseg = kDispatchBatchRows * segs_per_row;
+  const int32_t stride = nd * kDispatchBatchRows;
+  int32_t j0 = gid * kDispatchBatchRows;
+  DispatchRow row = dispatch_resolve(p, j0, n_send, nb, lane);
+  while (j0 < n_send) {
+    uint4 va[kBatch], vb[kBatch];
+    auto seg_load = [&](int32_t sgm, uint4 (&v)[kBatch]) {
+      const int32_t r = sgm / segs_per_row;
+      const int32_t c0 = (sgm - r * segs_per_row) * 32 * kBatch;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(
+          __shfl_sync(0xffffffffu, (unsigned long long)row.src, r));
+      if (src == nullptr) return;
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        const int32_t c = c0 + k * 32 + (int32_t)lane;
+        if (c < chunks) {
+          asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v[k].x), "=r"(v[k].y), "=r"(v[k].z), "=r"(v[k].w)
+                       : "l"(src + (size_t)c * 16));
+        }
+      }
+    };
+    auto seg_store = [&](int32_t sgm, const uint4 (&v)[kBatch]) {
+      const int32_t r = sgm / segs_per_row;
+      const int32_t c0 = (sgm - r * segs_per_row) * 32 * kBatch;
+      uint8_t* dst = reinterpret_cast<uint8_t*>(
+          __shfl_sync(0xffffffffu, (unsigned long long)row.dst, r));
+      if (dst == nullptr) return;
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        const int32_t c = c0 + k * 32 + (int32_t)lane;
+        if (c < chunks) *reinterpret_cast<uint4*>(dst + (size_t)c * 16) = v[k];
+      }
+    };
+    seg_load(0, va);
+    for (int32_t sgm = 0; sgm < nseg; sgm += 2) {
+      if (sgm + 1 < nseg) seg_load(sgm + 1, vb);
+      seg_store(sgm, va);
+      if (sgm + 2 < nseg) seg_load(sgm + 2, va);
+      if (sgm + 1 < nseg) seg_store(sgm + 1, vb);
+    }
+    // the next batch's lookups overlap the draining stores of this one
+    const DispatchRow next = dispatch_resolve(p, j0 + stride, n_send, nb, lane);
+    // Publication of a bucket is a release chain.  Every lane orders its row stores before
+    // the rows are counted at GPU scope (fence, then an acquire-release add on the counter that
+    // all CTAs of this GPU share); the one thread whose add completes the bucket has thereby
+    // acquired every earlier count and releases the flag at system scope.  A release is
+    // cumulative, so the destination's acquire of the flag also covers the rows counted by
+    // the other warps.  Only one system-scope release per bucket is issued: it drains
+    // everything this GPU has in flight towards peers and the host, which is slow while host
+    // copies are running.
+    __threadfence();
+    __syncwarp();
+    if ((int32_t)lane < kDispatchBatchRows && row.bucket >= 0) {
+      const int32_t b = row.bucket;
+      int32_t before;
+      asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;"
+                   : "=r"(before)
+                   : "l"(p.disp_bucket_done + b)
+                   : "memory");
+      if (before + 1 == p.disp_counts[b]) {
+        // the last row of the bucket: leave the counter at zero for the next launch
+        p.disp_bucket_done[b] = 0;
+        int32_t* flag = p.disp_peer_flags[row.dst_rank] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch)
+                     : "memory");
       }
     }
-    const int32_t n_send = *p.disp_num_send;
-    const int32_t chunks = p.disp_row_bytes >> 4;
-    constexpr int kRowsPerFence = 4;   // rows pushed between two fences
-    constexpr int kBatch = 14;         // 16-byte chunks per lane and segment (7 KB per warp)
-    const int32_t segs_per_row = (chunks + 32 * kBatch - 1) / (32 * kBatch);
-    for (int32_t j0 = gid * kRowsPerFence; j0 < n_send; j0 += nd * kRowsPerFence) {
-      // Lanes 0..3 resolve one row each (their dependent table lookups overlap), then the
-      // warp copies the rows.
-      int32_t my_b = -1, my_dst = 0, my_row = 0, my_tok = 0;
-      float my_w = 0.0f;
-      if ((int32_t)lane < kRowsPerFence && j0 + (int32_t)lane < n_send) {
-        const int32_t j = j0 + (int32_t)lane;
-        // largest q with order_prefix[q] <= j (empty buckets share their successor's prefix)
-        int32_t lo = 0, hi = nb;
-        while (hi - lo > 1) {
-          const int32_t mid = (lo + hi) >> 1;
-          if (p.disp_order_prefix[mid] <= j) lo = mid; else hi = mid;
-        }
-        my_b = dispatch_order_bucket(lo, p.disp_rank, p.disp_world, p.disp_epr);
-        const int32_t in_bucket = j - p.disp_order_prefix[lo];
-        const int32_t i = p.disp_bucket_starts[my_b] + in_bucket;
-        my_dst = my_b / p.disp_epr;
-        my_row = p.disp_dst_starts[my_b] + in_bucket;
-        my_tok = p.disp_send_token[i];
-        if (p.disp_weights != nullptr) my_w = p.disp_weights[p.disp_send_route[i]];
-      }
-      int32_t bucket_of[kRowsPerFence];
-      int32_t dst_of[kRowsPerFence];
-      const uint8_t* src_of[kRowsPerFence];
-      uint8_t* dst_ptr_of[kRowsPerFence];
-#pragma unroll
-      for (int r = 0; r < kRowsPerFence; ++r) {
-        const int32_t b = __shfl_sync(0xffffffffu, my_b, r);
-        const int32_t dst_rank = __shfl_sync(0xffffffffu, my_dst, r);
-        const int32_t dst_row = __shfl_sync(0xffffffffu, my_row, r);
-        const int32_t tok = __shfl_sync(0xffffffffu, my_tok, r);
-        const float wgt = __shfl_sync(0xffffffffu, my_w, r);
-        bucket_of[r] = b;
-        dst_of[r] = dst_rank;
-        // overflow (the metadata kernel reports it) and rows past the end: nothing to copy
-        const bool live = b >= 0 && dst_row < p.disp_capacity;
-        src_of[r] = live ? p.disp_src + (size_t)tok * p.disp_row_bytes : nullptr;
-        dst_ptr_of[r] = live ? reinterpret_cast<uint8_t*>(p.disp_peer_rows[dst_rank]) +
-                                   (size_t)dst_row * p.disp_row_bytes
-                             : nullptr;
-        if (live && p.disp_weights != nullptr && lane == 0)
-          p.disp_peer_weights[dst_rank][dst_row] = wgt;
-      }
-      // The rows are cut into segments of 32 x kBatch chunks and copied through two register
-      // buffers: the loads of segment s + 1 are in flight while segment s is stored, so the
-      // warp never drains its memory pipeline inside an iteration.
-      const int32_t nseg = kRowsPerFence * segs_per_row;
-      uint4 va[kBatch], vb[kBatch];
-      auto seg_load = [&](int32_t sgm, uint4 (&v)[kBatch]) {
-        const int32_t r = sgm / segs_per_row;
-        const int32_t c0 = (sgm - r * segs_per_row) * 32 * kBatch;
-        const uint8_t* src = src_of[0];
-#pragma unroll
-        for (int q = 1; q < kRowsPerFence; ++q) src = r == q ? src_of[q] : src;
-        if (src == nullptr) return;
-#pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-          const int32_t c = c0 + k * 32 + (int32_t)lane;
-          if (c < chunks) {
-            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(v[k].x), "=r"(v[k].y), "=r"(v[k].z), "=r"(v[k].w)
-                         : "l"(src + (size_t)c * 16));
-          }
-        }
-      };
-      auto seg_store = [&](int32_t sgm, const uint4 (&v)[kBatch]) {
-        const int32_t r = sgm / segs_per_row;
-        const int32_t c0 = (sgm - r * segs_per_row) * 32 * kBatch;
-        uint8_t* dst = dst_ptr_of[0];
-#pragma unroll
-        for (int q = 1; q < kRowsPerFence; ++q) dst = r == q ? dst_ptr_of[q] : dst;
-        if (dst == nullptr) return;
-#pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-          const int32_t c = c0 + k * 32 + (int32_t)lane;
-          if (c < chunks) *reinterpret_cast<uint4*>(dst + (size_t)c * 16) = v[k];
-        }
-      };
-      seg_load(0, va);
-      for (int32_t sgm = 0; sgm < nseg; sgm += 2) {
-        if (sgm + 1 < nseg) seg_load(sgm + 1, vb);
-        seg_store(sgm, va);
-        if (sgm + 2 < nseg) seg_load(sgm + 2, va);
-        if (sgm + 1 < nseg) seg_store(sgm + 1, vb);
-      }
-      // Publication of a bucket is a release chain: every lane orders its row stores before
-      // the warp's count at GPU scope (fence + atomic on the counter, which all CTAs of this
-      // GPU share), and the one thread that completes the bucket acquires those counts and
-      // releases the flag at system scope -- a release is cumulative, so the destination's
-      // acquire of the flag also covers the rows counted by the other warps.  Only one
-      // system-scope fence per bucket is issued: such a fence drains everything this GPU has
-      // in flight towards peers and the host, which is slow while host copies are running.
-      __threadfence();
-      __syncwarp();
-      if (lane == 0) {
-#pragma unroll
-        for (int r = 0; r < kRowsPerFence; ++r) {
-          const int32_t b = bucket_of[r];
-          if (b < 0) continue;
-          const int32_t done = atomicAdd(&p.disp_bucket_done[b], 1) + 1;
-          if (done == p.disp_counts[b]) {
-            // the last row of the bucket: leave the counter at zero for the next launch
-            p.disp_bucket_done[b] = 0;
-            __threadfence_system();
-            int32_t* flag =
-                p.disp_peer_flags[dst_of[r]] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
-            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch)
-                         : "memory");
-          }
-        }
-      }
-    }
+    __syncwarp();
+    row = next;
+    j0 += stride;
   }
 }
 
