@@ -452,6 +452,8 @@ def run_ours(args, w, name):
     forward_step()
     fwd_ms = timed(forward_step, args.steps) / args.steps
 
+    # MOE_BENCH_NO_E2E=1 (kernel comparisons): one end-to-end step only
+    e2e_steps = 1 if os.environ.get("MOE_BENCH_NO_E2E") else args.steps
     for _ in range(max(1, min(args.warmup, 2))):
         e2e_step()
     e2e_state["record"] = True
@@ -461,7 +463,7 @@ def run_ours(args, w, name):
     e2e_timer = GemmTimer()
     if not os.environ.get("MOE_BENCH_NO_EVENTS"):
         L.EVENT_HOOK = e2e_timer
-    e2e_ms = timed(e2e_step, args.steps)
+    e2e_ms = timed(e2e_step, e2e_steps) * args.steps / e2e_steps
     L.EVENT_HOOK = None
     e2e_clocks = e2e_sampler.stop() if rank == 0 else None
     e2e_state["record"] = False

@@ -640,7 +640,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // single-mode ragged reduction: a stage is free once the issuing warp's MMAs have
       // consumed it and the other issuing warp and the tail warp have passed it, so none of
       // them is ever more than one phase behind the ring
-      mbar_init(&empty_bar[s], (!kPair && p.kind == kGroupedReduce) ? 3 : 1);
+      // (default walk: one issuing warp and the tail warp)
+      mbar_init(&empty_bar[s],
+                (!kPair && p.kind == kGroupedReduce) ? (p.unit_walk != 0 ? 3 : 2) : 1);
       // ready_bar doubles as the single-mode "B half consumed" barrier; a ragged reduction has
       // two MMA-issuing warps and both report on it
       mbar_init(&ready_bar[s], (!kPair && p.kind == kGroupedReduce) ? 2 : 1);
@@ -675,9 +677,151 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int32_t ntiles = total_tiles(p);
   // Single mode tracks the A and B halves of the stage ring separately: a ragged reduction
   // whose group fits the ring keeps B resident over the m-tiles of a unit (see TileCursor).
-  const bool dual_issue = !kPair && p.kind == kGroupedReduce;   // two MMA-issuing warps
+  // A single-CTA ragged reduction comes in two forms.  The unit walk (groups with few rows, B
+  // resident over a unit's tiles) has two MMA-issuing warps and tracks the A and B rings
+  // separately.  The default walk (many rows per group) uses the lean form: one lane loads,
+  // one lane issues, the tail warp clears the rows past a group's end; a stage is [A | B].
+  const bool lean_reduce = !kPair && p.kind == kGroupedReduce && p.unit_walk == 0;
+  const bool dual_issue = !kPair && p.kind == kGroupedReduce && !lean_reduce;
 
-  if (warp == 0) {
+  if (warp == 0 && lean_reduce) {
+    // ------------------- TMA producer, ragged reduction, default walk -------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long pw_empty = 0, pw_issue = 0;
+      const long long p_begin = prof_now();
+      bool alive = true;
+      for (int32_t t = (int32_t)blockIdx.x; t < ntiles && alive; t += (int32_t)gridDim.x) {
+        const TileInfo ti = decode_tile(p, t, 0);
+        for (int kb = 0; kb < ti.num_kb; ++kb) {
+          const long long c1 = prof_now();
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kSiteSmemEmpty, stage)) {
+            alive = false;
+            break;
+          }
+          const long long c8 = prof_now();
+          pw_empty += c8 - c1;
+          uint8_t* sA = stages + stage * kStageBytes;
+          uint8_t* sB = sA + kStageABytes;
+          uint64_t* fb = &full_bar[stage];
+          mbar_arrive_expect_tx(fb, kStageBytes);
+          const int32_t kr = ti.krow0 + kb * kBlockK;
+          if (p.a_multibox) {
+            tma_load_3d(sA, &tmA, fb, 0, kr, ti.row0 >> 6);
+          } else {
+            tma_load_2d(sA, &tmA, fb, ti.row0, kr);
+            tma_load_2d(sA + kBoxBytes, &tmA, fb, ti.row0 + 64, kr);
+          }
+          if (p.b_multibox) {
+            tma_load_4d(sB, &tmB, fb, 0, kr, ti.n0 >> 6, 0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              tma_load_3d(sB + i * kBoxBytes, &tmB, fb, ti.n0 + 64 * i, kr, 0);
+          }
+          pw_issue += prof_now() - c8;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      prof_store(p, 0, pw_empty);
+      prof_store(p, 1, 0);
+      prof_store(p, 2, 0);
+      prof_store(p, 11, pw_issue);
+      prof_store(p, 12, prof_now() - p_begin);
+      if (!alive) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 1000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1 && lean_reduce) {
+    // -------------------- MMA issuer, ragged reduction, default walk --------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      uint32_t fixed_phase = 0;       // per-stage parity of the tail warp's barrier
+      const uint32_t stage0 = smem_u32(stages);
+      long long mw_acc = 0, mw_full = 0, mw_tail = 0, mw_issue = 0;
+      const long long m_begin = prof_now();
+      bool alive = true;
+      for (int32_t t = (int32_t)blockIdx.x; t < ntiles && alive; t += (int32_t)gridDim.x) {
+        const TileInfo ti = decode_tile(p, t, 0);
+        const long long c3 = prof_now();
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kSiteTmemEmpty, acc))
+          break;
+        tc_fence_after_sync();
+        mw_acc += prof_now() - c3;
+        const uint32_t d_tmem = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < ti.num_kb; ++kb) {
+          const int32_t rows_left = ti.kcnt - kb * kBlockK;
+          const bool tail = rows_left < kBlockK;
+          const int ksteps = tail ? (rows_left + kUmmaK - 1) / kUmmaK : kBlockK / kUmmaK;
+          const long long c4 = prof_now();
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kSiteSmemFull, stage)) {
+            alive = false;
+            break;
+          }
+          const long long c5 = prof_now();
+          mw_full += c5 - c4;
+          if (tail) {
+            // the tail warp clears the rows past the group's end as soon as the block lands
+            if (!mbar_wait(&fixed_bar[stage], (fixed_phase >> stage) & 1u, abort_flag, p.status,
+                           kSiteSmemFull, 16 + stage)) {
+              alive = false;
+              break;
+            }
+            fixed_phase ^= 1u << stage;
+            mw_tail += prof_now() - c5;
+          }
+          tc_fence_after_sync();
+          const long long c10 = prof_now();
+#ifdef MM_PROFILE
+          if (p.prof_skip_mma) {
+            mbar_arrive(&empty_bar[stage]);
+          } else
+#endif
+          {
+            const uint32_t a_addr = stage0 + stage * kStageBytes;
+            const uint64_t a_desc = make_smem_desc(a_addr, (uint32_t)kBoxBytes, 1024);
+            const uint64_t b_desc = make_smem_desc(a_addr + kStageABytes, (uint32_t)kBoxBytes, 1024);
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+              if (k >= ksteps) break;
+              umma_f16(d_tmem, a_desc + (uint64_t)(k * (2048 >> 4)),
+                       b_desc + (uint64_t)(k * (2048 >> 4)), p.idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&empty_bar[stage]);
+          }
+          mw_issue += prof_now() - c10;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!alive) break;
+#ifdef MM_PROFILE
+        if (p.prof_skip_mma) {
+          mbar_arrive(&tmem_full[acc]);
+        } else
+#endif
+        umma_commit(&tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+      prof_store(p, 3, mw_acc);
+      prof_store(p, 4, mw_full);
+      prof_store(p, 5, mw_tail);
+      prof_store(p, 6, prof_now() - m_begin);
+      prof_store(p, 13, mw_issue);
+      prof_store(p, 14, 0);
+    }
+  } else if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       int stage = 0;
