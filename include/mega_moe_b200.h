@@ -178,10 +178,11 @@ int mm_dispatch_rows(const void* src, int hidden, const float* weights, const in
 /* out[t] = bf16(sum_j fp32(rows[route_to_send[t*k + j]])) in slot order, -1 skipped
  * (reference: kernels/fused_forward.py:1319-1387).  When gate_in is not null also
  * gate_out[t, j] = gate_in[route_to_send[t*k + j]] (0 for dropped), the routing-weight
- * gradient gather of kernels/combine_fc1_bwd.py:357-394. */
+ * gradient gather of kernels/combine_fc1_bwd.py:357-394; gate_out_f32 (may be null) receives
+ * the same values as fp32, the dtype the router's autograd expects (ops/function.py:207-215). */
 int mm_topk_reduce(const void* rows, int64_t ld_rows, const int32_t* route_to_send, int tokens,
                    int top_k, int hidden, void* out, const void* gate_in, void* gate_out,
-                   cudaStream_t stream);
+                   float* gate_out_f32, cudaStream_t stream);
 
 /* ---- grouped GEMMs (tcgen05 / TMEM) ------------------------------------------------- */
 typedef struct mm_gemm_desc {

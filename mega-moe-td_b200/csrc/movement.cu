@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(kReduceThreads)
 topk_reduce_kernel(const uint8_t* __restrict__ rows, int64_t ld_bytes,
                    const int32_t* __restrict__ route_to_send, int tokens, int top_k, int row_bytes,
                    uint8_t* __restrict__ out, const __nv_bfloat16* __restrict__ gate_in,
-                   __nv_bfloat16* __restrict__ gate_out) {
+                   __nv_bfloat16* __restrict__ gate_out, float* __restrict__ gate_out_f32) {
   __shared__ int32_t idx[kMaxTopK];
   const int chunks = row_bytes >> 4;
   for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
@@ -83,8 +83,11 @@ topk_reduce_kernel(const uint8_t* __restrict__ rows, int64_t ld_bytes,
     if (threadIdx.x < top_k) {
       const int32_t r = route_to_send[(size_t)t * top_k + threadIdx.x];
       idx[threadIdx.x] = r;
-      if (gate_in != nullptr)
-        gate_out[(size_t)t * top_k + threadIdx.x] = r >= 0 ? gate_in[r] : __float2bfloat16(0.0f);
+      if (gate_in != nullptr) {
+        const __nv_bfloat16 g = r >= 0 ? gate_in[r] : __float2bfloat16(0.0f);
+        gate_out[(size_t)t * top_k + threadIdx.x] = g;
+        if (gate_out_f32 != nullptr) gate_out_f32[(size_t)t * top_k + threadIdx.x] = __bfloat162float(g);
+      }
     }
     __syncthreads();
     for (int c = threadIdx.x; c < chunks; c += kReduceThreads) {
@@ -415,7 +418,7 @@ int mm_dispatch_rows(const void* src, int hidden, const float* weights, const in
 
 int mm_topk_reduce(const void* rows, int64_t ld_rows, const int32_t* route_to_send, int tokens,
                    int top_k, int hidden, void* out, const void* gate_in, void* gate_out,
-                   cudaStream_t stream) {
+                   float* gate_out_f32, cudaStream_t stream) {
   if (!rows || !route_to_send || !out || (gate_in && !gate_out)) {
     set_error("mm_topk_reduce: null argument");
     return MM_ERR_ARG;
@@ -431,7 +434,7 @@ int mm_topk_reduce(const void* rows, int64_t ld_rows, const int32_t* route_to_se
   topk_reduce_kernel<<<blocks, kReduceThreads, 0, stream>>>(
       reinterpret_cast<const uint8_t*>(rows), ld_rows * 2, route_to_send, tokens, top_k, hidden * 2,
       reinterpret_cast<uint8_t*>(out), reinterpret_cast<const __nv_bfloat16*>(gate_in),
-      reinterpret_cast<__nv_bfloat16*>(gate_out));
+      reinterpret_cast<__nv_bfloat16*>(gate_out), gate_out_f32);
   return check_launch("topk_reduce_kernel");
 }
 

@@ -84,7 +84,7 @@ SIGNATURES = {
                                    _c_i32p, _c_i32p, C.c_int, C.c_int, C.c_int, _c_ptr, _c_ptr,
                                    _c_ptr]),
     "mm_topk_reduce": (C.c_int, [_c_ptr, C.c_int64, _c_i32p, C.c_int, C.c_int, C.c_int, _c_ptr,
-                                 _c_ptr, _c_ptr, _c_ptr]),
+                                 _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
     "mm_fc1_swiglu": (C.c_int, [C.POINTER(GemmDesc), C.POINTER(DispatchDesc), _c_ptr, C.c_int64,
                                 _c_ptr, C.c_int64, _c_ptr, _c_ptr, C.c_int, C.c_float, C.c_float,
                                 C.c_float, _c_ptr]),

@@ -255,12 +255,14 @@ def grouped_wgrad(ctx, grad_out, orig_in, rows_cap, group_offs, num_groups, out,
     N.count_launches(1)
 
 
-def topk_reduce(rows, route_to_send, tokens, top_k, hidden, out, gate_in=None, gate_out=None):
+def topk_reduce(rows, route_to_send, tokens, top_k, hidden, out, gate_in=None, gate_out=None,
+                gate_out_f32=None):
     _t = _timed("topk_reduce")
     _t.__enter__()
     N.check(N.lib().mm_topk_reduce(
         rows.data_ptr(), rows.stride(0), route_to_send.data_ptr(), tokens, top_k, hidden,
-        out.data_ptr(), N.ptr(gate_in), N.ptr(gate_out), N.stream_ptr()), "mm_topk_reduce")
+        out.data_ptr(), N.ptr(gate_in), N.ptr(gate_out), N.ptr(gate_out_f32), N.stream_ptr()),
+        "mm_topk_reduce")
     _t.__exit__()
     N.count_launches(1)
 

@@ -183,8 +183,11 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
     ctx.rank_wait()
     grad_hidden = torch.empty(tokens, hidden, dtype=dtype, device=device)
     grad_routing_weights = torch.empty(tokens, top_k, dtype=dtype, device=device)
+    # the same values as fp32 for the autograd wrappers (routing weights are fp32 inputs)
+    grad_routing_weights_f32 = torch.empty(tokens, top_k, dtype=torch.float32, device=device)
     L.topk_reduce(ctx.combine_mem, plan.route_to_send, tokens, top_k, hidden, grad_hidden,
-                  gate_in=ctx.combine_gate_mem, gate_out=grad_routing_weights)
+                  gate_in=ctx.combine_gate_mem, gate_out=grad_routing_weights,
+                  gate_out_f32=grad_routing_weights_f32)
 
     grad_fc1_1, grad_fc1_2 = torch.chunk(grad_fc1, 2, dim=1)
     return dict(
@@ -192,6 +195,7 @@ def moe_backward_triton(saved, dy, peer_mem, grad_transport=None, hidden_states=
         grad_fc1_1=grad_fc1_1, grad_fc1_2=grad_fc1_2, grad_fc2=grad_fc2,
         grad_swiglu=grad_swiglu, grad_fc1_output=grad_fc1_output, grad_gate=grad_gate,
         grad_fc2_out_sorted=grad_fc2_out_sorted, grad_fc1=grad_fc1,
+        _grad_routing_weights_f32=grad_routing_weights_f32,
     )
 
 
@@ -232,7 +236,8 @@ class MegaMoEBackwardFunction(torch.autograd.Function):
         grads = moe_backward_triton(ctx.saved, dy, ctx.peer_mem)
         return (
             grads["grad_hidden"],
-            grads["grad_routing_weights"].to(ctx.rw_dtype),
+            (grads["_grad_routing_weights_f32"] if ctx.rw_dtype == torch.float32
+             else grads["grad_routing_weights"].to(ctx.rw_dtype)),
             None,
             grads["grad_fc1_1"],
             grads["grad_fc1_2"],

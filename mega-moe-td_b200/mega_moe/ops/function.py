@@ -76,7 +76,7 @@ class MegaMoEFunction(torch.autograd.Function):
         return (
             None,
             grads["grad_hidden"],
-            grads["grad_routing_weights"].to(torch.float32),
+            grads["_grad_routing_weights_f32"],
             None,
             grad_gate_up,
             grads["grad_fc2"],
