@@ -526,6 +526,29 @@ def run_ours(args, w, name):
     d2h = sum(t.numel() * t.element_size() for t in
               ((host_out,) if forward_only else (host_out, host_gh, host_grw)))
 
+    # Yardstick for the write-dominated launches (the weight gradients at few rows per expert
+    # write 30x what they read): the rate at which this GPU fills memory, measured here with a
+    # plain fill of 2 GB outside every timed region.  A write stream does not reach the copy
+    # peak the roofline fraction is quoted against.
+    write_only_gbs = None
+    try:
+        free_b, _total = torch.cuda.mem_get_info(device)
+        if free_b > (6 << 30):
+            scratch = torch.empty(2 << 30, dtype=torch.uint8, device=device)
+            scratch.fill_(1)
+            torch.cuda.synchronize()
+            w0 = torch.cuda.Event(enable_timing=True)
+            w1 = torch.cuda.Event(enable_timing=True)
+            w0.record()
+            for _ in range(4):
+                scratch.fill_(0)
+            w1.record()
+            torch.cuda.synchronize()
+            write_only_gbs = round(4 * scratch.numel() / (w0.elapsed_time(w1) / 1e3) / 1e9, 1)
+            del scratch
+    except torch.OutOfMemoryError:
+        write_only_gbs = None
+
     # roofline of the dominant kernel (the grouped GEMM, six launches per step)
     peaks = measured_peaks()
     epr = E // world
@@ -559,6 +582,7 @@ def run_ours(args, w, name):
     roofline["kernel"] = "grouped_gemm_kernel / skinny_gemm_kernel (the GEMM launches of a step)"
     roofline["kernel_ms_per_step"] = round(gemm_total_ms, 3)
     roofline["peak_source"] = peaks["source"]
+    roofline["hbm_write_only_gbs_measured_here"] = write_only_gbs
     roofline["per_launch_ms"] = {k_: round(sum(v) / len(v), 3) for k_, v in gemm_ms.items()}
     # north_star's roofline: the slower of the step's FLOPs at the dense bf16 peak and the
     # dispatch + combine bytes that leave a rank at the NVLink rate, against the whole step

@@ -65,8 +65,9 @@ def gemm_tile_mode(ctx=None) -> int:
     ``MOE_GEMM_MODE`` = ``single`` (one CTA per 128x256 tile, cta_group::1), ``pair`` (clusters
     of two CTAs sharing 256-row tiles, cta_group::2; also ``MOE_GEMM_PAIR=1``), ``skinny``
     (transposed product: 256 output columns x up to 256 rows, the rows as the MMA's N extent in
-    steps of 16) or ``auto`` (default): skinny when the expected rows per local expert
-    (tokens x top_k x world / experts) fit one skinny tile, else single.
+    steps of 16), ``auto`` (default): skinny when the expected rows per local expert
+    (tokens x top_k x world / experts) fit one skinny tile, else single, or ``mixed``: auto with
+    CTA pairs for the GEMMs whose weights are K-major.
     """
     import os
     mode = os.environ.get("MOE_GEMM_MODE", "auto").lower()
@@ -76,12 +77,21 @@ def gemm_tile_mode(ctx=None) -> int:
         return TILE_SINGLE
     if mode == "skinny":
         return TILE_SKINNY
-    if mode != "auto":
-        raise ValueError(f"MOE_GEMM_MODE={mode!r} is not one of auto, single, pair, skinny")
+    if mode not in ("auto", "mixed"):
+        raise ValueError(f"MOE_GEMM_MODE={mode!r} is not one of auto, mixed, single, pair, skinny")
     if ctx is None:
         return TILE_SINGLE
     expected = ctx.max_tokens_per_rank * ctx.top_k * ctx.world_size / max(ctx.num_experts, 1)
     return TILE_SKINNY if expected <= SKINNY_MAX_ROWS_PER_EXPERT else TILE_SINGLE
+
+
+def _mixed_tile_mode() -> bool:
+    """``MOE_GEMM_MODE=mixed``: like ``auto``, but CTA pairs for the GEMMs whose weights are
+    K-major (FC2, FC1 input gradient).  Those two launches measured 8-10 % faster at 1170 rows
+    per expert, but under the power cap the other launches of the step slowed by as much, and at
+    292 / 585 rows per expert the pairs lose; so it is not the default."""
+    import os
+    return os.environ.get("MOE_GEMM_MODE", "auto").lower() == "mixed"
 
 
 def pair_mode_enabled() -> bool:
@@ -133,6 +143,10 @@ def make_desc(ctx: MoEForwardContext, a: torch.Tensor, a_rows_cap: int, lda: int
     d.K = k_extent
     d.grid_limit = grid_limit
     d.pair = gemm_tile_mode(ctx)
+    if (d.pair == TILE_SINGLE and b_k_major and _mixed_tile_mode()):
+        # K-major weights (FC2, FC1 input gradient): a CTA pair loads half of the 256-column
+        # weight tile per CTA
+        d.pair = TILE_PAIR
     src = plan if plan is not None else ctx
     d.group_offs = src.metadata_recv_expert_offs.data_ptr()
     if d.pair:
