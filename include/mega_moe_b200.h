@@ -214,13 +214,11 @@ typedef struct mm_gemm_desc {
 
 /* Optional fused dispatch of mm_fc1_swiglu / mm_grouped_gemm: two extra warps of every CTA push
  * this rank's send rows (row i = src[send_token[i]]) into the owning ranks' receive buffers
- * in dispatch order and flag arrival in the destination's `flags` array (st.release.sys of
- * `epoch`); the GEMM waits per expert until all `world` sources have flagged it instead of
- * waiting for a rank barrier (reference: dispatch overlapped with FC1,
- * kernels/dispatch_fc1.py:365-508 and kernels/fused_forward.py:483-534,1106-1158).  One flag
- * covers a group of G consecutive local experts of one source, flag index [source * epr + g],
- * with G = ceil(epr / min(epr, max(1, 128 / world))) on every rank, so that a launch issues at
- * most 128 system-scope releases; up to 128 ranks.  `epoch` must grow with every fused launch. */
+ * in dispatch order, flag each (source, expert) bucket as complete in the destination's
+ * `flags` array (st.release.sys of `epoch`), and the GEMM waits per expert until all `world`
+ * sources have flagged it instead of waiting for a rank barrier
+ * (reference: dispatch overlapped with FC1, kernels/dispatch_fc1.py:365-508 and
+ * kernels/fused_forward.py:483-534,1106-1158).  `epoch` must grow with every fused launch. */
 typedef struct mm_dispatch_desc {
   const void* src;                    /* [tokens, hidden] bf16 rows to send */
   const float* weights;               /* [tokens * top_k] fp32, sent alongside; may be null */

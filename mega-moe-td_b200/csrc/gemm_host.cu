@@ -181,10 +181,6 @@ bool fill_dispatch(const mm_dispatch_desc* x, GemmParams& p) {
     set_error("fused dispatch descriptor is incomplete or inconsistent");
     return false;
   }
-  if (x->world > kMaxFlagGroups) {
-    set_error("fused dispatch supports up to %d ranks (got %d)", kMaxFlagGroups, x->world);
-    return false;
-  }
   p.disp_src = reinterpret_cast<const uint8_t*>(x->src);
   p.disp_row_bytes = x->hidden * 2;
   p.disp_rank = x->rank;

@@ -73,7 +73,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   uint64_t* tmem_empty = tmem_full + 1;            // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-  int32_t* flag_targets = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
@@ -245,8 +244,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
   } else if (warp >= 2 + kEpiWarps) {
     // ----------------------------- dispatch warps -----------------------------
-    dispatch_warp_run(p, (int32_t)(warp - 2 - kEpiWarps), lane,
-                      flag_targets + (warp - 2 - kEpiWarps) * kMaxFlagGroups);
+    dispatch_warp_run(p, (int32_t)(warp - 2 - kEpiWarps), lane);
   } else {
     // -------------------------------- epilogue --------------------------------
     const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read

@@ -41,22 +41,8 @@ constexpr int kStagingPerWarp = 2 * 32 * 128;                     // two 32-row 
 constexpr int kDispatchWarps = 2;                                  // row-push warps of a fused launch
 constexpr int kGemmThreads = 32 * (2 + kEpiWarps + kDispatchWarps);
 constexpr int kTmemCols = 512;
-// Arrival flags of the fused dispatch cover groups of consecutive local experts: at most
-// kMaxFlagGroups (destination, group) pairs per rank, so that a launch issues few system-scope
-// releases.  Each dispatch warp keeps the groups' row totals in shared memory.
-constexpr int kMaxFlagGroups = 128;
-constexpr int kFlagTargetBytes = kDispatchWarps * kMaxFlagGroups * 4;
-constexpr int kGemmSmemBytes = kStages * kStageBytes + kEpiWarps * kStagingPerWarp +
-                               256 /*barriers*/ + kFlagTargetBytes + 1024 /*alignment*/;
-
-// Number of consecutive local experts that share one arrival flag (the same on every rank:
-// it depends on the world size and the experts per rank only).
-__host__ __device__ __forceinline__ int32_t flag_group_size(int32_t world, int32_t epr) {
-  int32_t groups_per_dst = kMaxFlagGroups / world;
-  if (groups_per_dst < 1) groups_per_dst = 1;
-  if (groups_per_dst > epr) groups_per_dst = epr;
-  return (epr + groups_per_dst - 1) / groups_per_dst;
-}
+constexpr int kGemmSmemBytes =
+    kStages * kStageBytes + kEpiWarps * kStagingPerWarp + 256 /*barriers*/ + 1024 /*alignment*/;
 
 enum GemmKind : int32_t { kGroupedRows = 0, kGroupedReduce = 1 };
 enum EpiMode : int32_t { kEpiStore = 0, kEpiSwiglu = 1, kEpiScatter = 2 };
@@ -389,30 +375,19 @@ __device__ __forceinline__ DispatchRow dispatch_resolve(const GemmParams& p, int
 }
 
 __device__ __forceinline__ void dispatch_warp_run(const GemmParams& p, int32_t dispatch_warp,
-                                                  uint32_t lane, int32_t* group_target) {
+                                                  uint32_t lane) {
   if (p.disp_src == nullptr) return;
   const int32_t gid = blockIdx.x * kDispatchWarps + dispatch_warp;
   const int32_t nd = gridDim.x * kDispatchWarps;
   const int32_t nb = p.disp_world * p.disp_epr;
-  // Arrival is flagged per (destination, group of G consecutive local experts).  This warp's
-  // table of the groups' row totals; groups without rows are complete from the start.
-  const int32_t G = flag_group_size(p.disp_world, p.disp_epr);
-  const int32_t groups_per_dst = (p.disp_epr + G - 1) / G;
-  const int32_t ngroups = p.disp_world * groups_per_dst;        // <= kMaxFlagGroups
-  if (ngroups > kMaxFlagGroups) return;                          // excluded by the host
-  for (int32_t i = (int32_t)lane; i < ngroups; i += 32) {
-    const int32_t dst = i / groups_per_dst;
-    const int32_t g = i - dst * groups_per_dst;
-    int32_t total = 0;
-    for (int32_t le = g * G; le < min((g + 1) * G, p.disp_epr); ++le)
-      total += p.disp_counts[dst * p.disp_epr + le];
-    group_target[i] = total;
-    if (total == 0 && i % nd == gid) {
-      int32_t* flag = p.disp_peer_flags[dst] + p.disp_rank * p.disp_epr + g;
+  // buckets without rows are complete from the start
+  for (int32_t q = gid * 32 + (int32_t)lane; q < nb; q += nd * 32) {
+    const int32_t b = dispatch_order_bucket(q, p.disp_rank, p.disp_world, p.disp_epr);
+    if (p.disp_counts[b] == 0) {
+      int32_t* flag = p.disp_peer_flags[b / p.disp_epr] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
       asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch) : "memory");
     }
   }
-  __syncwarp();
   const int32_t n_send = *p.disp_num_send;
   const int32_t chunks = p.disp_row_bytes >> 4;
   constexpr int kBatch = kDispatchSegChunks;
@@ -471,17 +446,16 @@ __device__ __forceinline__ void dispatch_warp_run(const GemmParams& p, int32_t d
     __threadfence();
     __syncwarp();
     if ((int32_t)lane < kDispatchBatchRows && row.bucket >= 0) {
-      const int32_t g = (row.bucket - row.dst_rank * p.disp_epr) / G;
-      const int32_t slot = row.dst_rank * p.disp_epr + g;     // counter and flag index of the group
+      const int32_t b = row.bucket;
       int32_t before;
       asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;"
                    : "=r"(before)
-                   : "l"(p.disp_bucket_done + slot)
+                   : "l"(p.disp_bucket_done + b)
                    : "memory");
-      if (before + 1 == group_target[row.dst_rank * groups_per_dst + g]) {
-        // the last row of the group: leave the counter at zero for the next launch
-        p.disp_bucket_done[slot] = 0;
-        int32_t* flag = p.disp_peer_flags[row.dst_rank] + p.disp_rank * p.disp_epr + g;
+      if (before + 1 == p.disp_counts[b]) {
+        // the last row of the bucket: leave the counter at zero for the next launch
+        p.disp_bucket_done[b] = 0;
+        int32_t* flag = p.disp_peer_flags[row.dst_rank] + p.disp_rank * p.disp_epr + (b % p.disp_epr);
         asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.disp_epoch)
                      : "memory");
       }
@@ -495,10 +469,9 @@ __device__ __forceinline__ void dispatch_warp_run(const GemmParams& p, int32_t d
 // Producer side of a fused launch: wait (bounded) until every source rank has flagged the
 // rows of local expert `group` complete for this launch's epoch, then order the tensor-map
 // (async proxy) reads after the flags just acquired.  False: gave up or the CTA is aborting.
-__device__ __forceinline__ bool wait_expert_arrival(const GemmParams& p, int32_t expert,
+__device__ __forceinline__ bool wait_expert_arrival(const GemmParams& p, int32_t group,
                                                     volatile int* abort_flag) {
   const uint64_t t0 = globaltimer_ns();
-  const int32_t group = expert / flag_group_size(p.disp_world, p.disp_epr);
   for (int32_t src = 0; src < p.disp_world; ++src) {
     const int32_t* flag = p.disp_my_flags + src * p.disp_epr + group;
     uint32_t spins = 0;
@@ -634,8 +607,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* fixed_bar = tmem_empty + 2;              // [kMaxStages] single mode: tail rows cleared
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(fixed_bar + kMaxStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
-  // per dispatch warp: row totals of the arrival-flag groups (fused launches)
-  int32_t* flag_targets = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31;
@@ -1360,8 +1331,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     } else {
       // ----------------------------- dispatch warps -----------------------------
-      dispatch_warp_run(p, (int32_t)(warp - 2 - kEpiWarps), lane,
-                        flag_targets + (warp - 2 - kEpiWarps) * kMaxFlagGroups);
+      dispatch_warp_run(p, (int32_t)(warp - 2 - kEpiWarps), lane);
     }
   } else {
     // -------------------------------- epilogue --------------------------------
