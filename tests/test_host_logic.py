@@ -350,3 +350,40 @@ def test_bench_binds_host_threads_to_the_gpus_cpus(monkeypatch):
     monkeypatch.setenv("MOE_BENCH_NO_AFFINITY", "1")
     assert bench.bind_host_threads_near_gpu(0, nvml=fake, uuid="abc") is None
     assert len(calls) == 1
+
+
+@pytest.mark.parametrize("world,experts,top_k,tokens", [(1, 8, 2, 70), (2, 8, 3, 48), (4, 16, 4, 33)])
+def test_saved_index_section_from_plan_tables(world, experts, top_k, tokens):
+    """The index keys the forward adds to its saved dict are pure functions of the routing
+    tables; on CPU tensors they must equal the oracle's restatement of the reference's
+    enrichment (ops/_single_saved_adapter.py:247-340) for every rank."""
+    import types
+
+    from mega_moe.ops.forward import FusedMoEForward
+    from oracle import moe_oracle as O
+    rng = np.random.default_rng(world * 100 + experts)
+    sels = [rng.integers(0, experts, size=(tokens, top_k)).astype(np.int32) for _ in range(world)]
+    meta = O.routing_metadata(sels, experts)
+    for r in range(world):
+        want = O.saved_contract_tables(meta[r], sels[r], world)
+        m = meta[r]["num_received_routes"]
+        sent = meta[r]["num_sent_routes"]
+        t = lambda a: torch.as_tensor(np.asarray(a).astype(np.int32))
+        plan = types.SimpleNamespace(
+            send_route_indices=t(meta[r]["send_route_indices"]),
+            route_to_send=t(meta[r]["route_to_send"]),
+            row_arrival=t(want["local_sort_idxs"]), arrival_row=t(want["inv_local"]),
+            metadata_recv_counts_re=t(meta[r]["recv_counts_re"]),
+            metadata_count_row=t(meta[r]["count_cube"][r]))
+        op = types.SimpleNamespace(num_experts=experts, world_size=world)
+        got = FusedMoEForward._saved_index_section(op, plan, m, sent, True)
+        for key in ("sort_idxs", "inv_sort", "forward_send_route", "local_sort_idxs", "inv_local",
+                    "meta_expert_ids", "meta_split_cum", "meta_tile_num", "meta_tile_num_cum",
+                    "num_tiles_total"):
+            np.testing.assert_array_equal(got[key].numpy().astype(np.int64),
+                                          np.asarray(want[key]).astype(np.int64), err_msg=key)
+        assert got["splits_send_list"] == want["splits_send_list"]
+        assert got["splits_recv_list"] == want["splits_recv_list"]
+        lazy = FusedMoEForward._saved_index_section(op, plan, m, sent, False)
+        assert lazy["splits_send_list"] is None and lazy["meta_expert_ids"] is None
+        assert torch.equal(lazy["inv_sort"], got["inv_sort"])
