@@ -1,0 +1,181 @@
+"""The numpy oracle of the MoonEP tables against fixtures written by the reference's own host
+code (tests/golden/make_golden_moonep.py) and against the known answers of the reference's
+tests (tests/function/test_moonep_planning.py:57-127, test_balanced_routing.py:69-120)."""
+
+from __future__ import annotations
+
+import hashlib
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import moonep_oracle as M
+
+GOLDEN = Path(__file__).resolve().parent / "golden" / "moonep_tables.npz"
+FIELDS = (
+    "final_order", "send_token_indices", "send_route_indices", "balanced_buckets",
+    "balanced_counts", "send_bucket_starts", "send_bucket_receive_offsets",
+    "receive_counts_by_source_slot", "received_routes_per_slot", "received_slot_offsets",
+)
+
+
+def digest(a: np.ndarray) -> str:
+    a = np.ascontiguousarray(a)
+    return hashlib.sha256(str(a.dtype).encode() + str(a.shape).encode() + a.tobytes()).hexdigest()
+
+
+@pytest.fixture(scope="module")
+def golden():
+    return np.load(GOLDEN)
+
+
+def case_names(golden, routed=None):
+    names = sorted({k.split("/")[0] for k in golden.files})
+    if routed is None:
+        return names
+    return [n for n in names if (f"{n}/selected_0" in golden.files) == routed]
+
+
+def test_fixture_has_planned_and_routed_cases(golden):
+    assert len(case_names(golden, routed=False)) >= 4
+    assert len(case_names(golden, routed=True)) >= 12
+
+
+def test_planning_tables_match_the_reference(golden):
+    for name in case_names(golden):
+        tpe = golden[f"{name}/tpe_all"]
+        plan = M.plan_tables(tpe)
+        assert plan.alloc_cumsum.dtype == np.int32 and plan.experts_to_copy.dtype == np.int32
+        np.testing.assert_array_equal(plan.alloc_cumsum, golden[f"{name}/alloc_cumsum"], name)
+        np.testing.assert_array_equal(plan.experts_to_copy, golden[f"{name}/experts_to_copy"], name)
+        inverse = M.inverse_experts_to_copy(plan.experts_to_copy, tpe.shape[1])
+        np.testing.assert_array_equal(inverse, golden[f"{name}/inverse"], name)
+        assert plan.replica_slot_high_water == int(golden[f"{name}/high_water"])
+        # invariants the reference's tests assert (test_moonep_planning.py:21-54)
+        assert (plan.allocation >= 0).all()
+        np.testing.assert_array_equal(plan.allocation.sum(axis=0), tpe.sum(axis=0))
+        np.testing.assert_array_equal(plan.allocation.sum(axis=1), tpe.sum(axis=1))
+
+
+def test_balanced_routing_tables_match_the_reference(golden):
+    for name in case_names(golden, routed=True):
+        tpe = golden[f"{name}/tpe_all"]
+        full = bool(golden[f"{name}/full"])
+        world = tpe.shape[0]
+        for rank in range(world):
+            got = M.balanced_routing_tables(golden[f"{name}/selected_{rank}"], tpe,
+                                            golden[f"{name}/alloc_cumsum"],
+                                            golden[f"{name}/inverse"], rank)
+            assert got.num_valid_routes == int(golden[f"{name}/r{rank}/num_valid_routes"])
+            for f in FIELDS:
+                want = golden[f"{name}/r{rank}/{f}"]
+                have = getattr(got, f)
+                if full:
+                    assert have.dtype == want.dtype, (name, rank, f)
+                    np.testing.assert_array_equal(have, want, f"{name} r{rank} {f}")
+                else:
+                    assert digest(have) == str(want), (name, rank, f)
+
+
+def test_receive_ranges_tile_the_receive_buffer(golden):
+    """Every receive row is written by exactly one (source, route), rows of one slot are
+    contiguous, and a slot holds only routes of its logical expert."""
+    for name in case_names(golden, routed=True):
+        if not bool(golden[f"{name}/full"]):
+            continue
+        tpe = golden[f"{name}/tpe_all"]
+        world, experts = tpe.shape
+        epr = experts // world
+        etc = golden[f"{name}/experts_to_copy"]
+        tables = [M.balanced_routing_tables(golden[f"{name}/selected_{r}"], tpe,
+                                            golden[f"{name}/alloc_cumsum"],
+                                            golden[f"{name}/inverse"], r) for r in range(world)]
+        rows = M.logical_to_physical_rows(tables)
+        for dest in range(world):
+            offs = tables[dest].received_slot_offsets
+            assert offs[-1] == tpe.sum(axis=1)[0]          # every rank ends at the common capacity
+            for slot in range(2 * epr):
+                logical = dest * epr + slot if slot < epr else int(etc[dest, slot - epr])
+                for src, route in rows[dest][offs[slot]:offs[slot + 1]]:
+                    sel = golden[f"{name}/selected_{src}"].reshape(-1)
+                    assert sel[route] == logical
+
+
+# ---- known answers written out in the reference's tests ---------------------------------
+
+def test_known_answer_balanced_input_stays_home():
+    plan = M.plan_tables(np.array([[2, 2, 0, 0], [0, 0, 2, 2]], np.int32))
+    np.testing.assert_array_equal(plan.alloc_cumsum, [[2, 2], [2, 2], [0, 2], [0, 2]])
+    np.testing.assert_array_equal(plan.experts_to_copy, np.full((2, 2), -1))
+    assert plan.replica_slot_high_water == 0
+
+
+def test_known_answer_hot_expert_is_split():
+    plan = M.plan_tables(np.array([[4, 0, 0, 0], [4, 0, 0, 0]], np.int64))
+    np.testing.assert_array_equal(plan.alloc_cumsum, [[4, 8], [0, 0], [0, 0], [0, 0]])
+    np.testing.assert_array_equal(plan.experts_to_copy, [[-1, -1], [0, -1]])
+    assert plan.replica_slot_high_water == 1
+    inverse = M.inverse_experts_to_copy(plan.experts_to_copy, 4)
+    assert inverse[1, 0] == 0 and (inverse >= 0).sum() == 1
+
+
+def test_known_answer_replica_tie_takes_larger_expert_id():
+    row = [1, 1, 1, 1, 2, 0, 0, 0, 2, 0, 0, 0, 0, 0, 0, 0]
+    plan = M.plan_tables(np.array([row] * 4, np.int32))
+    np.testing.assert_array_equal(plan.experts_to_copy[3], [1, 0, -1, -1])
+    inverse = M.inverse_experts_to_copy(plan.experts_to_copy, 16)
+    assert inverse[3, 1] == 0 and inverse[3, 0] == 1
+
+
+def test_known_answer_hot_expert_routing():
+    selected = [np.zeros((2, 2), np.int32)] * 2
+    tpe = np.array([[4, 0, 0, 0], [4, 0, 0, 0]], np.int32)
+    plan = M.plan_tables(tpe)
+    inverse = M.inverse_experts_to_copy(plan.experts_to_copy, 4)
+    t = [M.balanced_routing_tables(selected[r], tpe, plan.alloc_cumsum, inverse, r) for r in (0, 1)]
+    want_counts = [[4, 0, 0, 0, 0, 0, 0, 0], [0, 0, 0, 0, 0, 0, 4, 0]]
+    for r in (0, 1):
+        np.testing.assert_array_equal(t[r].balanced_counts, want_counts)
+    np.testing.assert_array_equal(t[0].received_routes_per_slot, [4, 0, 0, 0])
+    np.testing.assert_array_equal(t[1].received_routes_per_slot, [0, 0, 4, 0])
+    np.testing.assert_array_equal(t[0].received_slot_offsets, [0, 4, 4, 4, 4])
+    np.testing.assert_array_equal(t[1].received_slot_offsets, [0, 0, 0, 4, 4])
+    np.testing.assert_array_equal(t[0].balanced_buckets, [0, 0, 0, 0])
+    np.testing.assert_array_equal(t[1].balanced_buckets, [6, 6, 6, 6])
+    np.testing.assert_array_equal(t[0].send_bucket_receive_offsets, [0, 4, 4, 4, 0, 0, 0, 4])
+    np.testing.assert_array_equal(t[1].send_bucket_receive_offsets, [4, 4, 4, 4, 0, 0, 0, 4])
+
+
+@pytest.mark.parametrize("tpe, error, message", [
+    (np.zeros((2, 4), np.float32), TypeError, "dtype"),
+    (np.zeros((2, 3), np.int32), ValueError, "divisible"),
+    (np.array([[1, 0, 0, 0], [0, 0, 0, 0]], np.int32), ValueError, "equal route counts"),
+    (np.array([[0, -1], [0, -1]], np.int32), ValueError, "non-negative"),
+    (np.array([[(1 << 31) - 1, 0], [(1 << 31) - 1, 0]], np.int64), ValueError, "global route count"),
+])
+def test_invalid_planner_inputs_are_rejected(tpe, error, message):
+    with pytest.raises(error, match=message):
+        M.plan_tables(tpe)
+
+
+def test_inverse_rejects_home_and_duplicate_experts():
+    with pytest.raises(ValueError, match="remote"):
+        M.inverse_experts_to_copy(np.array([[0, -1], [-1, -1]], np.int32), 4)
+    with pytest.raises(ValueError, match="duplicate"):
+        M.inverse_experts_to_copy(np.array([[2, 2], [-1, -1]], np.int32), 4)
+
+
+def test_random_dropless_counts_keep_routes_and_capacity():
+    rng = np.random.default_rng(20260821)
+    for _ in range(20):
+        routes = rng.integers(0, 16, size=(4, 97))
+        tpe = np.stack([np.bincount(r, minlength=16) for r in routes]).astype(np.int32)
+        plan = M.plan_tables(tpe)
+        np.testing.assert_array_equal(plan.allocation.sum(axis=0), tpe.sum(axis=0))
+        np.testing.assert_array_equal(plan.allocation.sum(axis=1), tpe.sum(axis=1))
+        for dest in range(4):
+            remote = plan.allocation[dest].copy()
+            remote[dest * 4:(dest + 1) * 4] = 0
+            assert set(np.nonzero(remote)[0]) == set(plan.experts_to_copy[dest][
+                plan.experts_to_copy[dest] >= 0])
