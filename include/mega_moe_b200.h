@@ -51,8 +51,9 @@ enum { MM_ACT_SWIGLU = 0, MM_ACT_SITUGLU = 1, MM_ACT_CLAMP_SWIGLU = 2 };
 enum { MM_FC1_BF16 = 0, MM_FC1_FP16 = 1, MM_FC1_FP8 = 2 };
 
 /* Device status record (32 bytes).  code: 0 ok, 1 wait timed out, 2 receive-capacity
- * overflow, 3 bad index.  Mirrors the reference's bounded-spin diagnostic record
- * (kernels/dispatch_fc2_bwd.py:23-42). */
+ * overflow, 3 bad index, 4 the load-balancing planner rejected its input and planned "every
+ * expert stays at home" (site = MM_PLAN_* reason).  Mirrors the reference's bounded-spin
+ * diagnostic record (kernels/dispatch_fc2_bwd.py:23-42). */
 typedef struct mm_status_record {
   int32_t code, site, slot, want, seen, block, pad0, pad1;
 } mm_status_record;
@@ -162,6 +163,91 @@ int mm_route_finalize(const int32_t* count_cube, int rank, int world, int epr, i
                       int32_t* row_src_rank, int32_t* row_src_pos, int32_t* order_prefix,
                       int32_t* bucket_done, int32_t* row_arrival, int32_t* arrival_row,
                       void* status, cudaStream_t stream);
+
+/* ---- MoonEP load-balancing tables ---------------------------------------------------- */
+/* The reference's remedy for skewed routing (runtime/moonep_planning.py, runtime/
+ * balanced_routing.py): routes of an overloaded home rank are executed on under-loaded ranks,
+ * in replica slots that follow the E/R home slots of a rank (2 * E/R physical slots per rank).
+ * These entry points build the integer tables; they sit between mm_count_exchange and
+ * mm_route_finalize, which then runs on the balanced cube with epr = 2 * E/R:
+ *   mm_route_local -> mm_count_exchange -> mm_moonep_plan -> mm_moonep_count_cube
+ *   -> mm_route_finalize(cube, epr = 2 * E/R) -> mm_moonep_map_routes.
+ * Each has a *_host twin that runs the same arithmetic on host memory (all pointers host
+ * pointers, no stream): the counterpart of the reference's host planner, which takes CPU
+ * tensors (runtime/moonep_planning.py:239-276). */
+enum {
+  MM_PLAN_OK = 0,
+  MM_PLAN_BAD_COUNT = 1,      /* a count is negative */
+  MM_PLAN_UNEQUAL_ROWS = 2,   /* source ranks hold different numbers of routes */
+  MM_PLAN_NOT_DROPLESS = 3,   /* a rank's histogram total differs from its unfiltered count */
+  MM_PLAN_TOO_LARGE = 4,      /* an expert's global count or a rank's total exceeds int32 */
+  MM_PLAN_FILL_FAILED = 5,    /* B.1 did not reach zero balances */
+  MM_PLAN_CUT_FAILED = 6,     /* B.2 ran out of routes for a quota */
+  MM_PLAN_REPLICA_BUDGET = 7  /* a rank would need more than E/R replica slots */
+};
+
+/* Planning steps B.0-B.3 (reference: runtime/moonep_planning.py:112-276 on the host,
+ * kernels/moonep_planning.py:365-460 as four launches; here one launch of one CTA).
+ *   counts          [world, stride] routes per (source rank, logical expert); the replicated
+ *                   count cube of mm_count_exchange.  total_bin >= 0 names a column that holds
+ *                   each rank's unfiltered route count (the dropless check of
+ *                   runtime/routing.py:457-481); -1: no such column
+ *   allocation      [world, num_experts] out: routes of expert e executed on rank d
+ *   alloc_cumsum    [num_experts, world] out: inclusive prefix of `allocation` over ranks
+ *   experts_to_copy [world, E/R] out: logical expert in each replica slot, -1 = empty
+ *   inverse         [world, num_experts] out: replica slot of expert e on rank d, -1 = none
+ *   replica_counts  [world] out: remote experts with routes on each rank
+ *   plan_stats      [4] out: {routes per source rank, MM_PLAN_* reason, max of replica_counts, 0}
+ * An input the planner cannot balance (reason != 0) yields the plan that keeps every expert
+ * at home, and status code 4.  world <= 64, num_experts <= 4096 and divisible by world. */
+int mm_moonep_plan(const int32_t* counts, int stride, int world, int num_experts, int total_bin,
+                   int32_t* allocation, int32_t* alloc_cumsum, int32_t* experts_to_copy,
+                   int32_t* inverse, int32_t* replica_counts, int32_t* plan_stats, void* status,
+                   cudaStream_t stream);
+int mm_moonep_plan_host(const int32_t* counts, int stride, int world, int num_experts,
+                        int total_bin, int32_t* allocation, int32_t* alloc_cumsum,
+                        int32_t* experts_to_copy, int32_t* inverse, int32_t* replica_counts,
+                        int32_t* plan_stats);
+
+/* Balanced count cube (reference: runtime/balanced_routing.py:274-315,
+ * kernels/balanced_routing.py `_kernel_build_balanced_count_cube`): cube[s, d * 2 * E/R + p] =
+ * routes source s sends to physical slot p of rank d, every rank computes the whole cube from
+ * the replicated counts and the plan.  Columns from world * 2 * E/R to cube_stride are zeroed.
+ * Also, for this rank: expert_start [num_experts] = first index of each expert in the
+ * expert-major send order of mm_route_local, below [num_experts] = routes of each expert held
+ * by lower ranks.  `cube` must not alias `counts`. */
+int mm_moonep_count_cube(const int32_t* counts, int stride, int rank, int world, int num_experts,
+                         const int32_t* alloc_cumsum, const int32_t* experts_to_copy,
+                         int32_t* cube, int cube_stride, int32_t* expert_start, int32_t* below,
+                         cudaStream_t stream);
+int mm_moonep_count_cube_host(const int32_t* counts, int stride, int rank, int world,
+                              int num_experts, const int32_t* alloc_cumsum,
+                              const int32_t* experts_to_copy, int32_t* cube, int cube_stride,
+                              int32_t* expert_start, int32_t* below);
+
+/* Route placement (reference: runtime/balanced_routing.py:620-720 direct scatter,
+ * kernels/balanced_routing.py `_kernel_map_balanced_routes`): turns the expert-major send
+ * order of mm_route_local (route_in = its send_route, expert_in = its send_bucket, local_stats
+ * = its local_stats) into the bucket-major order over physical slots.  send_bucket_starts
+ * [world * 2 * E/R] comes from mm_route_finalize on the balanced cube.  Outputs (must not alias
+ * the inputs): send_route / send_token / send_bucket [num_routes], bucket = d * 2 * E/R + p;
+ * route_to_send [num_routes] is updated in place for the valid routes.  A route without an
+ * allocation or a slot is skipped and reported as status code 3 (the host twin counts them
+ * in num_misplaced instead). */
+int mm_moonep_map_routes(const int32_t* route_in, const int32_t* expert_in,
+                         const int32_t* local_stats, int num_routes, int top_k, int world,
+                         int num_experts, const int32_t* expert_start, const int32_t* below,
+                         const int32_t* alloc_cumsum, const int32_t* inverse,
+                         const int32_t* send_bucket_starts, int32_t* send_route,
+                         int32_t* send_token, int32_t* send_bucket, int32_t* route_to_send,
+                         void* status, cudaStream_t stream);
+int mm_moonep_map_routes_host(const int32_t* route_in, const int32_t* expert_in, int num_valid,
+                              int num_routes, int top_k, int world, int num_experts,
+                              const int32_t* expert_start, const int32_t* below,
+                              const int32_t* alloc_cumsum, const int32_t* inverse,
+                              const int32_t* send_bucket_starts, int32_t* send_route,
+                              int32_t* send_token, int32_t* send_bucket, int32_t* route_to_send,
+                              int32_t* num_misplaced);
 
 /* ---- dispatch / combine data movement ---------------------------------------------- */
 /* Push send row i (= src[send_token[i]]) to rank send_bucket[i] / epr at row

@@ -20,7 +20,7 @@ CSRC = ROOT / "csrc"
 LIB_DIR = ROOT / "lib"
 LIB_PATH = LIB_DIR / "libmegamoe_sm100.so"
 PROFILE_LIB_PATH = LIB_DIR / "libmegamoe_sm100_prof.so"
-SOURCES = ["abi.cu", "routing.cu", "movement.cu", "gemm_host.cu"]
+SOURCES = ["abi.cu", "routing.cu", "movement.cu", "gemm_host.cu", "moonep.cu"]
 HEADERS = (sorted(p.name for p in CSRC.glob("*.cuh")) + sorted(p.name for p in CSRC.glob("*.h"))
            + ["../../include/mega_moe_b200.h"])
 

@@ -99,6 +99,18 @@ SIGNATURES = {
                                 C.c_int, _c_ptr, C.c_int64, _c_ptr, C.c_int, C.c_float, C.c_float,
                                 C.c_float, _c_i32p, _c_i32p, _c_ptr, C.c_int, _c_ptr, C.c_int,
                                 _c_ptr]),
+    "mm_moonep_plan": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int] + [_c_i32p] * 6 +
+                       [_c_ptr, _c_ptr]),
+    "mm_moonep_plan_host": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int] +
+                            [_c_i32p] * 6),
+    "mm_moonep_count_cube": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, _c_i32p,
+                                       _c_i32p, _c_i32p, C.c_int, _c_i32p, _c_i32p, _c_ptr]),
+    "mm_moonep_count_cube_host": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int, C.c_int, _c_i32p,
+                                            _c_i32p, _c_i32p, C.c_int, _c_i32p, _c_i32p]),
+    "mm_moonep_map_routes": (C.c_int, [_c_i32p, _c_i32p, _c_i32p, C.c_int, C.c_int, C.c_int,
+                                       C.c_int] + [_c_i32p] * 9 + [_c_ptr, _c_ptr]),
+    "mm_moonep_map_routes_host": (C.c_int, [_c_i32p, _c_i32p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                            C.c_int] + [_c_i32p] * 10),
     "mm_router_topk": (C.c_int, [_c_ptr, C.c_int64, C.c_int, C.c_int, C.c_int, _c_i32p, _c_ptr,
                                  _c_ptr]),
     "mm_fc1_save_convert": (C.c_int, [_c_ptr, C.c_int64, C.c_int, _c_i32p, C.c_int, C.c_int,
