@@ -1,0 +1,153 @@
+// Runs CUDA kernel source on the host, one host thread per CUDA thread.  TEST INFRASTRUCTURE ONLY.
+//
+// Enough of the CUDA programming model for small integer kernels: __global__ / __device__ /
+// __shared__, threadIdx / blockIdx, __syncthreads, __syncwarp, __shfl_xor_sync / __shfl_up_sync
+// (all 32 lanes of a warp must take part, block sizes are multiples of 32), atomicMin / atomicCAS
+// on int, __threadfence.  The blocks of a launch run one after another; the threads of a block
+// run concurrently as std::thread, and barriers are real barriers, so a kernel that forgets one
+// can fail here as it can on a GPU.  __shared__ variables become function-local statics, which
+// is what they are while one block runs at a time.  Nothing here models memory spaces, the
+// memory consistency model, occupancy or timing.
+#pragma once
+
+#include <stdint.h>
+
+#include <algorithm>
+#include <condition_variable>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+#define __CUDACC__ 1
+#define __CUDA_ARCH__ 1000
+#define __host__
+#define __device__
+#define __global__
+#define __forceinline__ inline
+#define __launch_bounds__(...)
+#define __shared__ static
+
+namespace cot {
+
+class Barrier {
+ public:
+  explicit Barrier(int n) : n_(n) {}
+  void wait() {
+    std::unique_lock<std::mutex> lock(m_);
+    const unsigned gen = gen_;
+    if (++arrived_ == n_) {
+      arrived_ = 0;
+      ++gen_;
+      cv_.notify_all();
+    } else {
+      cv_.wait(lock, [&] { return gen_ != gen; });
+    }
+  }
+
+ private:
+  std::mutex m_;
+  std::condition_variable cv_;
+  int n_;
+  int arrived_ = 0;
+  unsigned gen_ = 0;
+};
+
+struct Warp {
+  Barrier barrier{32};
+  int64_t slot[32];
+};
+
+struct Block {
+  explicit Block(int threads) : barrier(threads), warps(threads / 32) {
+    for (auto& w : warps) w = new Warp();
+  }
+  ~Block() {
+    for (auto* w : warps) delete w;
+  }
+  Barrier barrier;
+  std::vector<Warp*> warps;
+};
+
+struct Dim3 {
+  int x, y, z;
+};
+
+struct ThreadState {
+  Dim3 thread{0, 0, 0};
+  Dim3 block{0, 0, 0};
+  Block* cta = nullptr;
+};
+
+inline ThreadState& self() {
+  static thread_local ThreadState s;
+  return s;
+}
+
+inline Warp& my_warp() { return *self().cta->warps[self().thread.x / 32]; }
+
+template <class T>
+T shuffle(T v, int from_lane_or_negative) {
+  Warp& w = my_warp();
+  const int lane = self().thread.x & 31;
+  w.slot[lane] = (int64_t)v;
+  w.barrier.wait();
+  const T r = from_lane_or_negative < 0 ? v : (T)w.slot[from_lane_or_negative];
+  w.barrier.wait();
+  return r;
+}
+
+// body() is the kernel call; grid x block threads run it
+template <class Body>
+void launch(int grid, int block, Body body) {
+  for (int b = 0; b < grid; ++b) {
+    Block cta(block);
+    std::vector<std::thread> threads;
+    threads.reserve(block);
+    for (int t = 0; t < block; ++t) {
+      threads.emplace_back([&, t, b] {
+        ThreadState& s = self();
+        s.thread = {t, 0, 0};
+        s.block = {b, 0, 0};
+        s.cta = &cta;
+        body();
+      });
+    }
+    for (auto& th : threads) th.join();
+  }
+}
+
+}  // namespace cot
+
+#define threadIdx (::cot::self().thread)
+#define blockIdx (::cot::self().block)
+
+inline void __syncthreads() { ::cot::self().cta->barrier.wait(); }
+inline void __syncwarp() { ::cot::my_warp().barrier.wait(); }
+inline void __threadfence() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
+
+template <class T>
+T __shfl_xor_sync(unsigned, T v, int lane_mask) {
+  return ::cot::shuffle(v, (::cot::self().thread.x & 31) ^ lane_mask);
+}
+
+template <class T>
+T __shfl_up_sync(unsigned, T v, int delta) {
+  const int lane = ::cot::self().thread.x & 31;
+  return ::cot::shuffle(v, lane >= delta ? lane - delta : -1);
+}
+
+inline int atomicMin(int* p, int v) {
+  int old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
+  while (old > v && !__atomic_compare_exchange_n(p, &old, v, false, __ATOMIC_SEQ_CST,
+                                                 __ATOMIC_SEQ_CST)) {
+  }
+  return old;
+}
+
+inline int atomicCAS(int* p, int compare, int value) {
+  __atomic_compare_exchange_n(p, &compare, value, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST);
+  return compare;
+}
+
+using std::max;
+using std::min;
