@@ -107,46 +107,58 @@ def routing_metadata(selected: list[np.ndarray], num_experts: int):
             valid_route_mask=valid, num_sent_routes=int(send_route.shape[0]),
         ))
     out = []
-    dst_totals = np.array([cube[:, d * epr:(d + 1) * epr].sum() for d in range(world)])
     for r in range(world):
-        row = cube[r, :num_experts]
-        send_bucket_starts = np.cumsum(row) - row
-        dst_starts = np.zeros(num_experts, dtype=np.int64)
-        for d in range(world):
-            block = cube[:, d * epr:(d + 1) * epr]
-            sums = block.sum(0)
-            dst_starts[d * epr:(d + 1) * epr] = (np.cumsum(sums) - sums) + block[:r].sum(0)
-        recv_counts_re = cube[:, r * epr:(r + 1) * epr].copy()            # [W, EPR]
-        recv_per_expert = recv_counts_re.sum(0)
-        recv_expert_offs = np.r_[0, np.cumsum(recv_per_expert)]
-        recv_seg_starts = np.column_stack(
-            (np.zeros(epr, dtype=np.int64), np.cumsum(recv_counts_re.T, axis=1)))  # [EPR, W+1]
-        pull = np.zeros((epr, world), dtype=np.int64)
-        for s in range(world):
-            excl = np.cumsum(cube[s]) - cube[s]
-            pull[:, s] = excl[r * epr:(r + 1) * epr]
-        stats = np.r_[recv_per_expert.sum(), dst_totals.max(), dst_totals]
-        # receive order: expert-major, source-major, then the source's send order
-        row_src_rank = np.zeros(int(recv_per_expert.sum()), dtype=np.int64)
-        row_src_pos = np.zeros_like(row_src_rank)
-        for e in range(epr):
-            for s in range(world):
-                c = recv_counts_re[s, e]
-                start = recv_expert_offs[e] + recv_seg_starts[e, s]
-                row_src_rank[start:start + c] = s
-                row_src_pos[start:start + c] = pull[e, s] + np.arange(c)
         d = dict(local[r])
-        d.update(
-            count_cube=cube.copy(), send_bucket_starts=send_bucket_starts,
-            send_bucket_dst_starts=dst_starts, recv_counts_re=recv_counts_re,
-            recv_per_expert=recv_per_expert, recv_expert_offs=recv_expert_offs,
-            recv_seg_starts=recv_seg_starts, pull_dst_start=pull.reshape(-1), stats=stats,
-            row_src_rank=row_src_rank, row_src_pos=row_src_pos,
-            num_received_routes=int(recv_per_expert.sum()),
-        )
+        d.update(count_cube=cube.copy())
+        d.update(offset_tables_from_cube(cube[:, :num_experts], r, epr))
         out.append({k: (v.astype(np.int32) if isinstance(v, np.ndarray) and v.dtype == np.int64
                         else v) for k, v in d.items()})
     return out
+
+
+def offset_tables_from_cube(cube, r: int, epr: int) -> dict:
+    """Send- and receive-side offset tables of rank ``r`` from the replicated count cube
+    ``cube[source, bucket]`` with ``bucket = dst_rank * epr + slot`` (int64 arrays).  With the
+    logical counts and ``epr = E/R`` these are the tables of runtime/routing.py:93-140; with the
+    MoonEP-balanced cube and ``epr = 2 * E/R`` physical slots they are the balanced tables of
+    runtime/balanced_routing.py:760-783."""
+    cube = np.asarray(cube).astype(np.int64)
+    world = cube.shape[0]
+    num_buckets = world * epr
+    dst_totals = np.array([cube[:, d * epr:(d + 1) * epr].sum() for d in range(world)])
+    row = cube[r, :num_buckets]
+    send_bucket_starts = np.cumsum(row) - row
+    dst_starts = np.zeros(num_buckets, dtype=np.int64)
+    for d in range(world):
+        block = cube[:, d * epr:(d + 1) * epr]
+        sums = block.sum(0)
+        dst_starts[d * epr:(d + 1) * epr] = (np.cumsum(sums) - sums) + block[:r].sum(0)
+    recv_counts_re = cube[:, r * epr:(r + 1) * epr].copy()            # [W, EPR]
+    recv_per_expert = recv_counts_re.sum(0)
+    recv_expert_offs = np.r_[0, np.cumsum(recv_per_expert)]
+    recv_seg_starts = np.column_stack(
+        (np.zeros(epr, dtype=np.int64), np.cumsum(recv_counts_re.T, axis=1)))  # [EPR, W+1]
+    pull = np.zeros((epr, world), dtype=np.int64)
+    for s in range(world):
+        excl = np.cumsum(cube[s]) - cube[s]
+        pull[:, s] = excl[r * epr:(r + 1) * epr]
+    stats = np.r_[recv_per_expert.sum(), dst_totals.max(), dst_totals]
+    # receive order: expert-major, source-major, then the source's send order
+    row_src_rank = np.zeros(int(recv_per_expert.sum()), dtype=np.int64)
+    row_src_pos = np.zeros_like(row_src_rank)
+    for e in range(epr):
+        for s in range(world):
+            c = recv_counts_re[s, e]
+            start = recv_expert_offs[e] + recv_seg_starts[e, s]
+            row_src_rank[start:start + c] = s
+            row_src_pos[start:start + c] = pull[e, s] + np.arange(c)
+    return dict(
+        send_bucket_starts=send_bucket_starts, send_bucket_dst_starts=dst_starts,
+        recv_counts_re=recv_counts_re, recv_per_expert=recv_per_expert,
+        recv_expert_offs=recv_expert_offs, recv_seg_starts=recv_seg_starts,
+        pull_dst_start=pull.reshape(-1), stats=stats, row_src_rank=row_src_rank,
+        row_src_pos=row_src_pos, num_received_routes=int(recv_per_expert.sum()),
+    )
 
 
 SAVED_TILE_ROWS = 64   # BLOCK_SIZE_M of ops/_torch_forward.py:28

@@ -179,3 +179,30 @@ def test_random_dropless_counts_keep_routes_and_capacity():
             remote[dest * 4:(dest + 1) * 4] = 0
             assert set(np.nonzero(remote)[0]) == set(plan.experts_to_copy[dest][
                 plan.experts_to_copy[dest] >= 0])
+
+
+def test_offset_tables_of_the_balanced_cube_are_the_balanced_tables(golden):
+    """The offset formulas of the unbalanced routing, applied to the balanced cube with
+    2 * E/R slots per rank, give the reference's balanced send / receive tables: the device path
+    reuses its offset kernel for MoonEP on the strength of this identity."""
+    from oracle import moe_oracle as O
+
+    pairs = (("send_bucket_starts", "send_bucket_starts"),
+             ("send_bucket_dst_starts", "send_bucket_receive_offsets"),
+             ("recv_counts_re", "receive_counts_by_source_slot"),
+             ("recv_per_expert", "received_routes_per_slot"),
+             ("recv_expert_offs", "received_slot_offsets"))
+    for name in case_names(golden, routed=True):
+        tpe = golden[f"{name}/tpe_all"]
+        world, experts = tpe.shape
+        full = bool(golden[f"{name}/full"])
+        cube = M.balanced_count_cube(tpe, golden[f"{name}/alloc_cumsum"], golden[f"{name}/inverse"])
+        for rank in range(world):
+            t = O.offset_tables_from_cube(cube, rank, 2 * experts // world)
+            for mine, theirs in pairs:
+                have = np.ascontiguousarray(t[mine]).astype(np.int32)
+                want = golden[f"{name}/r{rank}/{theirs}"]
+                if full:
+                    np.testing.assert_array_equal(have, want, f"{name} r{rank} {mine}")
+                else:
+                    assert digest(have) == str(want), (name, rank, mine)
