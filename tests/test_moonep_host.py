@@ -250,3 +250,60 @@ def test_random_plans_agree_with_the_oracle():
             got = plan_moonep_b0_b3(torch.from_numpy(tpe))
             np.testing.assert_array_equal(got.alloc_cumsum.numpy(), want.alloc_cumsum)
             np.testing.assert_array_equal(got.experts_to_copy.numpy(), want.experts_to_copy)
+
+
+def _plans(selected, experts):
+    tpe = torch.stack([torch.bincount(s.reshape(-1)[(s.reshape(-1) >= 0) & (s.reshape(-1) < experts)]
+                                      .long(), minlength=experts).to(torch.int32)
+                       for s in selected]).contiguous()
+    plan = plan_moonep_b0_b3(tpe)
+    inverse = build_inverse_experts_to_copy(plan.experts_to_copy, experts)
+    return tpe, plan, inverse, [build_balanced_routing_metadata(s, tpe, plan.alloc_cumsum, inverse, r)
+                                for r, s in enumerate(selected)]
+
+
+def test_invalid_routes_are_left_out_and_route_ids_keep_their_numbers():
+    # known answer of tests/function/test_balanced_routing.py:120-152
+    selected = [torch.tensor([[0, -1], [4, 0]], dtype=torch.int32),
+                torch.tensor([[0, 0]], dtype=torch.int32)]
+    _, _, _, plans = _plans(selected, 4)
+    assert plans[0].valid_route_mask.tolist() == [True, False, False, True]
+    assert plans[0].final_order.tolist() == [0, 3] and plans[0].final_order.dtype == torch.int64
+    assert plans[0].send_route_indices.tolist() == [0, 3]
+    assert plans[0].send_token_indices.tolist() == [0, 1]
+    assert plans[0].num_valid_routes == 2 and plans[0].num_input_tokens == 2
+
+
+def test_empty_input_gives_empty_tables():
+    selected = [torch.empty((0, 2), dtype=torch.int32)] * 2
+    _, _, _, plans = _plans(selected, 4)
+    for plan in plans:
+        assert plan.num_valid_routes == 0 and plan.final_order.numel() == 0
+        assert plan.balanced_counts.tolist() == [[0] * 8] * 2
+        assert plan.received_slot_offsets.tolist() == [0] * 5
+
+
+def test_send_order_is_bucket_major_and_agrees_with_the_cube():
+    # the invariants of tests/function/test_balanced_routing.py:175-212
+    selected = [torch.tensor([[3, 0], [1, 0], [3, 0], [1, 0]], dtype=torch.int32),
+                torch.tensor([[3, 0], [3, 0], [3, 0], [1, 0]], dtype=torch.int32)]
+    _, _, _, plans = _plans(selected, 4)
+    for plan in plans:
+        assert torch.equal(plan.balanced_counts, plans[0].balanced_counts)
+        assert bool((plan.balanced_buckets[1:] >= plan.balanced_buckets[:-1]).all())
+        assert torch.equal(torch.bincount(plan.balanced_buckets.long(), minlength=8).to(torch.int32),
+                           plan.balanced_counts[plan.rank])
+        assert torch.sort(plan.final_order).values.tolist() == list(range(plan.num_valid_routes))
+        cube = plan.balanced_counts.view(2, 2, 4).long()
+        totals = cube.sum(dim=0)
+        want = (totals.cumsum(dim=1) - totals + cube[:plan.rank].sum(dim=0)).reshape(-1)
+        assert plan.send_bucket_receive_offsets.tolist() == want.tolist()
+
+
+def test_flags_must_be_bools():
+    args = (torch.tensor([[0, 1]], dtype=torch.int32), torch.tensor([[1, 1]], dtype=torch.int32),
+            torch.tensor([[1], [1]], dtype=torch.int32), torch.full((1, 2), -1, dtype=torch.int32))
+    with pytest.raises(TypeError, match="use_direct_bucket_scatter"):
+        build_balanced_routing_metadata(*args, rank=0, use_direct_bucket_scatter=1)
+    plan = build_balanced_routing_metadata(*args, rank=0)
+    assert plan.balanced_buckets.tolist() == [0, 1] and plan.physical_slots_per_rank == 4
