@@ -24,7 +24,7 @@ using namespace mm;
 
 extern "C" {
 
-int mm_abi_version(void) { return 2; }
+int mm_abi_version(void) { return 3; }
 
 const char* mm_last_error(void) { return g_error; }
 
