@@ -341,3 +341,58 @@ def logical_to_physical_rows(tables: list[BalancedTables]) -> list[np.ndarray]:
             raise RuntimeError("a receive row was not written")
         out.append(rows)
     return out
+
+
+def forward_over_physical_slots(hidden, routing_weights, selected, w_gate, w_up, w_down,
+                                num_experts: int, activation: str = "swiglu"):
+    """The MoE forward executed the MoonEP way, all ranks in one process: every route goes to
+    the rank and physical slot the balanced tables name, replica slots compute with a copy of
+    the home rank's weights, rows come back to their source and are summed over the top-k slots
+    in slot order.  Must equal the forward over logical experts (the reference makes the same
+    claim with tests/function/test_moonep_logical_golden.py:21-120).
+
+    ``hidden[r]`` [T, H] bf16, ``routing_weights[r]`` [T, k] fp32, ``selected[r]`` [T, k] int32,
+    ``w_gate[r]`` / ``w_up[r]`` [E/R, F, H] and ``w_down[r]`` [E/R, H, F] bf16 per home rank.
+    Returns (per-rank outputs [T, H] bf16, the per-rank BalancedTables, the PlanTables)."""
+    import torch
+
+    from oracle.moe_oracle import gated_activation
+
+    world = len(hidden)
+    epr = num_experts // world
+    sel_np = [np.asarray(s.cpu().numpy()) for s in selected]
+    tpe = np.stack([np.bincount(s.reshape(-1)[(s.reshape(-1) >= 0) & (s.reshape(-1) < num_experts)]
+                                .astype(np.int64), minlength=num_experts) for s in sel_np])
+    plan = plan_tables(tpe.astype(np.int32))
+    inverse = inverse_experts_to_copy(plan.experts_to_copy, num_experts)
+    tables = [balanced_routing_tables(sel_np[r], tpe, plan.alloc_cumsum, inverse, r)
+              for r in range(world)]
+    rows = logical_to_physical_rows(tables)
+    hid = hidden[0].shape[1]
+    back = [torch.zeros(sel_np[r].size, hid, dtype=torch.bfloat16) for r in range(world)]
+    for dest in range(world):
+        offs = tables[dest].received_slot_offsets
+        for slot in range(2 * epr):
+            part = rows[dest][offs[slot]:offs[slot + 1]]
+            if part.shape[0] == 0:
+                continue
+            expert = dest * epr + slot if slot < epr else int(plan.experts_to_copy[dest, slot - epr])
+            owner, local = divmod(expert, epr)
+            top_k = [sel_np[s].shape[1] for s in part[:, 0]]
+            x = torch.stack([hidden[s][route // k] for (s, route), k in zip(part, top_k)]).float()
+            wts = torch.stack([routing_weights[s].reshape(-1)[route] for s, route in part]).float()
+            gate = (x @ w_gate[owner][local].T.float()).to(torch.bfloat16)
+            up = (x @ w_up[owner][local].T.float()).to(torch.bfloat16)
+            act = (gated_activation(gate, up, activation) * wts[:, None]).to(torch.bfloat16)
+            fc2 = (act.float() @ w_down[owner][local].T.float()).to(torch.bfloat16)
+            for i, (s, route) in enumerate(part):
+                back[s][route] = fc2[i]
+    outs = []
+    for r in range(world):
+        tokens, top_k = sel_np[r].shape
+        routes = back[r].view(tokens, top_k, hid)
+        acc = torch.zeros(tokens, hid, dtype=torch.float32)
+        for j in range(top_k):
+            acc += routes[:, j].float()
+        outs.append(acc.to(torch.bfloat16))
+    return outs, tables, plan

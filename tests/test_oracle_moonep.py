@@ -206,3 +206,28 @@ def test_offset_tables_of_the_balanced_cube_are_the_balanced_tables(golden):
                     np.testing.assert_array_equal(have, want, f"{name} r{rank} {mine}")
                 else:
                     assert digest(have) == str(want), (name, rank, mine)
+
+
+@pytest.mark.parametrize("world, experts, top_k, tokens, zipf", [
+    (2, 8, 3, 24, 1.2), (4, 16, 4, 20, 1.2), (8, 32, 4, 12, 1.5)])
+def test_forward_over_physical_slots_equals_the_logical_forward(world, experts, top_k, tokens, zipf):
+    """Routing every row through the balanced tables and computing replica slots with copies of
+    the home weights gives the same layer output as the forward over logical experts."""
+    import torch
+
+    from oracle import moe_oracle as O
+
+    inp = O.make_inputs(world, tokens, 64, 64, experts, top_k, seed=world,
+                        expert_bias=O.zipf_expert_bias(experts, zipf))
+    want = O.forward_golden(inp["hidden"], inp["routing_weights"], inp["selected"], inp["w_gate"],
+                            inp["w_up"], inp["w_down"], experts)
+    got, tables, plan = M.forward_over_physical_slots(
+        inp["hidden"], inp["routing_weights"], inp["selected"], inp["w_gate"], inp["w_up"],
+        inp["w_down"], experts)
+    assert (plan.experts_to_copy >= 0).any(), "the case must exercise a replica slot"
+    loads = [int(t.received_slot_offsets[-1]) for t in tables]
+    assert len(set(loads)) == 1                      # every rank executes the same number of rows
+    for r in range(world):
+        O_ = want[r].float()
+        diff = (got[r].float() - O_).abs().max().item()
+        assert diff <= O.LAYOUT_ATOL + 2.0 ** -7 * O_.abs().max().item(), (r, diff)
