@@ -249,6 +249,38 @@ int mm_moonep_map_routes_host(const int32_t* route_in, const int32_t* expert_in,
                               int32_t* send_token, int32_t* send_bucket, int32_t* route_to_send,
                               int32_t* num_misplaced);
 
+/* One weight (or weight-gradient) table of the replica transport.  `local` is this rank's
+ * [E/R][bytes] table of its home experts (experts `local_stride` bytes apart); peer[d] is rank
+ * d's replica table [E/R slots][bytes], slots contiguous, in memory every rank can address
+ * (mm_symm_alloc / mm_symm_open).  bytes and local_stride are multiples of 16, pointers 16-byte
+ * aligned. */
+typedef struct mm_replica_table {
+  const void* local;
+  int64_t local_stride;
+  int64_t bytes;
+  void* const* peer; /* device array of `world` pointers */
+} mm_replica_table;
+
+/* Owner-push of replica weights (reference: kernels/replica_weight_prefetch.py:17-180,
+ * runtime/replica_weight_prefetch.py): for every (rank d, slot b) with experts_to_copy[d, b]
+ * owned by `rank`, stores that expert's block of weights0 (and weights1, may be null) into slot
+ * b of rank d's replica table.  Plain peer stores from a persistent grid (grid_limit 0: two
+ * CTAs per SM); no waits.  The destinations may read their slots after a rank barrier that
+ * follows this launch on every rank (mm_rank_barrier). */
+int mm_moonep_push_replicas(const int32_t* experts_to_copy, int rank, int world, int epr,
+                            const mm_replica_table* weights0, const mm_replica_table* weights1,
+                            int grid_limit, cudaStream_t stream);
+
+/* Owner-pull of replica weight gradients (reference: kernels/replica_grad_reduce.py:62-190):
+ * for every home expert of `rank` with copies elsewhere (inverse[d, e] >= 0, d != rank),
+ * grads.local[e] = bf16(fp32(grads.local[e]) + sum over d ascending of fp32(peer[d][slot])),
+ * bf16 elements, one rounding.  The tables of the peers are only read.  All ranks must have
+ * finished writing their replica gradients (a rank barrier before this launch), and must not
+ * overwrite them before every owner has pulled (a rank barrier after it). */
+int mm_moonep_pull_replica_grads(const int32_t* inverse, int rank, int world, int epr,
+                                 const mm_replica_table* grads0, const mm_replica_table* grads1,
+                                 int grid_limit, cudaStream_t stream);
+
 /* ---- dispatch / combine data movement ---------------------------------------------- */
 /* Push send row i (= src[send_token[i]]) to rank send_bucket[i] / epr at row
  * send_bucket_dst_starts[b] + (i - send_bucket_starts[b]) of that rank's receive buffer,

@@ -11,6 +11,8 @@
 //   moonep_map_kernel      one thread per route: expert-major send order -> bucket-major send
 //                          order over the physical slots.
 // mm_route_finalize then runs unchanged on the balanced cube with 2 * E/R slots per rank.
+// Around the balanced GEMMs, moonep_transport.cuh moves replica weights to the ranks that execute
+// them (mm_moonep_push_replicas) and replica weight gradients back (mm_moonep_pull_replica_grads).
 // Reference: src/mega_moe/kernels/moonep_planning.py:365-460 (four launches there),
 // src/mega_moe/kernels/balanced_routing.py and src/mega_moe/runtime/balanced_routing.py:372-541.
 #include <algorithm>
@@ -20,6 +22,7 @@
 #include "internal.h"
 #include "moonep_core.h"
 #include "moonep_kernels.cuh"
+#include "moonep_transport.cuh"
 
 namespace mm {
 namespace {
@@ -45,6 +48,7 @@ int check_plan_sizes(const char* who, int stride, int world, int num_experts, in
 using namespace mm;
 using namespace mm::moonep;
 using namespace mm::moonep_kernels;
+using namespace mm::moonep_transport;
 
 extern "C" {
 
@@ -279,6 +283,82 @@ int mm_moonep_map_routes_host(const int32_t* route_in, const int32_t* expert_in,
   }
   *num_misplaced = bad;
   return MM_OK;
+}
+
+static int make_transport_table(const char* who, const mm_replica_table* in, bool required,
+                                TransportTable* out) {
+  *out = TransportTable{nullptr, 0, 0, nullptr};
+  if (!in) {
+    if (!required) return MM_OK;
+    set_error("%s: the first table is required", who);
+    return MM_ERR_ARG;
+  }
+  if (!in->local || !in->peer || in->bytes <= 0 || in->bytes % 16 != 0 ||
+      in->local_stride < in->bytes || in->local_stride % 16 != 0 ||
+      (reinterpret_cast<uintptr_t>(in->local) & 15) != 0) {
+    set_error("%s: a table needs 16-byte aligned pointers, bytes > 0 and a multiple of 16, "
+              "local_stride >= bytes and a multiple of 16 (bytes=%lld stride=%lld)",
+              who, (long long)in->bytes, (long long)in->local_stride);
+    return MM_ERR_ARG;
+  }
+  *out = TransportTable{in->local, in->local_stride, in->bytes, in->peer};
+  return MM_OK;
+}
+
+static int transport_grid(const char* who, int grid_limit, int* grid) {
+  if (grid_limit > 0) {
+    *grid = grid_limit;
+    return MM_OK;
+  }
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess || sms <= 0) {
+    set_error("%s: %s", who, cudaGetErrorString(e));
+    return MM_ERR_CUDA;
+  }
+  *grid = 2 * sms;
+  return MM_OK;
+}
+
+static int check_transport_sizes(const char* who, const void* table, int rank, int world,
+                                 int epr) {
+  if (!table || world <= 0 || world > kMaxWorld || epr <= 0 || rank < 0 || rank >= world ||
+      (int64_t)world * epr > kMaxListed) {
+    set_error("%s: bad sizes (rank=%d world=%d experts per rank=%d; world * experts per rank "
+              "<= %d)", who, rank, world, epr, kMaxListed);
+    return MM_ERR_ARG;
+  }
+  return MM_OK;
+}
+
+int mm_moonep_push_replicas(const int32_t* experts_to_copy, int rank, int world, int epr,
+                            const mm_replica_table* weights0, const mm_replica_table* weights1,
+                            int grid_limit, cudaStream_t stream) {
+  const char* who = "mm_moonep_push_replicas";
+  if (int rc = check_transport_sizes(who, experts_to_copy, rank, world, epr)) return rc;
+  TransportTable t0, t1;
+  if (int rc = make_transport_table(who, weights0, true, &t0)) return rc;
+  if (int rc = make_transport_table(who, weights1, false, &t1)) return rc;
+  int grid = 0;
+  if (int rc = transport_grid(who, grid_limit, &grid)) return rc;
+  replica_push_kernel<<<grid, kTransportThreads, 0, stream>>>(experts_to_copy, rank, world, epr,
+                                                              t0, t1);
+  return check_launch("replica_push_kernel");
+}
+
+int mm_moonep_pull_replica_grads(const int32_t* inverse, int rank, int world, int epr,
+                                 const mm_replica_table* grads0, const mm_replica_table* grads1,
+                                 int grid_limit, cudaStream_t stream) {
+  const char* who = "mm_moonep_pull_replica_grads";
+  if (int rc = check_transport_sizes(who, inverse, rank, world, epr)) return rc;
+  TransportTable t0, t1;
+  if (int rc = make_transport_table(who, grads0, true, &t0)) return rc;
+  if (int rc = make_transport_table(who, grads1, false, &t1)) return rc;
+  int grid = 0;
+  if (int rc = transport_grid(who, grid_limit, &grid)) return rc;
+  replica_pull_kernel<<<grid, kTransportThreads, 0, stream>>>(inverse, rank, world, epr, t0, t1);
+  return check_launch("replica_pull_kernel");
 }
 
 }  // extern "C"

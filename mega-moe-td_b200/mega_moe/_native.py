@@ -51,6 +51,11 @@ class GemmDesc(C.Structure):
     ]
 
 
+class ReplicaTable(C.Structure):
+    _fields_ = [("local", C.c_void_p), ("local_stride", C.c_int64), ("bytes", C.c_int64),
+                ("peer", C.c_void_p)]
+
+
 class DispatchDesc(C.Structure):
     _fields_ = [(name, C.c_void_p) for name in (
         "src", "weights", "send_token", "send_route", "send_bucket_starts",
@@ -111,6 +116,12 @@ SIGNATURES = {
                                        C.c_int] + [_c_i32p] * 9 + [_c_ptr, _c_ptr]),
     "mm_moonep_map_routes_host": (C.c_int, [_c_i32p, _c_i32p, C.c_int, C.c_int, C.c_int, C.c_int,
                                             C.c_int] + [_c_i32p] * 10),
+    "mm_moonep_push_replicas": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int,
+                                          C.POINTER(ReplicaTable), C.POINTER(ReplicaTable),
+                                          C.c_int, _c_ptr]),
+    "mm_moonep_pull_replica_grads": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int,
+                                               C.POINTER(ReplicaTable), C.POINTER(ReplicaTable),
+                                               C.c_int, _c_ptr]),
     "mm_router_topk": (C.c_int, [_c_ptr, C.c_int64, C.c_int, C.c_int, C.c_int, _c_i32p, _c_ptr,
                                  _c_ptr]),
     "mm_fc1_save_convert": (C.c_int, [_c_ptr, C.c_int64, C.c_int, _c_i32p, C.c_int, C.c_int,

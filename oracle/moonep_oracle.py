@@ -396,3 +396,49 @@ def forward_over_physical_slots(hidden, routing_weights, selected, w_gate, w_up,
             acc += routes[:, j].float()
         outs.append(acc.to(torch.bfloat16))
     return outs, tables, plan
+
+
+def replica_pools(experts_to_copy, home_tables, fill):
+    """Owner-push of replica weights (kernels/replica_weight_prefetch.py:17-180):
+    ``home_tables[r]`` is rank r's ``[E/R, ...]`` array; returns per rank a ``[E/R slots, ...]``
+    array whose slot b holds the home rank's entry of ``experts_to_copy[r, b]`` and ``fill``
+    where the slot is empty."""
+    etc = np.asarray(experts_to_copy)
+    world, epr = etc.shape
+    pools = []
+    for dest in range(world):
+        pool = np.full_like(home_tables[dest], fill)
+        for slot in range(epr):
+            e = int(etc[dest, slot])
+            if e >= 0:
+                pool[slot] = home_tables[e // epr][e % epr]
+        pools.append(pool)
+    return pools
+
+
+def reduced_weight_grads(inverse, home_grads, replica_grads):
+    """Owner-pull of replica weight gradients (kernels/replica_grad_reduce.py:62-190):
+    ``home_grads[r]`` [E/R, n] and ``replica_grads[d]`` [E/R slots, n] are bf16 torch tensors;
+    every home expert's gradient becomes bf16(fp32(home) + sum of its copies' gradients in fp32,
+    peers in ascending rank order)."""
+    import torch
+
+    inverse = np.asarray(inverse)
+    world, experts = inverse.shape
+    epr = experts // world
+    out = []
+    for rank in range(world):
+        g = home_grads[rank].clone()
+        for local in range(epr):
+            acc = None
+            for d in range(world):
+                slot = int(inverse[d, rank * epr + local])
+                if d == rank or slot < 0:
+                    continue
+                if acc is None:
+                    acc = home_grads[rank][local].float()
+                acc = acc + replica_grads[d][slot].float()
+            if acc is not None:
+                g[local] = acc.to(torch.bfloat16)
+        out.append(g)
+    return out

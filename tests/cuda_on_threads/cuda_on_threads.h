@@ -3,7 +3,8 @@
 // Enough of the CUDA programming model for small integer kernels: __global__ / __device__ /
 // __shared__, threadIdx / blockIdx, __syncthreads, __syncwarp, __shfl_xor_sync / __shfl_up_sync
 // (all 32 lanes of a warp must take part, block sizes are multiples of 32), atomicMin / atomicCAS
-// on int, __threadfence.  The blocks of a launch run one after another; the threads of a block
+// on int, __threadfence, uint4, __ldg, __uint_as_float / __float_as_uint, gridDim / blockDim.
+// The blocks of a launch run one after another; the threads of a block
 // run concurrently as std::thread, and barriers are real barriers, so a kernel that forgets one
 // can fail here as it can on a GPU.  __shared__ variables become function-local statics, which
 // is what they are while one block runs at a time.  Nothing here models memory spaces, the
@@ -11,6 +12,8 @@
 #pragma once
 
 #include <stdint.h>
+
+#include <string.h>
 
 #include <algorithm>
 #include <condition_variable>
@@ -75,6 +78,8 @@ struct Dim3 {
 struct ThreadState {
   Dim3 thread{0, 0, 0};
   Dim3 block{0, 0, 0};
+  Dim3 grid{1, 1, 1};
+  Dim3 block_dim{1, 1, 1};
   Block* cta = nullptr;
 };
 
@@ -108,6 +113,8 @@ void launch(int grid, int block, Body body) {
         ThreadState& s = self();
         s.thread = {t, 0, 0};
         s.block = {b, 0, 0};
+        s.grid = {grid, 1, 1};
+        s.block_dim = {block, 1, 1};
         s.cta = &cta;
         body();
       });
@@ -120,6 +127,29 @@ void launch(int grid, int block, Body body) {
 
 #define threadIdx (::cot::self().thread)
 #define blockIdx (::cot::self().block)
+#define gridDim (::cot::self().grid)
+#define blockDim (::cot::self().block_dim)
+
+struct alignas(16) uint4 {
+  unsigned x, y, z, w;
+};
+
+template <class T>
+T __ldg(const T* p) {
+  return *p;
+}
+
+inline float __uint_as_float(unsigned u) {
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+inline unsigned __float_as_uint(float f) {
+  unsigned u;
+  memcpy(&u, &f, 4);
+  return u;
+}
 
 inline void __syncthreads() { ::cot::self().cta->barrier.wait(); }
 inline void __syncwarp() { ::cot::my_warp().barrier.wait(); }

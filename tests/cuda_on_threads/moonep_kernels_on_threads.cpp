@@ -26,9 +26,11 @@ inline void report_status(StatusRecord* st, int32_t code, int32_t site, int32_t 
 }  // namespace mm
 
 #include "moonep_kernels.cuh"
+#include "moonep_transport.cuh"
 
 using namespace mm;
 using namespace mm::moonep_kernels;
+using namespace mm::moonep_transport;
 
 extern "C" {
 
@@ -67,6 +69,27 @@ void cot_moonep_map_routes(const int32_t* route_in, const int32_t* expert_in,
                       expert_start, below, alloc_cumsum, inverse, send_bucket_starts, send_route,
                       send_token, send_bucket, route_to_send, static_cast<StatusRecord*>(status));
   });
+}
+
+// tables: local pointer, bytes between local experts, bytes per expert, array of `world` pointers
+void cot_moonep_push_replicas(const int32_t* experts_to_copy, int rank, int world, int epr,
+                              const void* local0, int64_t stride0, int64_t bytes0,
+                              void* const* peer0, const void* local1, int64_t stride1,
+                              int64_t bytes1, void* const* peer1, int grid) {
+  const TransportTable t0 = {local0, stride0, bytes0, peer0};
+  const TransportTable t1 = {local1, stride1, bytes1, peer1};
+  cot::launch(grid, kTransportThreads,
+              [=] { replica_push_kernel(experts_to_copy, rank, world, epr, t0, t1); });
+}
+
+void cot_moonep_pull_replica_grads(const int32_t* inverse, int rank, int world, int epr,
+                                   void* local0, int64_t stride0, int64_t bytes0,
+                                   void* const* peer0, void* local1, int64_t stride1,
+                                   int64_t bytes1, void* const* peer1, int grid) {
+  const TransportTable t0 = {local0, stride0, bytes0, peer0};
+  const TransportTable t1 = {local1, stride1, bytes1, peer1};
+  cot::launch(grid, kTransportThreads,
+              [=] { replica_pull_kernel(inverse, rank, world, epr, t0, t1); });
 }
 
 }  // extern "C"

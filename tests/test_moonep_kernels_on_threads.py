@@ -38,6 +38,10 @@ def kernels(tmp_path_factory):
     lib = C.CDLL(str(out))
     for name in ("cot_moonep_plan", "cot_moonep_count_cube", "cot_moonep_map_routes"):
         getattr(lib, name).restype = None
+    table = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+    for name in ("cot_moonep_push_replicas", "cot_moonep_pull_replica_grads"):
+        getattr(lib, name).restype = None
+        getattr(lib, name).argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int] + table + table + [C.c_int]
     return lib
 
 
@@ -187,3 +191,78 @@ def test_map_kernel_reports_routes_without_a_slot(kernels):
                                   *[p(t) for t in tables], *[p(o) for o in outs], p(status))
     assert status[0] == 3 and status[1] == 1
     assert all((o == -1).all() for o in outs)
+
+
+def _pointer_table(arrays):
+    table = (C.c_void_p * len(arrays))(*[a.ctypes.data for a in arrays])
+    return table
+
+
+@pytest.mark.parametrize("name", ["owners_w8_e64_k4", "owners_w4_e32_k6", "hot_w2_e4"])
+@pytest.mark.parametrize("bytes0, bytes1, pad", [(40000, 16, 0), (16 * 1024, 0, 32), (48, 33008, 16)])
+def test_replica_push_kernel(kernels, golden, name, bytes0, bytes1, pad):
+    """Every rank pushes the experts it owns into the replica slots experts_to_copy names; empty
+    slots and bytes outside the tables stay as they were."""
+    from oracle import moonep_oracle as M
+
+    etc = np.ascontiguousarray(golden[f"{name}/experts_to_copy"], np.int32)
+    world, epr = etc.shape
+    rng = np.random.default_rng(bytes0 + bytes1)
+    sizes = [b for b in (bytes0, bytes1) if b]
+    home = [[rng.integers(0, 256, size=(epr, b + pad), dtype=np.uint8) for _ in range(world)]
+            for b in sizes]
+    pools = [[np.full((epr, b), 0xEE, np.uint8) for _ in range(world)] for b in sizes]
+    tables = [_pointer_table(pools[t]) for t in range(len(sizes))]
+    for rank in range(world):
+        args = []
+        for t in range(2):
+            if t < len(sizes):
+                args += [p(home[t][rank]), sizes[t] + pad, sizes[t], tables[t]]
+            else:
+                args += [None, 0, 0, None]
+        kernels.cot_moonep_push_replicas(p(etc), rank, world, epr, *args, 5)
+    for t, b in enumerate(sizes):
+        want = M.replica_pools(etc, [h[:, :b] for h in home[t]], 0xEE)
+        for d in range(world):
+            np.testing.assert_array_equal(pools[t][d], want[d], f"table {t} rank {d}")
+    assert (etc >= 0).any()
+
+
+@pytest.mark.parametrize("name", ["owners_w8_e64_k4", "owners_w4_e32_k6", "one_home_w8_e64"])
+def test_replica_pull_kernel(kernels, golden, name):
+    """Every home rank adds the gradients of its experts' copies onto its own, fp32, peers in
+    ascending order, one rounding; experts without copies and other ranks' tables stay as they
+    were."""
+    import torch
+
+    from oracle import moonep_oracle as M
+
+    inverse = np.ascontiguousarray(golden[f"{name}/inverse"], np.int32)
+    world, experts = inverse.shape
+    epr = experts // world
+    gen = torch.Generator().manual_seed(5)
+    n0, n1 = 8 * 1031, 8 * 3                     # bf16 elements per expert (16-byte multiples)
+    stride0 = n0 + 8                             # the home table may be strided
+    home, copies, home_np, copies_np = [], [], [], []
+    for n, stride in ((n0, stride0), (n1, n1)):
+        home.append([torch.randn(epr, stride, generator=gen).to(torch.bfloat16) for _ in range(world)])
+        copies.append([torch.randn(epr, n, generator=gen).to(torch.bfloat16) for _ in range(world)])
+        home_np.append([h.view(torch.int16).numpy().copy() for h in home[-1]])
+        copies_np.append([c.view(torch.int16).numpy().copy() for c in copies[-1]])
+    tables = [_pointer_table(copies_np[t]) for t in range(2)]
+    for rank in range(world):
+        kernels.cot_moonep_pull_replica_grads(
+            p(inverse), rank, world, epr,
+            p(home_np[0][rank]), stride0 * 2, n0 * 2, tables[0],
+            p(home_np[1][rank]), n1 * 2, n1 * 2, tables[1], 3)
+    touched = 0
+    for t, (n, stride) in enumerate(((n0, stride0), (n1, n1))):
+        want = M.reduced_weight_grads(inverse, [h[:, :n] for h in home[t]], copies[t])
+        for rank in range(world):
+            got = torch.from_numpy(home_np[t][rank]).view(torch.bfloat16)
+            assert torch.equal(got[:, :n].view(torch.int16), want[rank].view(torch.int16)), (t, rank)
+            assert torch.equal(got[:, n:].view(torch.int16), home[t][rank][:, n:].view(torch.int16))
+            assert np.array_equal(copies_np[t][rank], copies[t][rank].view(torch.int16).numpy())
+            touched += int((got[:, :n].view(torch.int16) != home[t][rank][:, :n].view(torch.int16))
+                           .any(dim=1).sum())
+    assert touched > 0

@@ -267,3 +267,103 @@ def test_map_kernel_reports_routes_without_a_slot():
     torch.cuda.synchronize()
     assert status.cpu()[:2].tolist() == [3, 1]
     assert all(bool((o == -1).all()) for o in outs)
+
+
+def _replica_table(local: torch.Tensor, stride_bytes: int, nbytes: int, peers: torch.Tensor):
+    from mega_moe import _native as N
+    return N.ReplicaTable(local.data_ptr(), stride_bytes, nbytes, peers.data_ptr())
+
+
+def _peer_pointers(tensors) -> torch.Tensor:
+    return torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device=DEV)
+
+
+@pytest.mark.parametrize("name", ["owners_w8_e64_k4", "owners_w4_e32_k6", "hot_w2_e4"])
+@pytest.mark.parametrize("bytes0, bytes1, pad", [(40000, 16, 0), (16 * 1024, 0, 32),
+                                                 (48, 33008, 16), (7168 * 512 * 2, 0, 0)])
+def test_replica_push_matches_the_oracle(tables, name, bytes0, bytes1, pad):
+    """All ranks of a case push in turn on one GPU (every peer pointer is local): each replica
+    slot named by experts_to_copy holds its expert's home block, the rest is untouched."""
+    import ctypes as C
+
+    from mega_moe import _native as N
+    from oracle import moonep_oracle as M
+
+    etc_np = np.ascontiguousarray(tables[f"{name}/experts_to_copy"], np.int32)
+    world, epr = etc_np.shape
+    etc = dev(etc_np)
+    sizes = [b for b in (bytes0, bytes1) if b]
+    gen = torch.Generator().manual_seed(bytes0 + bytes1)
+    home = [[torch.randint(0, 256, (epr, b + pad), dtype=torch.uint8, generator=gen).to(DEV)
+             for _ in range(world)] for b in sizes]
+    pools = [[torch.full((epr, b), 0xEE, dtype=torch.uint8, device=DEV) for _ in range(world)]
+             for b in sizes]
+    peers = [_peer_pointers(pools[t]) for t in range(len(sizes))]
+    for rank in range(world):
+        descs = [_replica_table(home[t][rank], sizes[t] + pad, sizes[t], peers[t])
+                 for t in range(len(sizes))]
+        N.check(N.lib().mm_moonep_push_replicas(
+            etc.data_ptr(), rank, world, epr, C.byref(descs[0]),
+            C.byref(descs[1]) if len(descs) > 1 else None, 0 if rank % 2 else 5, N.stream_ptr()),
+            "mm_moonep_push_replicas")
+    torch.cuda.synchronize()
+    for t, b in enumerate(sizes):
+        want = M.replica_pools(etc_np, [h[:, :b].cpu().numpy() for h in home[t]], 0xEE)
+        for d in range(world):
+            np.testing.assert_array_equal(pools[t][d].cpu().numpy(), want[d], f"table {t} rank {d}")
+
+
+@pytest.mark.parametrize("name", ["owners_w8_e64_k4", "owners_w4_e32_k6", "one_home_w8_e64"])
+def test_replica_pull_matches_the_oracle(tables, name):
+    """Every home rank adds its experts' replica gradients onto its own: fp32, peers ascending,
+    one rounding; bit-exact against the oracle."""
+    import ctypes as C
+
+    from mega_moe import _native as N
+    from oracle import moonep_oracle as M
+
+    inv_np = np.ascontiguousarray(tables[f"{name}/inverse"], np.int32)
+    world, experts = inv_np.shape
+    epr = experts // world
+    inv = dev(inv_np)
+    gen = torch.Generator().manual_seed(5)
+    shapes = ((8 * 1031, 8 * 1031 + 8), (8 * 3, 8 * 3))        # elements per expert, expert stride
+    home0, home, copies = [], [], []
+    for n, stride in shapes:
+        home0.append([torch.randn(epr, stride, generator=gen).to(torch.bfloat16) for _ in range(world)])
+        copies.append([torch.randn(epr, n, generator=gen).to(torch.bfloat16).to(DEV)
+                       for _ in range(world)])
+        home.append([h.clone().to(DEV) for h in home0[-1]])
+    peers = [_peer_pointers(copies[t]) for t in range(2)]
+    for rank in range(world):
+        descs = [_replica_table(home[t][rank], shapes[t][1] * 2, shapes[t][0] * 2, peers[t])
+                 for t in range(2)]
+        N.check(N.lib().mm_moonep_pull_replica_grads(
+            inv.data_ptr(), rank, world, epr, C.byref(descs[0]), C.byref(descs[1]),
+            0 if rank % 2 else 3, N.stream_ptr()), "mm_moonep_pull_replica_grads")
+    torch.cuda.synchronize()
+    for t, (n, stride) in enumerate(shapes):
+        want = M.reduced_weight_grads(inv_np, [h[:, :n] for h in home0[t]],
+                                      [c.cpu() for c in copies[t]])
+        for rank in range(world):
+            got = home[t][rank].cpu()
+            assert torch.equal(got[:, :n].view(torch.int16), want[rank].view(torch.int16)), (t, rank)
+            assert torch.equal(got[:, n:].view(torch.int16), home0[t][rank][:, n:].view(torch.int16))
+
+
+def test_replica_buffers_on_one_rank():
+    """World of one: the symmetric tables are allocated and the push has nothing to do."""
+    from mega_moe.runtime.replica_transport import (allocate_replica_weight_buffers,
+                                                    push_replica_weights)
+    gate_up = torch.randn(4, 64, 128, device=DEV).to(torch.bfloat16)
+    down = torch.randn(4, 64, 64, device=DEV).to(torch.bfloat16)
+    buffers = allocate_replica_weight_buffers(gate_up, down, rank=0, world_size=1)
+    try:
+        assert buffers.gate_up.shape == gate_up.shape and buffers.down.shape == down.shape
+        buffers.gate_up.fill_(1.0)
+        etc = torch.full((1, 4), -1, **I32)
+        push_replica_weights(etc, gate_up, down, buffers, rank=0, world_size=1)
+        torch.cuda.synchronize()
+        assert bool((buffers.gate_up == 1.0).all())
+    finally:
+        buffers.free()
