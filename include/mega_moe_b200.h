@@ -249,6 +249,20 @@ int mm_moonep_map_routes_host(const int32_t* route_in, const int32_t* expert_in,
                               int32_t* send_token, int32_t* send_bucket, int32_t* route_to_send,
                               int32_t* num_misplaced);
 
+/* MoonEP as a re-labelling of routes: physical[route] = d * 2 * E/R + p, the bucket that executes
+ * the route, -1 for routes mm_route_local dropped (route_to_send < 0).  Inputs as for
+ * mm_moonep_map_routes (expert_start and below from mm_moonep_count_cube).  Running the ordinary
+ * routing (mm_route_local, mm_count_exchange, mm_route_finalize) with `physical` as the expert ids
+ * of a layer of 2 * E experts yields the balanced send order, count cube and offsets, so the
+ * rest of the layer runs unchanged over 2 * E/R groups per rank
+ * (reference: the physical-slot forward, ops/_moonep_torch_forward.py:226-430). */
+int mm_moonep_relabel_routes(const int32_t* route_in, const int32_t* expert_in,
+                             const int32_t* route_to_send, const int32_t* local_stats,
+                             int num_routes, int world, int num_experts,
+                             const int32_t* expert_start, const int32_t* below,
+                             const int32_t* alloc_cumsum, const int32_t* inverse,
+                             int32_t* physical, void* status, cudaStream_t stream);
+
 /* One weight (or weight-gradient) table of the replica transport.  `local` is this rank's
  * [E/R][bytes] table of its home experts (experts `local_stride` bytes apart); peer[d] is rank
  * d's replica table [E/R slots][bytes], slots contiguous, in memory every rank can address

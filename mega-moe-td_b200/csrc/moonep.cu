@@ -285,6 +285,26 @@ int mm_moonep_map_routes_host(const int32_t* route_in, const int32_t* expert_in,
   return MM_OK;
 }
 
+int mm_moonep_relabel_routes(const int32_t* route_in, const int32_t* expert_in,
+                             const int32_t* route_to_send, const int32_t* local_stats,
+                             int num_routes, int world, int num_experts,
+                             const int32_t* expert_start, const int32_t* below,
+                             const int32_t* alloc_cumsum, const int32_t* inverse,
+                             int32_t* physical, void* status, cudaStream_t stream) {
+  const void* const ptrs[] = {route_in, expert_in,    route_to_send, local_stats, expert_start,
+                              below,    alloc_cumsum, inverse,       physical};
+  if (int rc = check_map_args("mm_moonep_relabel_routes", ptrs, 9, num_routes, 1, world,
+                              num_experts))
+    return rc;
+  if (num_routes == 0) return MM_OK;
+  const int blocks = (num_routes + kMapThreads - 1) / kMapThreads;
+  moonep_relabel_kernel<<<blocks, kMapThreads, 0, stream>>>(
+      route_in, expert_in, route_to_send, local_stats, num_routes, world, num_experts,
+      expert_start, below, alloc_cumsum, inverse, physical,
+      reinterpret_cast<StatusRecord*>(status));
+  return check_launch("moonep_relabel_kernel");
+}
+
 static int make_transport_table(const char* who, const mm_replica_table* in, bool required,
                                 TransportTable* out) {
   *out = TransportTable{nullptr, 0, 0, nullptr};

@@ -288,22 +288,35 @@ struct Placement {
 
 // Route number i of the expert-major stable order, an instance of expert e.
 // expert_start[e]: first index of expert e in that order; below[e]: lower_rank_routes.
+// Returns the bucket (destination rank * 2 * epr + physical slot, -1 if no allocation or slot
+// holds the route); *ordinal_out / *share_lo_out: the route's number among all routes of the
+// expert, and the first such number this rank sends to that bucket.
+MM_HD int32_t route_bucket(int i, int e, int world, int num_experts, int epr,
+                           const int32_t* expert_start, const int32_t* below,
+                           const int32_t* alloc_cumsum, const int32_t* inverse,
+                           int32_t* ordinal_out, int32_t* share_lo_out) {
+  const int32_t ordinal = below[e] + (i - expert_start[e]);
+  const int32_t* prefix = alloc_cumsum + (int64_t)e * world;
+  int dest = 0;
+  while (dest < world && prefix[dest] <= ordinal) ++dest;  // the prefix is non-decreasing
+  if (dest >= world) return -1;
+  const int32_t slot = physical_slot(inverse, num_experts, epr, dest, e);
+  if (slot < 0) return -1;
+  const int32_t alloc_lo = dest ? prefix[dest - 1] : 0;
+  *ordinal_out = ordinal;
+  *share_lo_out = below[e] > alloc_lo ? below[e] : alloc_lo;
+  return dest * 2 * epr + slot;
+}
+
 MM_HD Placement place_route(int i, int e, int world, int num_experts, int epr,
                             const int32_t* expert_start, const int32_t* below,
                             const int32_t* alloc_cumsum, const int32_t* inverse,
                             const int32_t* send_bucket_starts) {
   Placement p = {-1, -1};
-  const int32_t ordinal = below[e] + (i - expert_start[e]);
-  const int32_t* prefix = alloc_cumsum + (int64_t)e * world;
-  int dest = 0;
-  while (dest < world && prefix[dest] <= ordinal) ++dest;  // the prefix is non-decreasing
-  if (dest >= world) return p;
-  const int32_t slot = physical_slot(inverse, num_experts, epr, dest, e);
-  if (slot < 0) return p;
-  const int32_t alloc_lo = dest ? prefix[dest - 1] : 0;
-  const int32_t share_lo = below[e] > alloc_lo ? below[e] : alloc_lo;
-  p.bucket = dest * 2 * epr + slot;
-  p.position = send_bucket_starts[p.bucket] + (ordinal - share_lo);
+  int32_t ordinal = 0, share_lo = 0;
+  p.bucket = route_bucket(i, e, world, num_experts, epr, expert_start, below, alloc_cumsum,
+                          inverse, &ordinal, &share_lo);
+  if (p.bucket >= 0) p.position = send_bucket_starts[p.bucket] + (ordinal - share_lo);
   return p;
 }
 

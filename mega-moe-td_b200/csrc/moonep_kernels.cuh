@@ -228,5 +228,35 @@ moonep_map_kernel(const int32_t* __restrict__ route_in, const int32_t* __restric
   route_to_send[route] = p.position;
 }
 
+// MoonEP as a re-labelling: physical[t, j] = bucket (rank * 2 * E/R + slot) that executes route
+// (t, j), -1 for a route the filter dropped.  Routing `physical` as expert ids of a layer with
+// 2 * E experts reproduces the balanced send order, cube and offsets.
+__global__ void __launch_bounds__(kMapThreads)
+moonep_relabel_kernel(const int32_t* __restrict__ route_in, const int32_t* __restrict__ expert_in,
+                      const int32_t* __restrict__ route_to_send,
+                      const int32_t* __restrict__ local_stats, int num_routes, int world,
+                      int num_experts, const int32_t* __restrict__ expert_start,
+                      const int32_t* __restrict__ below, const int32_t* __restrict__ alloc_cumsum,
+                      const int32_t* __restrict__ inverse, int32_t* __restrict__ physical,
+                      StatusRecord* status) {
+  const int i = blockIdx.x * kMapThreads + threadIdx.x;
+  if (i >= num_routes) return;
+  if (route_to_send[i] < 0) physical[i] = -1;  // flat route i was dropped
+  int valid = local_stats[0];
+  if (valid > num_routes) valid = num_routes;
+  if (i >= valid) return;
+  const int32_t e = expert_in[i];
+  const int32_t route = route_in[i];
+  if (e < 0 || e >= num_experts || route < 0 || route >= num_routes) {
+    report_status(status, kBadIndex, 2, i, e, route);
+    return;
+  }
+  int32_t ordinal, share_lo;
+  const int32_t bucket = route_bucket(i, e, world, num_experts, num_experts / world, expert_start,
+                                      below, alloc_cumsum, inverse, &ordinal, &share_lo);
+  if (bucket < 0) report_status(status, kBadIndex, 3, i, e, route);
+  physical[route] = bucket;
+}
+
 }  // namespace moonep_kernels
 }  // namespace mm

@@ -116,6 +116,8 @@ SIGNATURES = {
                                        C.c_int] + [_c_i32p] * 9 + [_c_ptr, _c_ptr]),
     "mm_moonep_map_routes_host": (C.c_int, [_c_i32p, _c_i32p, C.c_int, C.c_int, C.c_int, C.c_int,
                                             C.c_int] + [_c_i32p] * 10),
+    "mm_moonep_relabel_routes": (C.c_int, [_c_i32p, _c_i32p, _c_i32p, _c_i32p, C.c_int, C.c_int,
+                                           C.c_int] + [_c_i32p] * 5 + [_c_ptr, _c_ptr]),
     "mm_moonep_push_replicas": (C.c_int, [_c_i32p, C.c_int, C.c_int, C.c_int,
                                           C.POINTER(ReplicaTable), C.POINTER(ReplicaTable),
                                           C.c_int, _c_ptr]),

@@ -312,9 +312,44 @@ def launch_balanced_routing(*, count_cube: torch.Tensor, rank: int, world_size: 
     N.count_launches(2)
 
 
+def launch_physical_relabel(*, count_cube: torch.Tensor, rank: int, world_size: int,
+                            num_experts: int, alloc_cumsum: torch.Tensor,
+                            experts_to_copy: torch.Tensor, inverse_experts_to_copy: torch.Tensor,
+                            expert_major_routes: torch.Tensor, expert_major_experts: torch.Tensor,
+                            route_to_send: torch.Tensor, local_stats: torch.Tensor,
+                            balanced_cube: torch.Tensor, expert_start: torch.Tensor,
+                            below: torch.Tensor, physical: torch.Tensor,
+                            status: Optional[torch.Tensor] = None) -> None:
+    """Queue MoonEP as a re-labelling on the current stream: ``physical[route]`` (int32, one
+    entry per flattened ``(token, top-k slot)``) receives the bucket ``rank * 2 * E/R + slot``
+    that executes the route, ``-1`` for dropped routes.  Feeding ``physical`` as the expert ids
+    of a layer with ``2 * E`` experts (``2 * E/R`` per rank: home slots, then replica slots) to
+    the ordinary routing gives the balanced send order, cube and offsets, so dispatch, GEMMs,
+    combine and backward run unchanged over the physical slots.  ``balanced_cube`` is written
+    too (a by-product of the per-expert tables)."""
+    device = count_cube.device
+    if device.type != "cuda":
+        raise ValueError("launch_physical_relabel takes device tensors")
+    lib = N.lib()
+    stream = N.stream_ptr(device)
+    N.check(lib.mm_moonep_count_cube(
+        count_cube.data_ptr(), count_cube.stride(0), rank, world_size, num_experts,
+        alloc_cumsum.data_ptr(), experts_to_copy.data_ptr(), balanced_cube.data_ptr(),
+        balanced_cube.stride(0), expert_start.data_ptr(), below.data_ptr(), stream),
+        "mm_moonep_count_cube")
+    N.check(lib.mm_moonep_relabel_routes(
+        expert_major_routes.data_ptr(), expert_major_experts.data_ptr(),
+        route_to_send.data_ptr(), local_stats.data_ptr(), int(physical.numel()), world_size,
+        num_experts, expert_start.data_ptr(), below.data_ptr(), alloc_cumsum.data_ptr(),
+        inverse_experts_to_copy.data_ptr(), physical.data_ptr(), N.ptr(status), stream),
+        "mm_moonep_relabel_routes")
+    N.count_launches(2)
+
+
 __all__ = [
     "BalancedRoutingMetadata",
     "build_balanced_routing_metadata",
     "experts_to_copy_from_inverse",
     "launch_balanced_routing",
+    "launch_physical_relabel",
 ]

@@ -71,6 +71,21 @@ void cot_moonep_map_routes(const int32_t* route_in, const int32_t* expert_in,
   });
 }
 
+void cot_moonep_relabel_routes(const int32_t* route_in, const int32_t* expert_in,
+                               const int32_t* route_to_send, const int32_t* local_stats,
+                               int num_routes, int world, int num_experts,
+                               const int32_t* expert_start, const int32_t* below,
+                               const int32_t* alloc_cumsum, const int32_t* inverse,
+                               int32_t* physical, void* status) {
+  if (num_routes == 0) return;
+  const int blocks = (num_routes + kMapThreads - 1) / kMapThreads;
+  cot::launch(blocks, kMapThreads, [=] {
+    moonep_relabel_kernel(route_in, expert_in, route_to_send, local_stats, num_routes, world,
+                          num_experts, expert_start, below, alloc_cumsum, inverse, physical,
+                          static_cast<StatusRecord*>(status));
+  });
+}
+
 // tables: local pointer, bytes between local experts, bytes per expert, array of `world` pointers
 void cot_moonep_push_replicas(const int32_t* experts_to_copy, int rank, int world, int epr,
                               const void* local0, int64_t stride0, int64_t bytes0,

@@ -266,3 +266,38 @@ def test_replica_pull_kernel(kernels, golden, name):
             touched += int((got[:, :n].view(torch.int16) != home[t][rank][:, :n].view(torch.int16))
                            .any(dim=1).sum())
     assert touched > 0
+
+
+def test_relabel_kernel_gives_every_route_its_bucket(kernels, golden):
+    for name in names(golden, routed=True):
+        if not bool(golden[f"{name}/full"]):
+            continue
+        tpe = np.ascontiguousarray(golden[f"{name}/tpe_all"], np.int32)
+        alloc = np.ascontiguousarray(golden[f"{name}/alloc_cumsum"], np.int32)
+        inverse = np.ascontiguousarray(golden[f"{name}/inverse"], np.int32)
+        world, experts = tpe.shape
+        for rank in range(world):
+            sel = golden[f"{name}/selected_{rank}"]
+            if sel.size == 0:
+                continue
+            route_in, expert_in = expert_major(sel, experts)
+            n = route_in.size
+            pad = sel.size
+            route_pad = np.full(pad, -1, np.int32)
+            route_pad[:n] = route_in
+            expert_pad = np.full(pad, -1, np.int32)
+            expert_pad[:n] = expert_in
+            route_to_send = np.full(pad, -1, np.int32)
+            route_to_send[route_in] = np.arange(n)
+            expert_start = (tpe[rank].cumsum() - tpe[rank]).astype(np.int32)
+            below = tpe[:rank].sum(axis=0).astype(np.int32)
+            physical = np.full(pad, 77, np.int32)
+            stats = np.array([n, 0], np.int32)
+            status = np.zeros(8, np.int32)
+            kernels.cot_moonep_relabel_routes(p(route_pad), p(expert_pad), p(route_to_send),
+                                              p(stats), pad, world, experts, p(expert_start),
+                                              p(below), p(alloc), p(inverse), p(physical), p(status))
+            assert status[0] == 0
+            want = np.full(pad, -1, np.int32)
+            want[golden[f"{name}/r{rank}/final_order"]] = golden[f"{name}/r{rank}/balanced_buckets"]
+            np.testing.assert_array_equal(physical, want, f"{name} r{rank}")

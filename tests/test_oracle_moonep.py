@@ -231,3 +231,41 @@ def test_forward_over_physical_slots_equals_the_logical_forward(world, experts, 
         O_ = want[r].float()
         diff = (got[r].float() - O_).abs().max().item()
         assert diff <= O.LAYOUT_ATOL + 2.0 ** -7 * O_.abs().max().item(), (r, diff)
+
+
+def test_relabelled_routes_through_the_ordinary_routing_give_the_balanced_tables(golden):
+    """Replace every route's logical expert by its physical bucket and run the ordinary routing
+    (stable sort by expert id, count cube, offsets) with 2E experts: send order, buckets, cube
+    and receive offsets are the reference's balanced tables.  MoonEP is therefore a re-labelling
+    in front of the unchanged pipeline."""
+    from oracle import moe_oracle as O
+
+    for name in case_names(golden, routed=True):
+        if not bool(golden[f"{name}/full"]):
+            continue
+        tpe = golden[f"{name}/tpe_all"]
+        world, experts = tpe.shape
+        relabelled = []
+        for rank in range(world):
+            sel = golden[f"{name}/selected_{rank}"]
+            phys = np.full(sel.size, -1, np.int32)
+            phys[golden[f"{name}/r{rank}/final_order"]] = golden[f"{name}/r{rank}/balanced_buckets"]
+            relabelled.append(phys.reshape(sel.shape))
+        if relabelled[0].size == 0:
+            continue
+        meta = O.routing_metadata(relabelled, 2 * experts)
+        for rank in range(world):
+            m = meta[rank]
+            n = m["num_sent_routes"]
+            assert n == int(golden[f"{name}/r{rank}/num_valid_routes"])
+            np.testing.assert_array_equal(m["send_route_indices"],
+                                          golden[f"{name}/r{rank}/send_route_indices"])
+            np.testing.assert_array_equal(m["send_token_indices"],
+                                          golden[f"{name}/r{rank}/send_token_indices"])
+            np.testing.assert_array_equal(m["send_bucket"], golden[f"{name}/r{rank}/balanced_buckets"])
+            np.testing.assert_array_equal(m["count_cube"][:, :2 * experts],
+                                          golden[f"{name}/r{rank}/balanced_counts"])
+            np.testing.assert_array_equal(m["send_bucket_dst_starts"],
+                                          golden[f"{name}/r{rank}/send_bucket_receive_offsets"])
+            np.testing.assert_array_equal(m["recv_expert_offs"],
+                                          golden[f"{name}/r{rank}/received_slot_offsets"])

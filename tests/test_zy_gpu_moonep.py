@@ -367,3 +367,81 @@ def test_replica_buffers_on_one_rank():
         assert bool((buffers.gate_up == 1.0).all())
     finally:
         buffers.free()
+
+
+def test_relabelled_routes_through_the_ordinary_routing_match_the_reference(tables):
+    """MoonEP as a re-labelling, on the device: mm_route_local -> mm_moonep_plan ->
+    mm_moonep_count_cube -> mm_moonep_relabel_routes, then the ordinary routing of a layer with
+    2E experts on the relabelled ids (mm_route_local again, mm_route_finalize on the gathered
+    count rows): send order, buckets, count cube and offsets are the reference's balanced
+    tables."""
+    from mega_moe import _native as N
+    from mega_moe.runtime.balanced_routing import launch_physical_relabel
+    from mega_moe.runtime.workspace import next_power_of_2
+    lib = N.lib()
+    for name in names(tables, routed=True):
+        tpe = np.ascontiguousarray(tables[f"{name}/tpe_all"], np.int32)
+        world, experts = tpe.shape
+        slots = 2 * (experts // world)
+        full = bool(tables[f"{name}/full"])
+        if tables[f"{name}/selected_0"].size == 0:
+            continue
+        bins = next_power_of_2(experts + 1)
+        cube = np.zeros((world, bins), np.int32)
+        cube[:, :experts] = tpe
+        cube_d = dev(cube)
+        plan, status = plan_on_device(cube_d, experts)
+        assert status[0] == 0
+        phys_bins = next_power_of_2(2 * experts)
+        second, rows = [], []
+        for rank in range(world):
+            sel = tables[f"{name}/selected_{rank}"]
+            local = route_local(sel, experts, bins)
+            physical = torch.full((sel.size,), 77, **I32)
+            relabel_status = torch.zeros(8, **I32)
+            launch_physical_relabel(
+                count_cube=cube_d, rank=rank, world_size=world, num_experts=experts,
+                alloc_cumsum=plan["alloc_cumsum"], experts_to_copy=plan["experts_to_copy"],
+                inverse_experts_to_copy=plan["inverse_experts_to_copy"],
+                expert_major_routes=local["send_route"], expert_major_experts=local["send_bucket"],
+                route_to_send=local["route_to_send"], local_stats=local["local_stats"],
+                balanced_cube=torch.full((world, phys_bins), 77, **I32),
+                expert_start=torch.full((experts,), 77, **I32),
+                below=torch.full((experts,), 77, **I32), physical=physical, status=relabel_status)
+            torch.cuda.synchronize()
+            assert relabel_status.cpu()[0] == 0
+            want = np.full(sel.size, -1, np.int32)
+            if full:
+                want[tables[f"{name}/r{rank}/final_order"]] = tables[f"{name}/r{rank}/balanced_buckets"]
+                np.testing.assert_array_equal(physical.cpu().numpy(), want, f"{name} r{rank}")
+            # the ordinary routing of 2E experts on the relabelled ids
+            again = route_local(physical.cpu().numpy().reshape(sel.shape), 2 * experts, phys_bins)
+            torch.cuda.synchronize()
+            second.append({k: v.cpu().numpy() for k, v in again.items()})
+            rows.append(second[-1]["count_row"])
+        gathered = dev(np.stack(rows))
+        capacity = int(tpe.sum(axis=1)[0]) + 7
+        for rank in range(world):
+            fin = finalize_tables(world, slots, capacity)
+            fin_status = torch.zeros(8, **I32)
+            N.check(lib.mm_route_finalize(gathered.data_ptr(), rank, world, slots, phys_bins,
+                                          capacity, *[fin[k].data_ptr() for k in FINALIZE_ORDER],
+                                          fin_status.data_ptr(), N.stream_ptr()), "mm_route_finalize")
+            torch.cuda.synchronize()
+            assert fin_status.cpu()[0] == 0
+            n = int(second[rank]["local_stats"][0])
+            have = {
+                "send_route_indices": second[rank]["send_route"][:n],
+                "send_token_indices": second[rank]["send_token"][:n],
+                "balanced_buckets": second[rank]["send_bucket"][:n],
+                "balanced_counts": np.ascontiguousarray(np.stack(rows)[:, :world * slots]),
+                "send_bucket_starts": fin["send_bucket_starts"].cpu().numpy(),
+                "send_bucket_receive_offsets": fin["send_bucket_dst_starts"].cpu().numpy(),
+                "received_slot_offsets": fin["recv_expert_offs"].cpu().numpy(),
+            }
+            for f, v in have.items():
+                want = tables[f"{name}/r{rank}/{f}"]
+                if full:
+                    np.testing.assert_array_equal(v, want, f"{name} r{rank} {f}")
+                else:
+                    assert digest(np.ascontiguousarray(v)) == str(want), (name, rank, f)
