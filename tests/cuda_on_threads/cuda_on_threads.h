@@ -3,7 +3,8 @@
 // Enough of the CUDA programming model for small integer kernels: __global__ / __device__ /
 // __shared__, threadIdx / blockIdx, __syncthreads, __syncwarp, __shfl_xor_sync / __shfl_up_sync
 // (all 32 lanes of a warp must take part, block sizes are multiples of 32), atomicMin / atomicCAS
-// on int, __threadfence, uint4, __ldg, __uint_as_float / __float_as_uint, gridDim / blockDim.
+// on int, __threadfence, uint4, __ldg, __uint_as_float / __float_as_uint, gridDim / blockDim,
+// __ballot_sync, __clz.
 // The blocks of a launch run one after another; the threads of a block
 // run concurrently as std::thread, and barriers are real barriers, so a kernel that forgets one
 // can fail here as it can on a GPU.  __shared__ variables become function-local statics, which
@@ -165,6 +166,20 @@ T __shfl_up_sync(unsigned, T v, int delta) {
   const int lane = ::cot::self().thread.x & 31;
   return ::cot::shuffle(v, lane >= delta ? lane - delta : -1);
 }
+
+inline unsigned __ballot_sync(unsigned, bool predicate) {
+  ::cot::Warp& w = ::cot::my_warp();
+  const int lane = ::cot::self().thread.x & 31;
+  w.slot[lane] = predicate ? 1 : 0;
+  w.barrier.wait();
+  unsigned mask = 0;
+  for (int i = 0; i < 32; ++i)
+    if (w.slot[i]) mask |= 1u << i;
+  w.barrier.wait();
+  return mask;
+}
+
+inline int __clz(int x) { return x == 0 ? 32 : __builtin_clz((unsigned)x); }
 
 inline int atomicMin(int* p, int v) {
   int old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
