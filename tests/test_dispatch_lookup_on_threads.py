@@ -13,8 +13,7 @@ from __future__ import annotations
 
 import ctypes as C
 import re
-import shutil
-import subprocess
+import sys
 from pathlib import Path
 
 import numpy as np
@@ -23,6 +22,7 @@ import pytest
 REPO = Path(__file__).resolve().parent.parent
 HERE = Path(__file__).resolve().parent
 CSRC = REPO / "mega-moe-td_b200" / "csrc"
+sys.path.insert(0, str(HERE))
 
 
 def cut(text: str, start: str, end: str = "\n}\n") -> str:
@@ -81,8 +81,7 @@ extern "C" void lookup_all(const GemmParams* p, int n_send, int warps, int32_t* 
 
 @pytest.fixture(scope="module")
 def lookup(tmp_path_factory):
-    if shutil.which("g++") is None:
-        pytest.skip("g++ is not installed")
+    from cuda_on_threads.host_build import compile_for_host
     gemm = (CSRC / "gemm_sm100.cuh").read_text()
     common = (CSRC / "common.cuh").read_text()
     src = HARNESS % dict(
@@ -94,10 +93,7 @@ def lookup(tmp_path_factory):
     )
     d = tmp_path_factory.mktemp("dispatch_lookup")
     (d / "lookup.cpp").write_text(src)
-    out = d / "liblookup.so"
-    subprocess.run(["g++", "-O1", "-std=c++17", "-pthread", "-shared", "-fPIC",
-                    "-Wno-unknown-pragmas", "-I", str(HERE / "cuda_on_threads"),
-                    str(d / "lookup.cpp"), "-o", str(out)], check=True)
+    out = compile_for_host(d / "lookup.cpp", d / "liblookup.so")
     lib = C.CDLL(str(out))
     lib.lookup_all.restype = None
     return lib

@@ -3,14 +3,14 @@ the host: g++ compiles it against tests/cuda_on_threads/cuda_on_threads.h, which
 thread as a host thread with real block and warp barriers and warp shuffles.  The results must
 equal the fixtures written by the reference's host planner and balanced routing.  This checks
 the kernels' indexing, phase order, warp reductions and scans; the GPU tests check the same
-entry points on the device."""
+entry points on the device.  With MOE_TEST_SANITIZE=1 (see cuda_on_threads/host_build.py) the
+kernels run under AddressSanitizer."""
 
 from __future__ import annotations
 
 import ctypes as C
 import hashlib
-import shutil
-import subprocess
+import sys
 from pathlib import Path
 
 import numpy as np
@@ -19,6 +19,7 @@ import pytest
 REPO = Path(__file__).resolve().parent.parent
 HERE = Path(__file__).resolve().parent
 GOLDEN = HERE / "golden" / "moonep_tables.npz"
+sys.path.insert(0, str(HERE))
 
 
 def digest(a: np.ndarray) -> str:
@@ -28,13 +29,10 @@ def digest(a: np.ndarray) -> str:
 
 @pytest.fixture(scope="module")
 def kernels(tmp_path_factory):
-    if shutil.which("g++") is None:
-        pytest.skip("g++ is not installed")
-    out = tmp_path_factory.mktemp("cuda_on_threads") / "libmoonep_on_threads.so"
-    cmd = ["g++", "-O1", "-std=c++17", "-pthread", "-shared", "-fPIC", "-Wno-unknown-pragmas",
-           "-I", str(REPO / "mega-moe-td_b200" / "csrc"), "-I", str(HERE / "cuda_on_threads"),
-           str(HERE / "cuda_on_threads" / "moonep_kernels_on_threads.cpp"), "-o", str(out)]
-    subprocess.run(cmd, check=True)
+    from cuda_on_threads.host_build import compile_for_host
+    out = compile_for_host(HERE / "cuda_on_threads" / "moonep_kernels_on_threads.cpp",
+                           tmp_path_factory.mktemp("cuda_on_threads") / "libmoonep_on_threads.so",
+                           [REPO / "mega-moe-td_b200" / "csrc"])
     lib = C.CDLL(str(out))
     for name in ("cot_moonep_plan", "cot_moonep_count_cube", "cot_moonep_map_routes"):
         getattr(lib, name).restype = None
