@@ -4,7 +4,9 @@
 // __shared__, threadIdx / blockIdx, __syncthreads, __syncwarp, __shfl_xor_sync / __shfl_up_sync
 // (all 32 lanes of a warp must take part, block sizes are multiples of 32), atomicMin / atomicCAS
 // on int, __threadfence, uint4, __ldg, __uint_as_float / __float_as_uint, gridDim / blockDim,
-// __ballot_sync, __clz.
+// __ballot_sync, __match_any_sync, __shfl_sync, __popc, __clz, atomicAdd / atomicMax on int,
+// dynamic shared memory (cot::dynamic_shared(), see the tests for how `extern __shared__` maps
+// to it).
 // The blocks of a launch run one after another; the threads of a block
 // run concurrently as std::thread, and barriers are real barriers, so a kernel that forgets one
 // can fail here as it can on a GPU.  __shared__ variables become function-local statics, which
@@ -62,7 +64,8 @@ struct Warp {
 };
 
 struct Block {
-  explicit Block(int threads) : barrier(threads), warps(threads / 32) {
+  explicit Block(int threads, size_t dynamic_bytes = 0)
+      : barrier(threads), warps(threads / 32), dynamic((dynamic_bytes + 15) / 16 * 16 + 16) {
     for (auto& w : warps) w = new Warp();
   }
   ~Block() {
@@ -70,6 +73,7 @@ struct Block {
   }
   Barrier barrier;
   std::vector<Warp*> warps;
+  std::vector<unsigned char> dynamic;  // the launch's dynamic shared memory
 };
 
 struct Dim3 {
@@ -91,37 +95,45 @@ inline ThreadState& self() {
 
 inline Warp& my_warp() { return *self().cta->warps[self().thread.x / 32]; }
 
+inline void* dynamic_shared() { return self().cta->dynamic.data(); }
+
 template <class T>
 T shuffle(T v, int from_lane_or_negative) {
   Warp& w = my_warp();
   const int lane = self().thread.x & 31;
-  w.slot[lane] = (int64_t)v;
+  static_assert(sizeof(T) <= sizeof(int64_t), "shuffles move at most 8 bytes");
+  memcpy(&w.slot[lane], &v, sizeof(T));          // the bits, not the value: T may be a float
   w.barrier.wait();
-  const T r = from_lane_or_negative < 0 ? v : (T)w.slot[from_lane_or_negative];
+  T r = v;
+  if (from_lane_or_negative >= 0) memcpy(&r, &w.slot[from_lane_or_negative], sizeof(T));
   w.barrier.wait();
   return r;
 }
 
-// body() is the kernel call; grid x block threads run it
+// body() is the kernel call; grid x block threads run it.  The host threads of a launch are
+// created once and walk the blocks together (a barrier separates two blocks), which is what
+// "one block at a time" means here.
 template <class Body>
-void launch(int grid, int block, Body body) {
-  for (int b = 0; b < grid; ++b) {
-    Block cta(block);
-    std::vector<std::thread> threads;
-    threads.reserve(block);
-    for (int t = 0; t < block; ++t) {
-      threads.emplace_back([&, t, b] {
-        ThreadState& s = self();
-        s.thread = {t, 0, 0};
+void launch(int grid, int block, Body body, size_t dynamic_bytes = 0) {
+  Block cta(block, dynamic_bytes);
+  Barrier between_blocks(block);
+  std::vector<std::thread> threads;
+  threads.reserve(block);
+  for (int t = 0; t < block; ++t) {
+    threads.emplace_back([&, t] {
+      ThreadState& s = self();
+      s.thread = {t, 0, 0};
+      s.grid = {grid, 1, 1};
+      s.block_dim = {block, 1, 1};
+      s.cta = &cta;
+      for (int b = 0; b < grid; ++b) {
         s.block = {b, 0, 0};
-        s.grid = {grid, 1, 1};
-        s.block_dim = {block, 1, 1};
-        s.cta = &cta;
         body();
-      });
-    }
-    for (auto& th : threads) th.join();
+        between_blocks.wait();
+      }
+    });
   }
+  for (auto& th : threads) th.join();
 }
 
 }  // namespace cot
@@ -177,6 +189,41 @@ inline unsigned __ballot_sync(unsigned, bool predicate) {
     if (w.slot[i]) mask |= 1u << i;
   w.barrier.wait();
   return mask;
+}
+
+template <class T>
+T __shfl_sync(unsigned, T v, int src_lane) {
+  return ::cot::shuffle(v, src_lane & 31);
+}
+
+inline unsigned __match_any_sync(unsigned, int value) {
+  ::cot::Warp& w = ::cot::my_warp();
+  const int lane = ::cot::self().thread.x & 31;
+  w.slot[lane] = value;
+  w.barrier.wait();
+  unsigned mask = 0;
+  for (int i = 0; i < 32; ++i)
+    if (w.slot[i] == value) mask |= 1u << i;
+  w.barrier.wait();
+  return mask;
+}
+
+inline int __popc(unsigned x) { return __builtin_popcount(x); }
+
+inline int __float_as_int(float f) {
+  int i;
+  memcpy(&i, &f, 4);
+  return i;
+}
+
+inline int atomicAdd(int* p, int v) { return __atomic_fetch_add(p, v, __ATOMIC_SEQ_CST); }
+
+inline int atomicMax(int* p, int v) {
+  int old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
+  while (old < v && !__atomic_compare_exchange_n(p, &old, v, false, __ATOMIC_SEQ_CST,
+                                                 __ATOMIC_SEQ_CST)) {
+  }
+  return old;
 }
 
 inline int __clz(int x) { return x == 0 ? 32 : __builtin_clz((unsigned)x); }
