@@ -83,6 +83,8 @@ FWD_CASES = [
     (300, 256, 384, 16, 4, 0.3, None),
     (1024, 512, 256, 32, 8, 0.0, 1.2),
     (130, 128, 128, 4, 3, 1.0, None),          # every route dropped -> zeros
+    (512, 256, 128, 64, 4, 0.0, None),         # 64 buckets: the dispatch warps' bucket search
+                                               # takes two 32-way steps
 ]
 
 
@@ -186,7 +188,8 @@ def _to_dev(saved):
     return out
 
 
-BWD_CASES = [(64, 128, 128, 8, 2, None), (512, 256, 128, 8, 2, None), (700, 256, 384, 16, 4, 1.2)]
+BWD_CASES = [(64, 128, 128, 8, 2, None), (512, 256, 128, 8, 2, None), (700, 256, 384, 16, 4, 1.2),
+             (600, 128, 128, 64, 4, 1.2)]      # 64 buckets, some of them empty
 
 
 @pytest.mark.parametrize("tokens,hidden,ffn,experts,top_k,zipf", BWD_CASES)
