@@ -5,7 +5,6 @@ reference's own host code and the known answers of its tests
 
 from __future__ import annotations
 
-import ctypes as C
 import hashlib
 import sys
 from pathlib import Path

@@ -213,8 +213,6 @@ def test_offset_tables_of_the_balanced_cube_are_the_balanced_tables(golden):
 def test_forward_over_physical_slots_equals_the_logical_forward(world, experts, top_k, tokens, zipf):
     """Routing every row through the balanced tables and computing replica slots with copies of
     the home weights gives the same layer output as the forward over logical experts."""
-    import torch
-
     from oracle import moe_oracle as O
 
     inp = O.make_inputs(world, tokens, 64, 64, experts, top_k, seed=world,
