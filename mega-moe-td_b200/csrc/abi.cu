@@ -29,7 +29,10 @@ int mm_abi_version(void) { return 3; }
 const char* mm_last_error(void) { return g_error; }
 
 int mm_num_sms(int* out_host) {
-  if (!out_host) return MM_ERR_ARG;
+  if (!out_host) {
+    set_error("mm_num_sms: null argument");
+    return MM_ERR_ARG;
+  }
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(out_host, cudaDevAttrMultiProcessorCount, dev);
@@ -41,7 +44,10 @@ int mm_num_sms(int* out_host) {
 }
 
 int mm_status_reset(void* status, cudaStream_t stream) {
-  if (!status) return MM_ERR_ARG;
+  if (!status) {
+    set_error("mm_status_reset: null argument");
+    return MM_ERR_ARG;
+  }
   cudaError_t e = cudaMemsetAsync(status, 0, sizeof(mm_status_record), stream);
   if (e != cudaSuccess) {
     set_error("mm_status_reset: %s", cudaGetErrorString(e));
@@ -51,7 +57,10 @@ int mm_status_reset(void* status, cudaStream_t stream) {
 }
 
 int mm_status_read(const void* status, mm_status_record* out_host, cudaStream_t stream) {
-  if (!status || !out_host) return MM_ERR_ARG;
+  if (!status || !out_host) {
+    set_error("mm_status_read: null argument");
+    return MM_ERR_ARG;
+  }
   cudaError_t e = cudaMemcpyAsync(out_host, status, sizeof(mm_status_record),
                                   cudaMemcpyDeviceToHost, stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
@@ -88,7 +97,10 @@ int mm_symm_alloc(size_t bytes, void** dptr_host, unsigned char handle_host[64])
 }
 
 int mm_symm_open(const unsigned char handle_host[64], void** peer_ptr_host) {
-  if (!handle_host || !peer_ptr_host) return MM_ERR_ARG;
+  if (!handle_host || !peer_ptr_host) {
+    set_error("mm_symm_open: null argument");
+    return MM_ERR_ARG;
+  }
   cudaIpcMemHandle_t h;
   memcpy(&h, handle_host, 64);
   void* p = nullptr;
@@ -102,7 +114,10 @@ int mm_symm_open(const unsigned char handle_host[64], void** peer_ptr_host) {
 }
 
 int mm_symm_close(void* peer_ptr) {
-  if (!peer_ptr) return MM_ERR_ARG;
+  if (!peer_ptr) {
+    set_error("mm_symm_close: null argument");
+    return MM_ERR_ARG;
+  }
   cudaError_t e = cudaIpcCloseMemHandle(peer_ptr);
   if (e != cudaSuccess) {
     set_error("mm_symm_close: %s", cudaGetErrorString(e));
@@ -112,7 +127,10 @@ int mm_symm_close(void* peer_ptr) {
 }
 
 int mm_symm_free(void* dptr) {
-  if (!dptr) return MM_ERR_ARG;
+  if (!dptr) {
+    set_error("mm_symm_free: null argument");
+    return MM_ERR_ARG;
+  }
   cudaError_t e = cudaFree(dptr);
   if (e != cudaSuccess) {
     set_error("mm_symm_free: %s", cudaGetErrorString(e));
