@@ -249,8 +249,8 @@ int mm_moonep_map_routes_host(const int32_t* route_in, const int32_t* expert_in,
                               int32_t* send_token, int32_t* send_bucket, int32_t* route_to_send,
                               int32_t* num_misplaced);
 
-/* MoonEP as a re-labelling of routes: physical[route] = d * 2 * E/R + p, the bucket that executes
- * the route, -1 for routes mm_route_local dropped (route_to_send < 0).  Inputs as for
+/* MoonEP as a re-labelling of routes: physical [num_routes] out, physical[route] = d * 2 * E/R + p,
+ * the bucket that executes the route, -1 for routes mm_route_local dropped (route_to_send < 0).  Inputs as for
  * mm_moonep_map_routes (expert_start and below from mm_moonep_count_cube).  Running the ordinary
  * routing (mm_route_local, mm_count_exchange, mm_route_finalize) with `physical` as the expert ids
  * of a layer of 2 * E experts yields the balanced send order, count cube and offsets, so the
