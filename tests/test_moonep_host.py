@@ -306,3 +306,60 @@ def test_flags_must_be_bools():
         build_balanced_routing_metadata(*args, rank=0, use_direct_bucket_scatter=1)
     plan = build_balanced_routing_metadata(*args, rank=0)
     assert plan.balanced_buckets.tolist() == [0, 1] and plan.physical_slots_per_rank == 4
+
+
+# ------------------------------------------------------------------------------------------
+# world_size-2 gloo ranks: every rank plans from the gathered counts and gets the same plan
+# ------------------------------------------------------------------------------------------
+def _gloo_moonep_worker(rank, world, port, q):
+    import os
+    import torch.distributed as dist
+    sys.path[:0] = [str(REPO), str(REPO / "mega-moe-td_b200")]
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    experts, tokens, top_k = 8, 40, 2
+    gen = torch.Generator().manual_seed(100 + rank)
+    hot = torch.zeros(tokens, 1, dtype=torch.int32)                     # every token picks expert 0
+    other = torch.randint(1, experts, (tokens, 1), generator=gen, dtype=torch.int32)
+    selected = torch.cat([hot, other], dim=1).contiguous()
+    row = torch.bincount(selected.reshape(-1).long(), minlength=experts).to(torch.int32)
+    cube = torch.zeros(world * experts, dtype=torch.int32)
+    dist.all_gather_into_tensor(cube, row)
+    tpe = cube.view(world, experts).contiguous()
+    plan = plan_moonep_b0_b3(tpe)
+    inverse = build_inverse_experts_to_copy(plan.experts_to_copy, experts)
+    mine = build_balanced_routing_metadata(selected, tpe, plan.alloc_cumsum, inverse, rank)
+    # the plans of all ranks are identical, and so are their views of the whole cube
+    tables = torch.cat([plan.alloc_cumsum.reshape(-1), plan.experts_to_copy.reshape(-1),
+                        mine.balanced_counts.reshape(-1)])
+    gathered = [torch.zeros_like(tables) for _ in range(world)]
+    dist.all_gather(gathered, tables)
+    ok = all(torch.equal(g, tables) for g in gathered)
+    # what this rank sends to rank d is what rank d expects from it
+    sent = mine.balanced_counts[rank].view(world, -1)
+    expect = [torch.zeros_like(mine.receive_counts_by_source_slot) for _ in range(world)]
+    dist.all_gather(expect, mine.receive_counts_by_source_slot)
+    ok &= all(torch.equal(sent[d], expect[d][rank]) for d in range(world))
+    ok &= int(mine.received_slot_offsets[-1]) == tokens * top_k          # balanced: equal loads
+    ok &= bool((plan.experts_to_copy >= 0).any())                        # a replica was needed
+    q.put((rank, bool(ok)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_derive_the_same_plan_and_matching_counts():
+    import os
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    world = 2
+    port = 29750 + (os.getpid() % 40)
+    procs = [ctx.Process(target=_gloo_moonep_worker, args=(r, world, port, q)) for r in range(world)]
+    for proc in procs:
+        proc.start()
+    results = dict(q.get(timeout=120) for _ in range(world))
+    for proc in procs:
+        proc.join(timeout=60)
+        assert proc.exitcode == 0
+    assert results == {0: True, 1: True}
