@@ -59,3 +59,60 @@ def test_size_limits_and_shapes_are_reported():
     # scratch sizing of the route filter: (blocks of 2048 routes + 1) x bins x 4 bytes
     assert lib.mm_route_scratch_bytes(4096, 1024) == 3 * 1024 * 4
     assert lib.mm_route_scratch_bytes(-1, 8) == 0
+
+
+def _gemm_desc(**over):
+    buf = (C.c_int32 * 64)()
+    base = C.addressof(buf)                      # 16-byte aligned? make it so
+    base = (base + 15) & ~15
+    d = N.GemmDesc()
+    d.a, d.lda, d.a_rows_cap = base, 64, 128
+    d.b, d.b_k_major, d.b_cols_total, d.b_ld, d.b_group_stride = base, 1, 64, 64, 64 * 64
+    d.num_groups, d.N, d.K, d.grid_limit, d.pair = 1, 64, 64, 0, 0
+    d.group_offs = d.mtile_group = d.mtile_row0 = d.num_mtiles = base
+    for k, v in over.items():
+        setattr(d, k, v)
+    d._keep = buf
+    return d, base
+
+
+def test_grouped_gemm_descriptor_checks_precede_any_device_call():
+    lib = N.lib()
+    d, base = _gemm_desc(a=0)
+    d.a = base + 2                                                   # not 16-byte aligned
+    assert lib.mm_grouped_gemm(C.byref(d), None, base, 64, None) == MM_ERR_ARG
+    assert b"16-byte aligned" in lib.mm_last_error()
+    d, base = _gemm_desc(lda=68)                                     # stride not a multiple of 8
+    assert lib.mm_grouped_gemm(C.byref(d), None, base, 64, None) == MM_ERR_ARG
+    d, base = _gemm_desc(K=60)
+    assert lib.mm_grouped_gemm(C.byref(d), None, base, 64, None) == MM_ERR_ARG
+    assert b"K % 8 == 0" in lib.mm_last_error()
+    d, base = _gemm_desc(N=48)
+    assert lib.mm_grouped_gemm(C.byref(d), None, base, 64, None) == MM_ERR_ARG
+    d, base = _gemm_desc(pair=3)
+    assert lib.mm_grouped_gemm(C.byref(d), None, base, 64, None) == MM_ERR_ARG
+    assert b"tile mode 3" in lib.mm_last_error()
+    # a fused-dispatch descriptor with missing tables is refused before the GEMM is looked at
+    d, base = _gemm_desc()
+    x = N.DispatchDesc()
+    x.src, x.hidden, x.world, x.epr, x.epoch = base, 64, 1, 1, 1
+    assert lib.mm_grouped_gemm(C.byref(d), C.byref(x), base, 64, None) == MM_ERR_ARG
+    assert b"fused dispatch descriptor" in lib.mm_last_error()
+
+
+def test_weight_gradient_extent_checks():
+    lib = N.lib()
+    buf = (C.c_int32 * 64)()
+    base = (C.addressof(buf) + 15) & ~15
+    args = dict(grad_out=base, ld_go=64, Mw=64, orig_in=base, ld_in=64, Nw=64, rows_cap=128,
+                group_offs=base, num_groups=1, out=base, ld_out=64, out_group_stride=64 * 64,
+                status=None, grid_limit=0, pair=0, stream=None)
+
+    def call(**over):
+        a = dict(args, **over)
+        return lib.mm_grouped_wgrad(*a.values())
+
+    assert call(Mw=60) == MM_ERR_ARG and b"multiples of 8" in lib.mm_last_error()
+    assert call(Nw=48) == MM_ERR_ARG
+    assert call(ld_out=66) == MM_ERR_ARG
+    assert call(out=base + 4) == MM_ERR_ARG and b"16-byte aligned" in lib.mm_last_error()
