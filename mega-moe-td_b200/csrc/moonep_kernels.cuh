@@ -162,7 +162,7 @@ __device__ __forceinline__ int cube_block_scan(int v, int* warp_sums) {
   return warp_sums[w] + inc - v;
 }
 
-__global__ void __launch_bounds__(kCubeThreads)
+__global__ void __launch_bounds__(kCubeThreads, 1)
 moonep_cube_kernel(const int32_t* __restrict__ counts, int stride, int rank, int world,
                    int num_experts, const int32_t* __restrict__ alloc_cumsum,
                    const int32_t* __restrict__ experts_to_copy, int32_t* __restrict__ cube,
