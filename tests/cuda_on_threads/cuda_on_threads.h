@@ -167,6 +167,8 @@ inline unsigned __float_as_uint(float f) {
 inline void __syncthreads() { ::cot::self().cta->barrier.wait(); }
 inline void __syncwarp() { ::cot::my_warp().barrier.wait(); }
 inline void __threadfence() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
+inline void __threadfence_system() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
+inline void __nanosleep(unsigned) { std::this_thread::yield(); }
 
 template <class T>
 T __shfl_xor_sync(unsigned, T v, int lane_mask) {

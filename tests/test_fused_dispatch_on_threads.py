@@ -31,46 +31,7 @@ sys.path.insert(0, str(HERE))
 
 from oracle import moe_oracle as O  # noqa: E402
 
-OPERAND = r'"(=?[rl])"\(((?:[^()]|\((?:[^()]|\([^()]*\))*\))*)\)'
-
-
-def map_ptx(text: str) -> str:
-    """Replace each ``asm volatile(...)`` statement of the dispatch code by host code of the same
-    meaning; fail on any instruction this test does not know."""
-    out, pos = [], 0
-    while True:
-        i = text.find("asm volatile(", pos)
-        if i < 0:
-            out.append(text[pos:])
-            return "".join(out)
-        j = text.index(");", i) + 2
-        stmt = text[i:j]
-        instr = re.search(r'"([^"]+)"', stmt).group(1)
-        ops = re.findall(OPERAND, stmt[stmt.index(instr) + len(instr):])
-        outs = [e for kind, e in ops if kind.startswith("=")]
-        ins = [e for kind, e in ops if not kind.startswith("=")]
-        if instr.startswith("ld.global.nc") and ".v4.u32" in instr:
-            new = ("{ const uint4 t_ = *reinterpret_cast<const uint4*>(%s); %s = t_.x; %s = t_.y; "
-                   "%s = t_.z; %s = t_.w; }" % (ins[0], *outs))
-        elif instr.startswith("st.release.sys.global.s32"):
-            new = "__atomic_store_n((int32_t*)(%s), (int32_t)(%s), __ATOMIC_RELEASE);" % tuple(ins)
-        elif instr.startswith("atom.add.acq_rel.gpu.global.s32"):
-            new = "%s = __atomic_fetch_add((int32_t*)(%s), 1, __ATOMIC_ACQ_REL);" % (outs[0], ins[0])
-        elif instr.startswith("ld.acquire.sys.global.s32"):
-            new = "%s = __atomic_load_n((const int32_t*)(%s), __ATOMIC_ACQUIRE);" % (outs[0], ins[0])
-        elif instr.startswith("fence.proxy.async"):
-            new = ";"
-        else:
-            raise AssertionError(f"unknown PTX in the dispatch code: {instr}")
-        out.append(text[pos:i] + new)
-        pos = j
-
-
-def cut(text: str, start: str, end: str = "\n}\n") -> str:
-    i = text.index(start)
-    i = text.rfind("\n", 0, i) + 1
-    j = text.index(end, i) + len(end)
-    return text[i:j]
+from cuda_on_threads.host_build import cut, map_ptx  # noqa: E402
 
 
 HARNESS = r"""
