@@ -387,3 +387,22 @@ def test_saved_index_section_from_plan_tables(world, experts, top_k, tokens):
         lazy = FusedMoEForward._saved_index_section(op, plan, m, sent, False)
         assert lazy["splits_send_list"] is None and lazy["meta_expert_ids"] is None
         assert torch.equal(lazy["inv_sort"], got["inv_sort"])
+
+
+def test_epochs_grow_and_exhaustion_raises_instead_of_wrapping():
+    """Flags carry epochs that only grow (the reference's rule, ops/forward.py:368-385,
+    tests/function/test_single_replica_epoch.py:57-62): at the end of the int32 range the
+    context raises instead of wrapping to a value an old flag could satisfy."""
+    from mega_moe.runtime.workspace import MoEForwardContext
+    ctx = MoEForwardContext(hidden_size=64, num_experts=8, experts_per_rank=4, replica_budget=0,
+                            physical_experts_per_rank=4, world_size=2, rank=0,
+                            receive_capacity_factor=1.0, max_source_tiles=1)
+    first = [ctx.next_dispatch_epoch() for _ in range(3)]
+    assert first == sorted(first) and len(set(first)) == 3 and first[0] >= 1
+    ctx.dispatch_epoch = 2**31 - 3
+    assert ctx.next_dispatch_epoch() == 2**31 - 2
+    with pytest.raises(RuntimeError, match="epoch exhausted"):
+        ctx.next_dispatch_epoch()
+    ctx.barrier_epoch = 2**31 - 2
+    with pytest.raises(RuntimeError, match="epoch exhausted"):
+        ctx._next_epoch()
